@@ -1,0 +1,91 @@
+"""Shared builders for the test suite: seeded inputs and the tiny random-init decoder of
+configuration 0 (2 layers, hidden 256, 4 q / 2 kv heads, head_dim 64, SwiGLU 688, vocab 1024)."""
+import numpy as np
+
+INC = np.uint64(0x9E3779B97F4A7C15)
+
+
+def splitmix_stream(seed, n):
+    """First n outputs of SplitMix64(seed) (src/primitives/sampler.rs:36-61), vectorised."""
+    with np.errstate(over="ignore"):
+        z = np.uint64(seed) + (np.arange(1, n + 1, dtype=np.uint64)) * INC
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return z ^ (z >> np.uint64(31))
+
+
+def splitmix_f32(seed, n):
+    return ((splitmix_stream(seed, n) >> np.uint64(40)).astype(np.float32)) / np.float32(1 << 24)
+
+
+class NormalStream:
+    """N(0,1) draws from one SplitMix64 stream via Box-Muller, two uniforms per value, in draw order."""
+
+    def __init__(self, seed):
+        self.seed = seed
+        self.used = 0
+
+    def normal(self, n):
+        u = splitmix_f32(self.seed, self.used + 2 * n)[self.used:]
+        self.used += 2 * n
+        u1 = np.maximum(u[0::2].astype(np.float64), 2.0 ** -25)
+        u2 = u[1::2].astype(np.float64)
+        return (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(np.float32)
+
+
+CONFIG0 = dict(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=688, vocab=1024, eps=1e-5, theta=10000.0,
+               rope_kind=0, rope_factor=1.0, rope_low=1.0, rope_high=4.0, rope_orig=8192.0, qk_norm=0, quant_bits=0, group=64,
+               f32_mode=0)
+CONFIG0_PROMPT_LENS = [17, 33, 64, 129]
+
+
+def tiny_weights(cfg=CONFIG0, seed=0, std=0.02):
+    """Weights ~ N(0, std) drawn from SplitMix64(seed) in the order: embed, lm_head, then per layer
+    q, k, v, o, gate, up, down.  Norm weights are ones."""
+    ns = NormalStream(seed)
+    H, qd, kvd, I, V = cfg["hidden"], cfg["heads"] * cfg["head_dim"], cfg["kv_heads"] * cfg["head_dim"], cfg["inter"], cfg["vocab"]
+    w = {"embed": (ns.normal(V * H) * std).reshape(V, H), "lm_head": (ns.normal(V * H) * std).reshape(V, H), "layers": []}
+    shapes = dict(q=(qd, H), k=(kvd, H), v=(kvd, H), o=(H, qd), gate=(I, H), up=(I, H), down=(H, I))
+    for _ in range(cfg["layers"]):
+        w["layers"].append({k: (ns.normal(s[0] * s[1]) * std).reshape(s) for k, s in shapes.items()})
+    return w
+
+
+def config0_prompts(seed=1, vocab=1024, lens=CONFIG0_PROMPT_LENS):
+    u = splitmix_f32(seed, sum(lens))
+    ids = np.minimum((u * vocab).astype(np.int32), vocab - 1)
+    out, o = [], 0
+    for n in lens:
+        out.append(ids[o:o + n].copy())
+        o += n
+    return out
+
+
+def build_oracle_model(orc, cfg=CONFIG0, weights=None, quant_bits=0):
+    """Load the tiny weights into an oracle model; quant_bits quantizes the projections on load."""
+    weights = weights or tiny_weights(cfg)
+    m = orc.Model(**cfg)
+    m.set_dense(0, "embed", weights["embed"])
+    m.set_dense(0, "lm_head", weights["lm_head"])
+    m.set_norm(0, "norm", np.ones(cfg["hidden"], np.float32))
+    for l, lw in enumerate(weights["layers"]):
+        for k, v in lw.items():
+            m.set_dense(l, k, v)
+            if quant_bits:
+                m.quantize_projection(l, k, quant_bits)
+        m.set_norm(l, "input_ln", np.ones(cfg["hidden"], np.float32))
+        m.set_norm(l, "post_ln", np.ones(cfg["hidden"], np.float32))
+        if cfg.get("qk_norm"):
+            m.set_norm(l, "q_norm", np.ones(cfg["head_dim"], np.float32))
+            m.set_norm(l, "k_norm", np.ones(cfg["head_dim"], np.float32))
+    return m
+
+
+def lcg_randf(n, seed):
+    """The reference attention tests' input generator (src/primitives/attention.rs:312-322)."""
+    out = np.empty(n, np.float32)
+    s = seed & 0xFFFFFFFFFFFFFFFF
+    for i in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        out[i] = np.float32(np.float32(s >> 40) / np.float32(1 << 24)) * np.float32(2.0) - np.float32(1.0)
+    return out
