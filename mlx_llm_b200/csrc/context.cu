@@ -1,0 +1,156 @@
+// Context, error reporting and raw device-memory plumbing of the C ABI.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+static thread_local std::string g_last_error;
+
+void b2_set_error(const std::string& msg) { g_last_error = msg; }
+int32_t b2_fail(int32_t code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+extern "C" {
+
+const char* b2_last_error(void) { return g_last_error.c_str(); }
+int32_t b2_version(void) { return 100; }
+
+int32_t b2_device_count(int32_t* out) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *out = 0;
+        return b2_fail(B2_ERR_CUDA, std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e));
+    }
+    *out = n;
+    return B2_OK;
+}
+
+int32_t b2_ctx_create(int32_t device, b2_ctx** out) {
+    B2_REQUIRE(out != nullptr, B2_ERR_MSG, "b2_ctx_create: null out");
+    int n = 0;
+    B2_CUDA(cudaGetDeviceCount(&n));
+    B2_REQUIRE(n > 0, B2_ERR_CUDA, "b2_ctx_create: no CUDA device (this library has no CPU fallback)");
+    B2_REQUIRE(device >= 0 && device < n, B2_ERR_MSG, "b2_ctx_create: device index out of range");
+    B2_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    B2_CUDA(cudaGetDeviceProperties(&prop, device));
+    B2_REQUIRE(prop.major >= 10, B2_ERR_UNSUPPORTED,
+               std::string("b2_ctx_create: kernels are built for sm_100a only; device is ") + prop.name);
+    b2_ctx* c = new b2_ctx();
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    B2_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    B2_CUDA(cudaEventCreate(&c->ev0));
+    B2_CUDA(cudaEventCreate(&c->ev1));
+    *out = c;
+    return B2_OK;
+}
+
+int32_t b2_ctx_free(b2_ctx* ctx) {
+    if (!ctx) return B2_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+    if (ctx->stage) cudaFree(ctx->stage);
+    cudaEventDestroy(ctx->ev0);
+    cudaEventDestroy(ctx->ev1);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return B2_OK;
+}
+
+int32_t b2_ctx_sync(b2_ctx* ctx) {
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int32_t b2_malloc(b2_ctx* ctx, size_t bytes, void** out_dev) {
+    B2_CUDA(cudaSetDevice(ctx->device));
+    B2_CUDA(cudaMalloc(out_dev, bytes ? bytes : 16));
+    return B2_OK;
+}
+int32_t b2_free(b2_ctx* ctx, void* dev) {
+    B2_CUDA(cudaSetDevice(ctx->device));
+    B2_CUDA(cudaFree(dev));
+    return B2_OK;
+}
+int32_t b2_memcpy_h2d(b2_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+    B2_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    return B2_OK;
+}
+int32_t b2_memcpy_d2h(b2_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
+    B2_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    return B2_OK;
+}
+int32_t b2_memset(b2_ctx* ctx, void* dst_dev, int value, size_t bytes) {
+    B2_CUDA(cudaMemsetAsync(dst_dev, value, bytes, ctx->stream));
+    return B2_OK;
+}
+int32_t b2_host_alloc_pinned(size_t bytes, void** out_host) {
+    B2_CUDA(cudaHostAlloc(out_host, bytes ? bytes : 16, cudaHostAllocDefault));
+    return B2_OK;
+}
+int32_t b2_host_free_pinned(void* host) {
+    B2_CUDA(cudaFreeHost(host));
+    return B2_OK;
+}
+
+int32_t b2_timer_start(b2_ctx* ctx) {
+    B2_CUDA(cudaEventRecord(ctx->ev0, ctx->stream));
+    return B2_OK;
+}
+int32_t b2_timer_stop_ms(b2_ctx* ctx, float* ms_out) {
+    B2_CUDA(cudaEventRecord(ctx->ev1, ctx->stream));
+    B2_CUDA(cudaEventSynchronize(ctx->ev1));
+    B2_CUDA(cudaEventElapsedTime(ms_out, ctx->ev0, ctx->ev1));
+    return B2_OK;
+}
+
+int32_t b2_flush_l2(b2_ctx* ctx) {
+    const size_t bytes = 256ull << 20;  // 2x the 126 MB L2
+    if (!ctx->flush_buf) {
+        B2_CUDA(cudaMalloc(&ctx->flush_buf, bytes));
+        ctx->flush_bytes = bytes;
+    }
+    B2_CUDA(cudaMemsetAsync(ctx->flush_buf, 1, ctx->flush_bytes, ctx->stream));
+    return B2_OK;
+}
+
+int32_t b2_launch_count(b2_ctx* ctx, int64_t* out) {
+    *out = ctx->launches;
+    return B2_OK;
+}
+
+}  // extern "C"
+
+int32_t b2_ctx_scratch(b2_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->scratch_bytes) {
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch) B2_CUDA(cudaFree(ctx->scratch));
+        ctx->scratch = nullptr;
+        size_t want = bytes + (bytes >> 2) + (1 << 20);
+        B2_CUDA(cudaMalloc(&ctx->scratch, want));
+        ctx->scratch_bytes = want;
+    }
+    *out = ctx->scratch;
+    return B2_OK;
+}
+int32_t b2_ctx_stage(b2_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->stage_bytes) {
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->stage) B2_CUDA(cudaFree(ctx->stage));
+        ctx->stage = nullptr;
+        size_t want = bytes + (bytes >> 2) + (1 << 16);
+        B2_CUDA(cudaMalloc(&ctx->stage, want));
+        ctx->stage_bytes = want;
+    }
+    *out = ctx->stage;
+    return B2_OK;
+}

@@ -1,0 +1,390 @@
+// Paged-attention decode for sm_100a: one query token per sequence over a paged bf16 KV pool.
+//
+// Replaces the reference's gather-then-SDPA decode (src/primitives/paged_kv_cache.rs:342-354
+// concatenates the whole sequence every layer every step, then src/primitives/attention.rs:87-102
+// runs the stock fused SDPA on the copy): here K/V pages are read in place, once.
+//
+// Work decomposition
+//   CTA        = (split-K work item, kv head): a chunk of `chunk_tiles` 16-token tiles of one
+//                sequence, all q heads of the GQA group at once (K/V bytes are read once per group).
+//   warp       = every 4th tile of the chunk, with a private 3-stage cp.async pipeline
+//                (16-byte coalesced copies, XOR-swizzled rows so ldmatrix is conflict free);
+//                no CTA-wide barrier inside the main loop.
+//   tensor op  = mma.sync m16n8k16 with the 16 TOKENS of a tile on M and the (<= 8) q heads of
+//                the group on N:  S^T = K Q^T, then O^T += V^T P^T.  P^T reaches the B-operand
+//                layout with one movmatrix per 8 tokens.  Softmax statistics are per column,
+//                reduced with three xor-shuffles.
+//   merge      = per-CTA cross-warp log-sum-exp merge in shared memory; chunks of a sequence are
+//                merged by a second small kernel (skipped for single-chunk sequences).
+// This is HBM-bound byte streaming: the tensor cores are used only to keep the CUDA cores off the
+// critical path, so no tcgen05/TMEM here.
+#include <cfloat>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+constexpr unsigned kFull = 0xffffffffu;
+
+template <int HD>
+__global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const DecodeAttnParams p) {
+    constexpr int ROWB = HD * 2;        // bytes per token row of one head
+    constexpr int CHUNKS = ROWB / 16;   // 16-byte chunks per row
+    constexpr int TILE_B = 16 * ROWB;   // bytes of a 16-token tile
+    constexpr int KSTEPS = HD / 16;
+    constexpr int MT = HD / 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+
+    const int w = blockIdx.x;
+    if (w >= *p.n_work) return;
+    const int kvh = blockIdx.y;
+    const int seq = p.work_seq[w], chunk = p.work_chunk[w];
+    const int ctx = p.ctx_lens[seq];
+    const int tiles_total = (ctx + 15) >> 4;
+    const int tile0 = chunk * p.chunk_tiles;
+    const int n_tiles = min(p.chunk_tiles, tiles_total - tile0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int group = p.hq / p.hkv;
+    const int qrow = p.q_rows ? p.q_rows[seq] : seq;
+
+    // Q^T as the B operand: thread (g,t) holds Q[head g][16*ks + 2t, +1] and [.. + 8, + 9].
+    uint32_t qf[KSTEPS][2];
+    {
+        const uint16_t* qh = p.q + ((size_t)qrow * p.hq + (size_t)kvh * group + g) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            qf[ks][0] = g < group ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = g < group ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8) : 0u;
+        }
+    }
+
+    const int n_my = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
+    const int32_t* bt = p.block_tables + (size_t)(p.bt_rows ? p.bt_rows[seq] : seq) * p.max_blocks;
+    // lane i keeps the physical page of this warp's i-th tile
+    int my_page = 0;
+    if (lane < n_my) my_page = bt[(tile0 + warp + lane * kWarps) / p.page_tiles];
+
+    const uint32_t wsm = smem_u32(smem) + warp * (kStages * 2 * TILE_B);
+
+    auto issue = [&](int i) {
+        const int tile = tile0 + warp + i * kWarps;
+        const int page = __shfl_sync(kFull, my_page, i);
+        const size_t off = (((size_t)page * p.hkv + kvh) * p.page_tiles + (tile % p.page_tiles)) * (size_t)(16 * HD);
+        const uint8_t* ks = reinterpret_cast<const uint8_t*>(p.k_pool + off);
+        const uint8_t* vs = reinterpret_cast<const uint8_t*>(p.v_pool + off);
+        const uint32_t dst = wsm + (i % kStages) * 2 * TILE_B;
+#pragma unroll
+        for (int c = lane; c < 16 * CHUNKS; c += 32) {
+            const int r = c / CHUNKS, cc = c % CHUNKS;
+            const uint32_t o = r * ROWB + ((cc ^ (r & 7)) << 4);
+            cp_async16(dst + o, ks + (size_t)c * 16);
+            cp_async16(dst + TILE_B + o, vs + (size_t)c * 16);
+        }
+    };
+
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+
+#pragma unroll
+    for (int i = 0; i < kStages - 1; i++) {
+        if (i < n_my) issue(i);
+        cp_async_commit();
+    }
+    const int mi = lane >> 3, lr = lane & 7;
+    for (int i = 0; i < n_my; i++) {
+        if (i + kStages - 1 < n_my) issue(i + kStages - 1);
+        cp_async_commit();
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+        const uint32_t kb = wsm + (i % kStages) * 2 * TILE_B, vb = kb + TILE_B;
+
+        // S^T[token, head] = K[token, :] . Q[head, :]
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int r = lr + (mi & 1) * 8;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                const int ch = 2 * ks + (mi >> 1);
+                uint32_t a[4];
+                ldmatrix_x4(a[0], a[1], a[2], a[3], kb + r * ROWB + ((ch ^ (r & 7)) << 4));
+                mma_bf16_16816(s, a, qf[ks]);
+            }
+        }
+        const int tok0 = (tile0 + warp + i * kWarps) * 16;
+#pragma unroll
+        for (int j = 0; j < 4; j++) s[j] *= p.scale_log2;
+        if (tok0 + 16 > ctx) {
+            if (tok0 + g >= ctx) s[0] = s[1] = -INFINITY;
+            if (tok0 + g + 8 >= ctx) s[2] = s[3] = -INFINITY;
+        }
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int sh = 4; sh <= 16; sh <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, sh));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, sh));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+        const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
+        const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
+        l0 = l0 * a0 + p0 + p2;
+        l1 = l1 * a1 + p1 + p3;
+        m0 = mn0;
+        m1 = mn1;
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            o[mt][0] *= a0;
+            o[mt][1] *= a1;
+            o[mt][2] *= a0;
+            o[mt][3] *= a1;
+        }
+        // P^T as the B operand (tokens on K, heads on N)
+        uint32_t pb[2];
+        pb[0] = movmatrix_trans(pack_bf2(p0, p1));
+        pb[1] = movmatrix_trans(pack_bf2(p2, p3));
+        // O^T[d, head] += V^T[d, token] P^T[token, head]
+        {
+            const int r = lr + (mi >> 1) * 8;
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const int ch = 2 * mt + (mi & 1);
+                uint32_t a[4];
+                ldmatrix_x4_trans(a[0], a[1], a[2], a[3], vb + r * ROWB + ((ch ^ (r & 7)) << 4));
+                mma_bf16_16816(o[mt], a, pb);
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int sh = 4; sh <= 16; sh <<= 1) {
+        l0 += __shfl_xor_sync(kFull, l0, sh);
+        l1 += __shfl_xor_sync(kFull, l1, sh);
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // cross-warp merge through shared memory (pipeline buffers are free now)
+    float* so = reinterpret_cast<float*>(smem);      // [kWarps][HD][8]
+    float* sm_m = so + kWarps * HD * 8;              // [kWarps][8]
+    float* sm_l = sm_m + kWarps * 8;                 // [kWarps][8]
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        float* base = so + ((size_t)warp * HD + 16 * mt + g) * 8 + 2 * t;
+        base[0] = o[mt][0];
+        base[1] = o[mt][1];
+        base[64] = o[mt][2];  // row g + 8
+        base[65] = o[mt][3];
+    }
+    if (g == 0) {
+        sm_m[warp * 8 + 2 * t] = m0;
+        sm_m[warp * 8 + 2 * t + 1] = m1;
+        sm_l[warp * 8 + 2 * t] = l0;
+        sm_l[warp * 8 + 2 * t + 1] = l1;
+    }
+    __syncthreads();
+    const int n_chunks = p.seq_work_off[seq + 1] - p.seq_work_off[seq];
+    for (int e = threadIdx.x; e < group * HD; e += kWarps * 32) {
+        const int h = e / HD, d = e % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int ww = 0; ww < kWarps; ww++) M = fmaxf(M, sm_m[ww * 8 + h]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < kWarps; ww++) {
+            const float f = fast_exp2(sm_m[ww * 8 + h] - M);
+            L += sm_l[ww * 8 + h] * f;
+            O += so[((size_t)ww * HD + d) * 8 + h] * f;
+        }
+        if (n_chunks == 1) {
+            p.out[((size_t)qrow * p.hq + (size_t)kvh * group + h) * HD + d] = f2bf(O / L);
+        } else {
+            const size_t slot = ((size_t)w * p.hkv + kvh) * group + h;
+            p.part_o[slot * HD + d] = O;
+            if (d == 0) {
+                p.part_ml[slot * 2] = M;
+                p.part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// Merge the chunks of one (sequence, kv head): out = sum_c O_c 2^(m_c-M) / sum_c l_c 2^(m_c-M).
+template <int HD>
+__global__ void paged_attn_merge_kernel(const DecodeAttnParams p) {
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int w0 = p.seq_work_off[seq], n = p.seq_work_off[seq + 1] - w0;
+    if (n <= 1) return;
+    const int group = p.hq / p.hkv;
+    const int qrow = p.q_rows ? p.q_rows[seq] : seq;
+    for (int e = threadIdx.x; e < group * HD; e += blockDim.x) {
+        const int h = e / HD, d = e % HD;
+        float M = -INFINITY;
+        for (int c = 0; c < n; c++) M = fmaxf(M, p.part_ml[((((size_t)(w0 + c)) * p.hkv + kvh) * group + h) * 2]);
+        float L = 0.f, O = 0.f;
+        for (int c = 0; c < n; c++) {
+            const size_t slot = ((size_t)(w0 + c) * p.hkv + kvh) * group + h;
+            const float f = fast_exp2(p.part_ml[slot * 2] - M);
+            L += p.part_ml[slot * 2 + 1] * f;
+            O += p.part_o[slot * HD + d] * f;
+        }
+        p.out[((size_t)qrow * p.hq + (size_t)kvh * group + h) * HD + d] = f2bf(O / L);
+    }
+}
+
+// Split-K work list for a plain [num_seqs] batch (the engine's packer builds the same list
+// together with the rest of the step metadata).
+__global__ void decode_worklist_kernel(const int32_t* ctx_lens, int num_seqs, int chunk_tiles, int32_t* work_seq,
+                                       int32_t* work_chunk, int32_t* seq_work_off, int32_t* n_work) {
+    __shared__ int sh[1024];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < num_seqs; base += 1024) {
+        const int i = base + threadIdx.x;
+        int n = 0;
+        if (i < num_seqs) {
+            const int tiles = (ctx_lens[i] + 15) >> 4;
+            n = (tiles + chunk_tiles - 1) / chunk_tiles;
+        }
+        sh[threadIdx.x] = n;
+        __syncthreads();
+        for (int d = 1; d < 1024; d <<= 1) {
+            int v = threadIdx.x >= d ? sh[threadIdx.x - d] : 0;
+            __syncthreads();
+            sh[threadIdx.x] += v;
+            __syncthreads();
+        }
+        const int incl = sh[threadIdx.x] + carry, excl = incl - n;
+        if (i < num_seqs) {
+            seq_work_off[i] = excl;
+            for (int c = 0; c < n; c++) {
+                work_seq[excl + c] = i;
+                work_chunk[excl + c] = c;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        seq_work_off[num_seqs] = carry;
+        *n_work = carry;
+    }
+}
+
+template <int HD>
+int32_t launch_decode(b2_ctx* ctx, const DecodeAttnParams& p, int grid_work, int num_seqs) {
+    const int smem = kWarps * kStages * 2 * 16 * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        B2_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    dim3 grid(grid_work, p.hkv);
+    paged_attn_decode_kernel<HD><<<grid, kWarps * 32, smem, ctx->stream>>>(p);
+    B2_LAUNCHED(ctx);
+    const int group = p.hq / p.hkv;
+    int threads = group * HD;
+    if (threads > 1024) threads = 1024;
+    paged_attn_merge_kernel<HD><<<dim3(num_seqs, p.hkv), threads, 0, ctx->stream>>>(p);
+    B2_LAUNCHED(ctx);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+}  // namespace
+
+size_t b2_decode_attn_scratch_bytes(int max_work, int hq, int head_dim) {
+    // part_o [work, hq, hd] f32 + part_ml [work, hq, 2] f32
+    return (size_t)max_work * hq * (head_dim + 2) * sizeof(float);
+}
+
+int32_t b2_decode_attn_launch(b2_ctx* ctx, const DecodeAttnParams& p, int head_dim, int grid_work, int num_seqs) {
+    const int group = p.hq / p.hkv;
+    B2_REQUIRE(p.hq % p.hkv == 0 && (group == 1 || group == 2 || group == 4 || group == 8), B2_ERR_UNSUPPORTED,
+               "paged_attn_decode: q heads per kv head must be 1, 2, 4 or 8");
+    B2_REQUIRE(p.chunk_tiles >= 1 && p.chunk_tiles <= 32 * kWarps, B2_ERR_MSG, "paged_attn_decode: chunk must be 16..2048 tokens");
+    if (grid_work <= 0 || num_seqs <= 0) return B2_OK;
+    if (head_dim == 128) return launch_decode<128>(ctx, p, grid_work, num_seqs);
+    if (head_dim == 64) return launch_decode<64>(ctx, p, grid_work, num_seqs);
+    return b2_fail(B2_ERR_UNSUPPORTED, "paged_attn_decode: head_dim must be 64 or 128");
+}
+
+extern "C" int32_t b2_paged_attn_decode(b2_ctx* ctx, const uint16_t* q_dev, const uint16_t* k_pool_dev,
+                                        const uint16_t* v_pool_dev, const int32_t* block_tables_dev, int32_t max_blocks,
+                                        const int32_t* ctx_lens_dev, int32_t num_seqs, int32_t hq, int32_t hkv,
+                                        int32_t head_dim, int32_t page_size, float scale, int32_t chunk_tokens,
+                                        uint16_t* out_dev) {
+    B2_REQUIRE(ctx && q_dev && k_pool_dev && v_pool_dev && block_tables_dev && ctx_lens_dev && out_dev, B2_ERR_MSG,
+               "b2_paged_attn_decode: null argument");
+    B2_REQUIRE(num_seqs >= 0 && max_blocks > 0, B2_ERR_MSG, "b2_paged_attn_decode: bad sizes");
+    B2_REQUIRE(page_size > 0 && page_size % 16 == 0, B2_ERR_UNSUPPORTED, "b2_paged_attn_decode: page_size must be a multiple of 16");
+    B2_REQUIRE(hkv > 0 && hq % hkv == 0, B2_ERR_MSG, "b2_paged_attn_decode: hq must be a multiple of hkv");
+    if (num_seqs == 0) return B2_OK;
+    if (chunk_tokens <= 0) chunk_tokens = 256;
+    B2_REQUIRE(chunk_tokens % 16 == 0, B2_ERR_MSG, "b2_paged_attn_decode: chunk_tokens must be a multiple of 16");
+    const int chunk_tiles = chunk_tokens / 16;
+    const int page_tiles = page_size / 16;
+    const long max_tiles = (long)max_blocks * page_tiles;
+    const long per_seq = (max_tiles + chunk_tiles - 1) / chunk_tiles;
+    const long max_work = per_seq * num_seqs;
+    B2_REQUIRE(max_work < (1l << 30), B2_ERR_MSG, "b2_paged_attn_decode: work list too large");
+
+    // scratch: partials, then the work list
+    size_t part_bytes = b2_decode_attn_scratch_bytes((int)max_work, hq, head_dim);
+    part_bytes = (part_bytes + 255) & ~(size_t)255;
+    const size_t list_bytes = ((size_t)max_work * 2 + num_seqs + 2) * sizeof(int32_t);
+    void* scratch = nullptr;
+    B2_CHECK(b2_ctx_scratch(ctx, part_bytes + list_bytes, &scratch));
+    DecodeAttnParams p{};
+    p.q = q_dev;
+    p.k_pool = k_pool_dev;
+    p.v_pool = v_pool_dev;
+    p.block_tables = block_tables_dev;
+    p.max_blocks = max_blocks;
+    p.ctx_lens = ctx_lens_dev;
+    p.chunk_tiles = chunk_tiles;
+    p.hq = hq;
+    p.hkv = hkv;
+    p.page_tiles = page_tiles;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.part_o = reinterpret_cast<float*>(scratch);
+    p.part_ml = p.part_o + (size_t)max_work * hq * head_dim;
+    int32_t* lists = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(scratch) + part_bytes);
+    int32_t* work_seq = lists;
+    int32_t* work_chunk = lists + max_work;
+    int32_t* seq_off = lists + 2 * max_work;
+    int32_t* n_work = seq_off + num_seqs + 1;
+    p.work_seq = work_seq;
+    p.work_chunk = work_chunk;
+    p.seq_work_off = seq_off;
+    p.n_work = n_work;
+    p.out = out_dev;
+    decode_worklist_kernel<<<1, 1024, 0, ctx->stream>>>(ctx_lens_dev, num_seqs, chunk_tiles, work_seq, work_chunk, seq_off, n_work);
+    B2_LAUNCHED(ctx);
+    return b2_decode_attn_launch(ctx, p, head_dim, (int)max_work, num_seqs);
+}
+
+extern "C" int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host, const uint16_t* k_pool_dev,
+                                             const uint16_t* v_pool_dev, const int32_t* block_tables_dev, int32_t max_blocks,
+                                             const int32_t* ctx_lens_dev, int32_t num_seqs, int32_t hq, int32_t hkv,
+                                             int32_t head_dim, int32_t page_size, float scale, int32_t chunk_tokens,
+                                             uint16_t* out_host) {
+    B2_REQUIRE(ctx && q_host && out_host, B2_ERR_MSG, "b2_paged_attn_decode_host: null argument");
+    const size_t bytes = (size_t)num_seqs * hq * head_dim * 2;
+    void* stage = nullptr;
+    B2_CHECK(b2_ctx_stage(ctx, 2 * bytes, &stage));
+    uint16_t* qd = reinterpret_cast<uint16_t*>(stage);
+    uint16_t* od = qd + bytes / 2;
+    B2_CUDA(cudaMemcpyAsync(qd, q_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    B2_CHECK(b2_paged_attn_decode(ctx, qd, k_pool_dev, v_pool_dev, block_tables_dev, max_blocks, ctx_lens_dev, num_seqs, hq, hkv,
+                                  head_dim, page_size, scale, chunk_tokens, od));
+    B2_CUDA(cudaMemcpyAsync(out_host, od, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    return B2_OK;
+}

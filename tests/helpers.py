@@ -89,3 +89,41 @@ def lcg_randf(n, seed):
         s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
         out[i] = np.float32(np.float32(s >> 40) / np.float32(1 << 24)) * np.float32(2.0) - np.float32(1.0)
     return out
+
+
+def f32_to_bf16_np(x):
+    """Round-to-nearest-even f32 -> bf16 bit patterns (uint16), numpy only."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    lsb = (u >> np.uint64(16)) & np.uint64(1)
+    return ((u + np.uint64(0x7FFF) + lsb) >> np.uint64(16)).astype(np.uint16)
+
+
+def bf16_to_f32_np(h):
+    return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def make_paged_case(seed, ctx_lens, hq, hkv, hd, page, q_lens=None, pool_factor=2):
+    """Seeded paged-KV case: N(0,1) q/K/V in bf16, pool of pool_factor x the needed pages, block
+    tables drawn from a random permutation of the physical pages (BASELINE configuration 1)."""
+    rng = np.random.default_rng(seed)
+    ctx_lens = np.asarray(ctx_lens, np.int32)
+    n = ctx_lens.size
+    q_lens = np.ones(n, np.int32) if q_lens is None else np.asarray(q_lens, np.int32)
+    pages_per = (ctx_lens + page - 1) // page
+    total = int(pages_per.sum())
+    pool_pages = max(1, pool_factor * total)
+    perm = rng.permutation(pool_pages).astype(np.int32)
+    max_blocks = int(max(1, pages_per.max()))
+    bt = np.zeros((n, max_blocks), np.int32)
+    o = 0
+    for i in range(n):
+        bt[i, : pages_per[i]] = perm[o:o + pages_per[i]]
+        o += pages_per[i]
+    kpool = f32_to_bf16_np(rng.standard_normal((pool_pages, hkv, page, hd), dtype=np.float32))
+    vpool = f32_to_bf16_np(rng.standard_normal((pool_pages, hkv, page, hd), dtype=np.float32))
+    T = int(q_lens.sum())
+    q = f32_to_bf16_np(rng.standard_normal((T, hq, hd), dtype=np.float32))
+    cu = np.zeros(n + 1, np.int32)
+    cu[1:] = np.cumsum(q_lens)
+    return dict(q=q, kpool=kpool, vpool=vpool, block_tables=bt, ctx_lens=ctx_lens, cu_seqlens=cu, max_blocks=max_blocks,
+                pool_pages=pool_pages, hq=hq, hkv=hkv, hd=hd, page=page, scale=float(hd) ** -0.5)

@@ -1,0 +1,136 @@
+"""Parity of the CUDA paged-attention decode kernel (through the C ABI) against the CPU oracle.
+
+Tolerance: max-abs 2e-3 on the bf16 output against the oracle's f64-accumulated result (BASELINE's
+bound) wherever the outputs stay below 1 in magnitude, which includes every configuration-1 shaped
+case.  Very short contexts give outputs of magnitude 2-4, where one bf16 output ulp alone is up to
+1.6e-2; there the reference's own relative gate applies (max|diff| / max|ref| < 2e-3,
+src/primitives/attention.rs:445-449, :457-480)."""
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def env():
+    from mlx_llm_b200 import _lib, kernels
+    from oracle import oracle as orc
+
+    ctx = _lib.Context(0)
+    yield ctx, kernels, orc
+    ctx.close()
+
+
+def run_case(env, case, chunk_tokens=0, host_io=False, strict_abs=False):
+    ctx, kernels, orc = env
+    n = case["ctx_lens"].size
+    kp, vp = ctx.buf(case["kpool"]), ctx.buf(case["vpool"])
+    bt, cl = ctx.buf(case["block_tables"]), ctx.buf(case["ctx_lens"])
+    args = (n, case["hq"], case["hkv"], case["hd"], case["page"], case["scale"])
+    if host_io:
+        out = np.zeros_like(case["q"])
+        kernels.paged_attn_decode_host(ctx, case["q"], kp, vp, bt, cl, *args, out, case["max_blocks"], chunk_tokens)
+    else:
+        q = ctx.buf(case["q"])
+        o = ctx.empty(case["q"].shape, np.uint16)
+        kernels.paged_attn_decode(ctx, q, kp, vp, bt, cl, *args, o, case["max_blocks"], chunk_tokens)
+        ctx.sync()
+        out = o.download()
+        q.free(); o.free()
+    for b in (kp, vp, bt, cl):
+        b.free()
+    ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"],
+                              case["ctx_lens"], case["scale"])
+    got = H.bf16_to_f32_np(out)
+    assert np.isfinite(got).all()
+    err = np.abs(got - ref).max()
+    tol = TOL * max(1.0, float(np.abs(ref).max())) if not strict_abs else TOL
+    assert err <= tol, f"max-abs {err} (tol {tol})"
+    return err
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 8, 128), (8, 2, 64), (4, 4, 128), (64, 8, 128), (4, 2, 64), (8, 8, 64)])
+def test_decode_shapes(env, hq, hkv, hd):
+    ctx_lens = [1, 15, 16, 17, 31, 33, 64, 129, 255, 256, 257, 700]
+    run_case(env, H.make_paged_case(1, ctx_lens, hq, hkv, hd, 16))
+
+
+@pytest.mark.parametrize("chunk", [16, 64, 256, 512, 2048])
+def test_decode_chunk_sizes(env, chunk):
+    ctx_lens = [5, 100, 1000, 2049, 3000]
+    run_case(env, H.make_paged_case(2, ctx_lens, 32, 8, 128, 16), chunk_tokens=chunk)
+
+
+def test_decode_page_32(env):
+    run_case(env, H.make_paged_case(3, [1, 31, 32, 33, 500, 1025], 16, 4, 128, 32))
+
+
+def test_decode_single_sequence_and_empty(env):
+    ctx, kernels, _ = env
+    run_case(env, H.make_paged_case(4, [4096], 32, 8, 128, 16))
+    # empty batch is a no-op
+    case = H.make_paged_case(5, [16], 8, 2, 64, 16)
+    kp, vp = ctx.buf(case["kpool"]), ctx.buf(case["vpool"])
+    bt, cl, q = ctx.buf(case["block_tables"]), ctx.buf(case["ctx_lens"]), ctx.buf(case["q"])
+    kernels.paged_attn_decode(ctx, q, kp, vp, bt, cl, 0, 8, 2, 64, 16, 0.125, q, 1)
+    ctx.sync()
+
+
+def test_decode_host_buffers(env):
+    run_case(env, H.make_paged_case(6, [77, 300, 1024], 32, 8, 128, 16), host_io=True)
+
+
+def test_decode_rejects_unsupported(env):
+    ctx, kernels, _ = env
+    from mlx_llm_b200._lib import B2Error
+
+    case = H.make_paged_case(7, [16], 8, 2, 64, 16)
+    kp, vp = ctx.buf(case["kpool"]), ctx.buf(case["vpool"])
+    bt, cl, q = ctx.buf(case["block_tables"]), ctx.buf(case["ctx_lens"]), ctx.buf(case["q"])
+    with pytest.raises(B2Error):
+        kernels.paged_attn_decode(ctx, q, kp, vp, bt, cl, 1, 8, 2, 96, 16, 0.1, q, 1)  # head_dim 96
+    with pytest.raises(B2Error):
+        kernels.paged_attn_decode(ctx, q, kp, vp, bt, cl, 1, 8, 2, 64, 8, 0.1, q, 1)  # page 8
+    with pytest.raises(B2Error):
+        kernels.paged_attn_decode(ctx, q, kp, vp, bt, cl, 1, 32, 2, 64, 16, 0.1, q, 1)  # group 16
+
+
+def test_decode_config1_shape_scaled(env):
+    """BASELINE configuration 1 at reduced batch: 32 q / 8 kv heads, head_dim 128, page 16, contexts
+    uniform in [128, 4096] (seeded), permuted block tables, pool 2x."""
+    rng = np.random.default_rng(0)
+    ctx_lens = rng.integers(128, 4097, size=12)
+    run_case(env, H.make_paged_case(0, ctx_lens, 32, 8, 128, 16), strict_abs=True)
+
+
+def test_decode_linearity_full_size(env):
+    """Full configuration-1 size (64 sequences) through a size-independent property: attention is
+    linear in V, so out(V) + out(V') == out(V + V') within tolerance when V' = 2V."""
+    ctx, kernels, _ = env
+    rng = np.random.default_rng(0)
+    ctx_lens = rng.integers(128, 4097, size=64)
+    case = H.make_paged_case(0, ctx_lens, 32, 8, 128, 16)
+    v2 = H.f32_to_bf16_np(2.0 * H.bf16_to_f32_np(case["vpool"]))
+    kp, bt, cl, q = ctx.buf(case["kpool"]), ctx.buf(case["block_tables"]), ctx.buf(case["ctx_lens"]), ctx.buf(case["q"])
+    outs = []
+    for v in (case["vpool"], v2):
+        vp = ctx.buf(v)
+        o = ctx.empty(case["q"].shape, np.uint16)
+        kernels.paged_attn_decode(ctx, q, kp, vp, bt, cl, 64, 32, 8, 128, 16, case["scale"], o, case["max_blocks"], 0)
+        ctx.sync()
+        outs.append(H.bf16_to_f32_np(o.download()))
+        vp.free(); o.free()
+    assert np.abs(2.0 * outs[0] - outs[1]).max() <= 2 * TOL
+    # spot-check 3 sequences against the oracle
+    for i in (0, 31, 63):
+        sub = dict(case)
+        sub["ctx_lens"] = case["ctx_lens"][i:i + 1]
+        sub["block_tables"] = case["block_tables"][i:i + 1]
+        sub["q"] = case["q"][i:i + 1]
+        from oracle import oracle as orc
+        ref = orc.paged_attention(sub["q"], case["kpool"], case["vpool"], sub["block_tables"], np.array([0, 1], np.int32),
+                                  sub["ctx_lens"], case["scale"])
+        assert np.abs(outs[0][i:i + 1] - ref).max() <= TOL
