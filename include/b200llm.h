@@ -83,6 +83,206 @@ int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host, const uin
                                   const int32_t* ctx_lens_dev, int32_t num_seqs, int32_t hq, int32_t hkv, int32_t head_dim,
                                   int32_t page_size, float scale, int32_t chunk_tokens, uint16_t* out_host);
 
+/* Chunked-prefill paged attention over a ragged batch (replaces the whole-prompt prefill attention,
+ * src/decode/continuous.rs:255 -> src/models/llama.rs:837-852 -> attention.rs:68-102).  Sequence i
+ * owns query rows cu_seqlens[i]..cu_seqlens[i+1]; ctx_lens[i] counts the cached positions including
+ * those rows; query r of n new tokens sees keys 0..=ctx-n+r (bottom-right causal, attention.rs:31-39).
+ * Block-table row of sequence i is i.  Works for any q_len >= 1 (decode rows included). */
+int32_t b2_paged_attn_prefill(b2_ctx* ctx, const uint16_t* q_dev, const uint16_t* k_pool_dev, const uint16_t* v_pool_dev,
+                              const int32_t* block_tables_dev, int32_t max_blocks, const int32_t* cu_seqlens_host,
+                              const int32_t* ctx_lens_host, int32_t num_seqs, int32_t hq, int32_t hkv, int32_t head_dim,
+                              int32_t page_size, float scale, uint16_t* out_dev);
+
+/* ---- MLX-format group-wise affine quantization (src/primitives/quant.rs:20-82,
+ *      src/primitives/projection.rs:15-102) ------------------------------------------------------
+ * Weight W [out, in]; packed [out, in*bits/32] u32 with codes along `in`, lowest bits first
+ * (8 nibbles or 4 bytes per word); scales/biases [out, in/group] bf16; group must be 64, bits 4/8.
+ * w = bf16(code*scale + bias), one rounding. */
+int32_t b2_quantize(b2_ctx* ctx, const uint16_t* w_dev, int64_t out_dim, int64_t in_dim, int32_t group, int32_t bits,
+                    uint32_t* packed_dev, uint16_t* scales_dev, uint16_t* biases_dev);   /* QuantizedLinear::quantize, quant.rs:38-54 */
+int32_t b2_dequantize(b2_ctx* ctx, const uint32_t* packed_dev, const uint16_t* scales_dev, const uint16_t* biases_dev,
+                      int64_t out_dim, int64_t in_dim, int32_t group, int32_t bits, uint16_t* w_dev); /* dequantize_weight, quant.rs:73-82 */
+int32_t b2_unpack_codes(b2_ctx* ctx, const uint32_t* packed_dev, int64_t out_dim, int64_t in_dim, int32_t bits,
+                        uint8_t* codes_dev);
+/* y[m, out] = x[m, in] @ dequant(W)^T (QuantizedLinear::forward, quant.rs:56-70).  Exactly one of
+ * y_bf16_dev / y_f32_dev may be null; the f32 output is the unrounded accumulation. */
+int32_t b2_qmm(b2_ctx* ctx, const uint16_t* x_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
+               const uint16_t* biases_dev, int32_t m, int32_t out_dim, int32_t in_dim, int32_t group, int32_t bits,
+               uint16_t* y_bf16_dev, float* y_f32_dev);
+/* Dense x @ W^T (primitives::nn::linear, src/primitives/nn.rs:26-33). */
+int32_t b2_linear(b2_ctx* ctx, const uint16_t* x_dev, const uint16_t* w_dev, int32_t m, int32_t out_dim, int32_t in_dim,
+                  uint16_t* y_bf16_dev, float* y_f32_dev);
+
+/* ---- fused leaves --------------------------------------------------------------------------- */
+/* rms_norm (src/primitives/nn.rs:35-37): out = bf16(x / rms(x) * w), rows of `dim`. */
+int32_t b2_rms_norm(b2_ctx* ctx, const uint16_t* x_dev, const uint16_t* w_dev, float eps, int32_t rows, int32_t dim,
+                    uint16_t* out_dev);
+/* silu(gate) * up with the reference's bf16 rounding after each op (src/models/llama.rs:1040-1045). */
+int32_t b2_swiglu(b2_ctx* ctx, const uint16_t* gate_dev, const uint16_t* up_dev, int64_t n, uint16_t* out_dev);
+/* bf16 residual add (src/models/llama.rs:730-732). */
+int32_t b2_add(b2_ctx* ctx, const uint16_t* a_dev, const uint16_t* b_dev, int64_t n, uint16_t* out_dev);
+/* embedding row gather (src/primitives/nn.rs:86-93). */
+int32_t b2_embed(b2_ctx* ctx, const uint16_t* table_dev, const int32_t* ids_dev, int32_t n, int32_t dim, int32_t vocab,
+                 uint16_t* out_dev);
+/* greedy argmax per row, ties -> lowest index (src/primitives/sampler.rs:221-241). */
+int32_t b2_argmax(b2_ctx* ctx, const uint16_t* logits_dev, int32_t rows, int32_t vocab, int32_t* out_dev);
+/* RoPE inverse frequencies: kind 0 = Rope::standard (src/primitives/rope.rs:42-52), 1 = Rope::llama3
+ * (rope.rs:125-156); host computation, f32 powf as the reference. */
+int32_t b2_rope_inv_freq(int32_t head_dim, float theta, int32_t kind, float factor, float low_freq_factor,
+                         float high_freq_factor, float original_context, float* out_host);
+/* cos/sin tables for positions 0..n_pos-1 as bf16 [n_pos, head_dim/2] (Rope::cos_sin_at,
+ * rope.rs:183-208: angle = pos*inv_freq in f32, evaluated on the host, cast to bf16). */
+int32_t b2_rope_tables(const float* inv_freq_host, int32_t half, int32_t n_pos, uint16_t* cos_host, uint16_t* sin_host);
+/* Fused [per-head q/k RMSNorm ->] NeoX RoPE -> KV append (LlamaAttention::project,
+ * src/models/llama.rs:806-825 + PagedKvCache::update, src/primitives/paged_kv_cache.rs:379-394).
+ * qkv_dev [T, (hq+2*hkv)*head_dim]: q heads, k heads, v heads per token.  Rotated q goes to
+ * q_out_dev [T, hq, head_dim]; rotated k and raw v are scattered to slot_mapping[t] of the pools
+ * ([pages, hkv, page_size, head_dim]); a negative slot skips the cache write.  q_norm/k_norm may
+ * be null. */
+int32_t b2_rope_kv_append(b2_ctx* ctx, uint16_t* qkv_dev, int32_t T, int32_t hq, int32_t hkv, int32_t head_dim,
+                          const int32_t* positions_dev, const int32_t* slot_mapping_dev, const uint16_t* cos_dev,
+                          const uint16_t* sin_dev, const uint16_t* q_norm_dev, const uint16_t* k_norm_dev, float eps,
+                          int32_t page_size, uint16_t* k_pool_dev, uint16_t* v_pool_dev, uint16_t* q_out_dev);
+
+/* ---- ragged-batch packer / step metadata (no counterpart in the reference, which never packs:
+ *      src/decode/continuous.rs:254-301) ----------------------------------------------------------
+ * Host inputs: per sequence the block-table row, new-token count, cached length, sample flag;
+ * block-table updates (slot, block index, page).  Device outputs are written into one int32 buffer
+ * `out_dev` laid out as consecutive arrays (sizes in elements):
+ *   cu_seqlens[B+1] context_lens[B] positions[T] token_seq[T] slot_mapping[T] logit_rows[B]
+ *   logit_seq[B] dec_ctx[B] dec_qrow[B] dec_slot[B] dec_work_off[B+1] dec_work_seq[W] dec_work_chunk[W]
+ *   pf_seq[P] pf_qstart[P] counts[8]
+ * with W = max_dec_work, P = max_pf_work as given.  counts = {n_logits, n_dec, n_dec_work,
+ * n_pf_work, error, T}.  block_tables_dev [slots, max_blocks] is updated in place. */
+int32_t b2_build_batch_metadata(b2_ctx* ctx, const int32_t* seq_slot_host, const int32_t* q_len_host,
+                                const int32_t* ctx_before_host, const int32_t* want_logits_host, int32_t B,
+                                const int32_t* upd_slot_host, const int32_t* upd_index_host, const int32_t* upd_page_host,
+                                int32_t U, int32_t chunk_tokens, int32_t q_tile, int32_t page_size, int32_t max_blocks,
+                                int32_t max_dec_work, int32_t max_pf_work, int32_t* block_tables_dev, int32_t* out_dev);
+int64_t b2_batch_metadata_elems(int32_t B, int32_t T, int32_t max_dec_work, int32_t max_pf_work);
+
+/* ================================================================================================
+ * Engine API
+ * ============================================================================================== */
+typedef struct b2_weights b2_weights;
+typedef struct b2_model b2_model;
+typedef struct b2_pool b2_pool;
+typedef struct b2_cache b2_cache;
+
+/* QuantSpec (src/primitives/projection.rs:15-32). */
+typedef struct { int32_t group_size, bits; } b2_quant_spec;
+
+/* The Llama / Qwen3 subset of ModelConfig (src/config.rs:315-502). */
+typedef struct {
+    int32_t num_layers, hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size, vocab_size;
+    float rms_norm_eps, rope_theta;
+    int32_t rope_kind;                /* 0 standard, 1 llama3 (build_rope, config.rs:551-581) */
+    float rope_factor, rope_low_freq_factor, rope_high_freq_factor, rope_original_context;
+    int32_t qk_norm;                  /* Qwen3 per-head q/k RMSNorm */
+    int32_t quant_bits, quant_group;  /* `quantization` block of a pre-quantized snapshot, 0 if dense */
+    int32_t tie_word_embeddings;
+} b2_model_config;
+
+enum { B2_DTYPE_F32 = 0, B2_DTYPE_BF16 = 1, B2_DTYPE_F16 = 2, B2_DTYPE_U32 = 3, B2_DTYPE_I32 = 4 };
+
+/* Weights (src/primitives/weights.rs:17-96): a name -> tensor map, from a safetensors file or
+ * directory, or assembled from host buffers (copied). */
+int32_t b2_weights_new(b2_weights** out);
+int32_t b2_weights_from_dir(const char* path, b2_weights** out);            /* Weights::from_dir / from_file */
+int32_t b2_weights_add(b2_weights* w, const char* name, int32_t dtype, const int64_t* shape, int32_t ndim,
+                       const void* data_host);
+int32_t b2_weights_contains(const b2_weights* w, const char* name);        /* Weights::contains */
+int32_t b2_weights_free(b2_weights* w);
+
+/* ModelConfig::from_json (src/config.rs:315-502) for the Llama/Qwen3 subset. */
+int32_t b2_model_config_from_json(const char* json, b2_model_config* out);
+/* CausalLm::from_weights_with (src/models/llama.rs:57-303): every tensor is cast to bf16 (:71);
+ * projections are read as packed triplets when `<key>.scales` exists (:77-95), else dense with
+ * optional quantize-on-load (:97).  `prefix` is prepended to every key ("" for plain checkpoints). */
+int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,
+                              const b2_quant_spec* quant /* nullable */, b2_model** out);
+/* Random-init model generated on the device from a counter-based recipe (benchmark / parity helper;
+ * no counterpart in the reference). cfg->quant_bits selects dense / Q4 / Q8 projections. */
+int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t seed, b2_model** out);
+int32_t b2_model_free(b2_model* m);
+int32_t b2_model_get_config(const b2_model* m, b2_model_config* out);      /* CausalLm::config */
+int32_t b2_model_is_quantized(const b2_model* m);                          /* CausalLm::is_quantized */
+int64_t b2_model_weight_bytes(const b2_model* m);
+
+/* BlockPool (src/primitives/paged_kv_cache.rs:72-160) with bounded physical storage: `max_pages`
+ * pages of `block_size` tokens for every layer, `max_seqs` block-table rows. */
+typedef struct { int64_t live_blocks, shared_blocks, peak_live_blocks, reserved_tokens, free_pages, total_pages; } b2_pool_stats_t;
+int32_t b2_pool_new(b2_ctx* ctx, const b2_model* m, int32_t block_size, int64_t max_pages, int32_t max_seqs,
+                    int32_t max_blocks_per_seq, b2_pool** out);                 /* BlockPool::new */
+int32_t b2_pool_free(b2_pool* p);
+int32_t b2_pool_stats(const b2_pool* p, b2_pool_stats_t* out);              /* live/shared/peak/reserved, :95-114 */
+
+/* PagedKvCache + impl KvCache (src/primitives/paged_kv_cache.rs:168-516, src/primitives/kv_cache.rs:30-64). */
+int32_t b2_cache_new(b2_pool* p, b2_cache** out);                           /* PagedKvCache::with_pool */
+int32_t b2_cache_new_seeded(b2_pool* p, const int64_t* shared_block_ids, int32_t n, b2_cache** out); /* new_seeded :221-235 */
+int32_t b2_cache_free(b2_cache* c);                                         /* Drop :507-516 */
+int32_t b2_cache_offset(const b2_cache* c);                                 /* KvCache::offset */
+int32_t b2_cache_batch_size(const b2_cache* c);
+int32_t b2_cache_num_layers(const b2_cache* c);
+int64_t b2_cache_blocks(const b2_cache* c);                                 /* frozen (full) blocks */
+int64_t b2_cache_reserved_tokens(const b2_cache* c);                        /* :284-286 */
+int32_t b2_cache_block_ids(const b2_cache* c, int64_t* out, int32_t cap);   /* reference-view ids; returns count */
+int32_t b2_cache_truncate(b2_cache* c, int32_t len);                        /* KvCache::truncate :422-485 */
+int32_t b2_cache_reset(b2_cache* c);                                        /* KvCache::reset */
+int32_t b2_cache_retain_sequences(b2_cache* c, const int32_t* keep, int32_t n); /* :408-420 */
+int32_t b2_cache_shareable_prefix_blocks(b2_cache* c, int64_t tokens, int64_t* out, int32_t cap); /* :250-275; returns count */
+/* What KvCache::update returns (kv_cache.rs:31-33), materialised for tests: K and V of `layer`
+ * as [n_kv_heads, len, head_dim] bf16 host arrays. */
+int32_t b2_cache_gather(b2_cache* c, int32_t layer, uint16_t* k_host, uint16_t* v_host);
+
+/* One forward over a ragged batch: sequence i contributes n_tokens[i] ids at positions
+ * offset(caches[i])..; returns last-position logits [num_seqs, vocab] bf16 on the host and advances
+ * the caches.  Covers Decode::step (src/decode/stream.rs:22-29), CausalLm::decode_logits
+ * (llama.rs:351-370) and decode_logits_per_seq (llama.rs:530-558). */
+int32_t b2_model_step(b2_model* m, const int32_t* ids_host, const int32_t* n_tokens, int32_t num_seqs, b2_cache** caches,
+                      uint16_t* logits_host /* nullable */, int32_t* argmax_host /* nullable */);
+
+/* FinishReason (src/decode/stream.rs:31-46). */
+enum { B2_FINISH_STOP_TOKEN = 0, B2_FINISH_MAX_TOKENS = 1, B2_FINISH_CANCELLED = 2, B2_FINISH_STOPPED = 3 };
+/* StreamEvent (stream.rs:48-64): kind 0 Token{id=a, step=b}; kind 1 Done{reason=a, generated=b}. */
+typedef void (*b2_event_cb)(void* user, int32_t request_index, int32_t kind, int32_t a, int32_t b);
+
+/* SamplingParams (src/primitives/sampler.rs:64-90). */
+typedef struct { float temperature, top_p; int32_t top_k; float repetition_penalty; int32_t repetition_context; } b2_sampling;
+/* GenerationConfig (stream.rs:66-89) / BatchRequest (src/decode/batch.rs:47-59). */
+typedef struct {
+    const int32_t* prompt_ids; int32_t n_prompt;
+    b2_sampling sampling;
+    uint64_t seed; int32_t has_seed;
+    int32_t max_new_tokens;
+    const int32_t* stop_tokens; int32_t n_stop;
+    double arrival_s;              /* extension: earliest admission time since the call started */
+} b2_request;
+typedef struct { int32_t* tokens; int32_t capacity; int32_t n_tokens; int32_t finish_reason; } b2_gen_output;
+
+/* ContinuousConfig (src/decode/continuous.rs:67-85) + the bounded-pool / chunking extensions. */
+typedef struct {
+    int32_t max_batch, block_size;
+    int32_t exactness;             /* 0 Exact (per-sequence forwards), 1 Throughput (one ragged batch) */
+    int32_t prefill_chunk_tokens;  /* 0: whole-prompt prefill at admission (the reference's schedule) */
+    int64_t max_pages;             /* 0: sized from the requests */
+    int32_t max_blocks_per_seq;    /* 0: sized from the requests */
+} b2_continuous_config;
+typedef struct {
+    int64_t steps, decode_tokens, prefill_tokens, kernel_launches;
+    double device_ms, wall_ms;
+    int64_t peak_live_blocks, peak_concurrent;
+    int64_t h2d_bytes, d2h_bytes;
+} b2_run_stats;
+
+/* generate (src/decode/stream.rs:113-121 + decode_loop :259-327). cancel may be null. */
+int32_t b2_generate(b2_model* m, const b2_request* req, const volatile int32_t* cancel, b2_event_cb cb, void* user,
+                    b2_gen_output* out);
+/* generate_continuous (src/decode/continuous.rs:117-229). outs has n entries; stats may be null. */
+int32_t b2_generate_continuous(b2_model* m, const b2_request* reqs, int32_t n, const b2_continuous_config* cfg,
+                               const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_gen_output* outs,
+                               b2_run_stats* stats);
+
 #ifdef __cplusplus
 }
 #endif

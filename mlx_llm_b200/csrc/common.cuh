@@ -48,6 +48,16 @@ int32_t b2_ctx_scratch(b2_ctx* ctx, size_t bytes, void** out);
 int32_t b2_ctx_stage(b2_ctx* ctx, size_t bytes, void** out);
 #define B2_LAUNCHED(ctx) ((ctx)->launches++)
 
+// Opt a kernel into a large dynamic shared-memory size, once per (kernel, device).
+#define B2_SMEM_ONCE(ctx, func, bytes)                                                                       \
+    do {                                                                                                     \
+        static bool done__[16] = {};                                                                         \
+        if (!done__[(ctx)->device & 15]) {                                                                   \
+            B2_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (bytes)));       \
+            done__[(ctx)->device & 15] = true;                                                               \
+        }                                                                                                    \
+    } while (0)
+
 // ---- device helpers -------------------------------------------------------------------------
 #ifdef __CUDACC__
 typedef __nv_bfloat16 bf16;

@@ -1,0 +1,317 @@
+// Generation loops: the single-sequence loop and iteration-level continuous batching.
+//
+// b2_generate            <- generate / decode_loop      (src/decode/stream.rs:113-121, :259-327)
+// b2_generate_continuous <- generate_continuous         (src/decode/continuous.rs:117-340)
+// The admission / retirement policy restates core_llm::schedule::Scheduler as its call sites use it
+// (continuous.rs:147-151, :247-252, :306-340): a stop token retires a sequence and is excluded from
+// its output; a filled budget retires it including the token; a zero budget retires at admission.
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <memory>
+#include <thread>
+
+#include "engine.h"
+
+namespace {
+
+struct SchedSeq {
+    std::vector<int32_t> generated;
+    int finish = -1;  // -1 active, else B2_FINISH_STOP_TOKEN / B2_FINISH_MAX_TOKENS
+};
+
+struct Lane {
+    int req = 0;
+    b2_cache* cache = nullptr;
+    int32_t next_token = 0;
+    int prefill_pos = 0;  // prompt tokens already in the cache
+    int64_t page_budget = 0;
+};
+
+bool is_stop(const b2_request& r, int32_t tok) {
+    for (int i = 0; i < r.n_stop; i++)
+        if (r.stop_tokens[i] == tok) return true;
+    return false;
+}
+
+int32_t check_greedy(const b2_request& r) {
+    // sample()'s device fast path (src/primitives/sampler.rs:105-115) is the only sampler on this path
+    B2_REQUIRE(r.sampling.temperature <= 0.f && (r.sampling.repetition_penalty == 1.f || r.sampling.repetition_penalty == 0.f),
+               B2_ERR_UNSUPPORTED, "only greedy sampling (temperature <= 0, repetition_penalty == 1) runs on the device path");
+    return B2_OK;
+}
+
+void fill_output(b2_gen_output* o, const std::vector<int32_t>& gen, int reason) {
+    if (!o) return;
+    o->n_tokens = (int32_t)gen.size();
+    o->finish_reason = reason;
+    if (o->tokens)
+        for (size_t i = 0; i < gen.size() && (int32_t)i < o->capacity; i++) o->tokens[i] = gen[i];
+}
+
+}  // namespace
+
+extern "C" int32_t b2_generate(b2_model* m, const b2_request* req, const volatile int32_t* cancel, b2_event_cb cb, void* user,
+                               b2_gen_output* out) {
+    B2_REQUIRE(m && req, B2_ERR_MSG, "b2_generate: null argument");
+    B2_REQUIRE(req->n_prompt > 0 && req->prompt_ids, B2_ERR_MSG, "generate: empty prompt");
+    B2_CHECK(check_greedy(*req));
+    if (cancel && *cancel) return b2_fail(B2_ERR_CANCELED, "canceled before inference");
+    const int bs = 16;
+    const int max_blocks = (req->n_prompt + std::max(req->max_new_tokens, 0) + bs - 1) / bs + 1;
+    b2_pool* pool = nullptr;
+    B2_CHECK(b2_pool_new(m->ctx, m, bs, max_blocks, 1, max_blocks, &pool));
+    b2_cache* cache = nullptr;
+    int32_t rc = b2_cache_new(pool, &cache);
+    std::vector<int32_t> gen;
+    int finish = B2_FINISH_MAX_TOKENS;
+    int32_t next = 0;
+    if (rc == B2_OK) {
+        std::vector<SeqStep> s{SeqStep{cache, req->prompt_ids, req->n_prompt, true}};
+        rc = b2_engine_forward(m, s, nullptr, &next);
+    }
+    for (int step = 0; rc == B2_OK && step < req->max_new_tokens; step++) {
+        if (cancel && *cancel) {
+            finish = B2_FINISH_CANCELLED;
+            break;
+        }
+        if (is_stop(*req, next)) {
+            finish = B2_FINISH_STOP_TOKEN;
+            break;
+        }
+        if (cb) cb(user, 0, 0, next, step);
+        gen.push_back(next);
+        if (step + 1 == req->max_new_tokens) break;
+        const int32_t feed = next;
+        std::vector<SeqStep> s{SeqStep{cache, &feed, 1, true}};
+        rc = b2_engine_forward(m, s, nullptr, &next);
+    }
+    if (rc == B2_OK) {
+        if (cb) cb(user, 0, 1, finish, (int32_t)gen.size());
+        fill_output(out, gen, finish);
+    }
+    if (cache) b2_cache_free(cache);
+    b2_pool_free(pool);
+    return rc;
+}
+
+extern "C" int32_t b2_generate_continuous(b2_model* m, const b2_request* reqs, int32_t n, const b2_continuous_config* cfg,
+                                          const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_gen_output* outs,
+                                          b2_run_stats* stats) {
+    B2_REQUIRE(m && cfg, B2_ERR_MSG, "b2_generate_continuous: null argument");
+    B2_REQUIRE(n > 0 && reqs, B2_ERR_MSG, "generate_continuous: no requests");
+    B2_REQUIRE(cfg->max_batch > 0, B2_ERR_MSG, "generate_continuous: max_batch must be > 0");
+    B2_REQUIRE(cfg->block_size > 0, B2_ERR_MSG, "generate_continuous: block_size must be > 0");
+    for (int i = 0; i < n; i++) {
+        B2_REQUIRE(reqs[i].n_prompt > 0 && reqs[i].prompt_ids, B2_ERR_MSG,
+                   "generate_continuous: request " + std::to_string(i) + " has an empty prompt");
+        B2_CHECK(check_greedy(reqs[i]));
+    }
+    if (cancel && *cancel) return b2_fail(B2_ERR_CANCELED, "canceled before inference");
+
+    const int bs = cfg->block_size;
+    auto pages_of = [&](const b2_request& r) { return (int64_t)((r.n_prompt + std::max(r.max_new_tokens, 0) + bs - 1) / bs); };
+    int max_blocks = cfg->max_blocks_per_seq;
+    if (max_blocks <= 0) {
+        for (int i = 0; i < n; i++) max_blocks = std::max<int64_t>(max_blocks, pages_of(reqs[i]) + 1);
+    }
+    int64_t max_pages = cfg->max_pages;
+    if (max_pages <= 0) {
+        // room for the max_batch largest requests at full length
+        std::vector<int64_t> need(n);
+        for (int i = 0; i < n; i++) need[i] = pages_of(reqs[i]) + 1;
+        std::sort(need.begin(), need.end(), std::greater<int64_t>());
+        for (int i = 0; i < n && i < cfg->max_batch; i++) max_pages += need[i];
+    }
+    b2_pool* pool = nullptr;
+    B2_CHECK(b2_pool_new(m->ctx, m, bs, max_pages, cfg->max_batch, max_blocks, &pool));  // BlockPool::new (:142)
+
+    std::vector<SchedSeq> sched(n);
+    for (int i = 0; i < n; i++)
+        if (reqs[i].max_new_tokens <= 0) sched[i].finish = B2_FINISH_MAX_TOKENS;  // retired at admission
+    std::vector<Lane> lanes;
+    int next_req = 0;
+    int32_t rc = B2_OK;
+    int64_t committed_pages = 0;
+    b2_run_stats st{};
+    const double dev0 = m->device_ms;
+    const int64_t h2d0 = m->h2d_bytes, d2h0 = m->d2h_bytes, launch0 = m->ctx->launches;
+    const auto t_start = std::chrono::steady_clock::now();
+    auto now_s = [&]() { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t_start).count(); };
+    auto emit = [&](int req, int kind, int a, int b) {
+        if (cb) cb(user, req, kind, a, b);
+    };
+    // record_token (continuous.rs:306-340); returns true when the lane keeps decoding
+    auto record = [&](Lane& lane, int32_t tok) -> bool {
+        SchedSeq& s = sched[lane.req];
+        const b2_request& r = reqs[lane.req];
+        if (is_stop(r, tok)) {
+            s.finish = B2_FINISH_STOP_TOKEN;
+            emit(lane.req, 1, B2_FINISH_STOP_TOKEN, (int)s.generated.size());
+            return false;
+        }
+        s.generated.push_back(tok);
+        st.decode_tokens++;
+        emit(lane.req, 0, tok, (int)s.generated.size() - 1);
+        if ((int)s.generated.size() >= r.max_new_tokens) {
+            s.finish = B2_FINISH_MAX_TOKENS;
+            emit(lane.req, 1, B2_FINISH_MAX_TOKENS, (int)s.generated.size());
+            return false;
+        }
+        lane.next_token = tok;
+        return true;
+    };
+    auto retire = [&](Lane& lane) {
+        committed_pages -= lane.page_budget;
+        b2_cache_free(lane.cache);
+        lane.cache = nullptr;
+    };
+    auto forward = [&](std::vector<SeqStep>& seqs, int32_t* argmax) -> int32_t {
+        st.steps++;
+        for (auto& s : seqs)
+            if (s.n > 1 || s.cache->len == 0) st.prefill_tokens += s.n;
+        return b2_engine_forward(m, seqs, nullptr, argmax);
+    };
+    const bool chunked = cfg->prefill_chunk_tokens > 0;
+    const bool throughput = cfg->exactness != 0;
+
+    // admit request ri: returns 1 if a lane was created, 0 if it retired immediately, -1 if it has to
+    // wait (arrival time or page budget)
+    auto admit = [&](int ri) -> int {
+        const b2_request& r = reqs[ri];
+        if (r.arrival_s > 0 && now_s() < r.arrival_s) return -1;
+        if (sched[ri].finish != -1) {  // zero budget: terminal event, no prefill (continuous.rs:247-252)
+            emit(ri, 1, B2_FINISH_MAX_TOKENS, 0);
+            return 0;
+        }
+        const int64_t need = pages_of(r) + 1;
+        if (committed_pages + need > max_pages) {
+            if (lanes.empty()) {
+                rc = b2_fail(B2_ERR_OOM_PAGES, "generate_continuous: request " + std::to_string(ri) + " does not fit the page pool");
+                return -2;
+            }
+            return -1;
+        }
+        Lane lane;
+        lane.req = ri;
+        lane.page_budget = need;
+        rc = b2_cache_new(pool, &lane.cache);  // PagedKvCache::with_pool (:254)
+        if (rc != B2_OK) return -2;
+        committed_pages += need;
+        if (!chunked) {
+            // whole-prompt batch-1 prefill at admission, first token sampled from it (:255-269)
+            std::vector<SeqStep> s{SeqStep{lane.cache, r.prompt_ids, r.n_prompt, true}};
+            int32_t tok = 0;
+            rc = forward(s, &tok);
+            if (rc != B2_OK) {
+                retire(lane);
+                return -2;
+            }
+            lane.prefill_pos = r.n_prompt;
+            if (!record(lane, tok)) {
+                retire(lane);
+                return 0;
+            }
+        }
+        lanes.push_back(lane);
+        st.peak_concurrent = std::max<int64_t>(st.peak_concurrent, (int64_t)lanes.size());
+        return 1;
+    };
+    auto fill_slots = [&]() {
+        while (rc == B2_OK && (int)lanes.size() < cfg->max_batch && next_req < n) {
+            const int a = admit(next_req);
+            if (a == -1 || a == -2) break;
+            next_req++;
+        }
+    };
+
+    fill_slots();
+    bool cancelled = false;
+    std::vector<SeqStep> batch;
+    std::vector<int> batch_lane;
+    std::vector<int32_t> toks;
+    while (rc == B2_OK && (!lanes.empty() || (chunked && next_req < n))) {
+        if (cancel && *cancel) {
+            cancelled = true;
+            break;
+        }
+        if (chunked) fill_slots();
+        if (rc != B2_OK) break;
+        if (lanes.empty()) {
+            if (next_req >= n) break;
+            // nothing to run until the next arrival
+            const double wait = reqs[next_req].arrival_s - now_s();
+            if (wait > 0) std::this_thread::sleep_for(std::chrono::duration<double>(std::min(wait, 0.002)));
+            continue;
+        }
+        // assemble the step: every decoding lane feeds one token; prefill chunks fill the budget
+        batch.clear();
+        batch_lane.clear();
+        int budget = chunked ? cfg->prefill_chunk_tokens : 0;
+        for (size_t i = 0; i < lanes.size(); i++) {
+            Lane& l = lanes[i];
+            const b2_request& r = reqs[l.req];
+            if (l.prefill_pos >= r.n_prompt) {
+                batch.push_back(SeqStep{l.cache, &l.next_token, 1, true});
+                batch_lane.push_back((int)i);
+            } else if (budget > 0) {
+                const int take = std::min(budget, r.n_prompt - l.prefill_pos);
+                budget -= take;
+                batch.push_back(SeqStep{l.cache, r.prompt_ids + l.prefill_pos, take, l.prefill_pos + take == r.n_prompt});
+                batch_lane.push_back((int)i);
+            }
+        }
+        toks.assign(batch.size(), 0);
+        if (throughput) {
+            rc = forward(batch, toks.data());
+        } else {
+            // Exact: every sequence is its own forward (continuous.rs:277-285)
+            size_t k = 0;
+            for (size_t i = 0; i < batch.size() && rc == B2_OK; i++) {
+                std::vector<SeqStep> one{batch[i]};
+                int32_t tok = 0;
+                rc = forward(one, &tok);
+                if (batch[i].want_logits) toks[k++] = tok;
+            }
+        }
+        if (rc != B2_OK) break;
+        std::vector<char> done(lanes.size(), 0);
+        size_t k = 0;
+        for (size_t i = 0; i < batch.size(); i++) {
+            Lane& l = lanes[batch_lane[i]];
+            if (l.prefill_pos < reqs[l.req].n_prompt) l.prefill_pos += batch[i].n;
+            if (!batch[i].want_logits) continue;
+            if (!record(l, toks[k++])) done[batch_lane[i]] = 1;
+        }
+        std::vector<Lane> survivors;
+        for (size_t i = 0; i < lanes.size(); i++) {
+            if (done[i])
+                retire(lanes[i]);
+            else
+                survivors.push_back(lanes[i]);
+        }
+        lanes.swap(survivors);
+        if (!chunked) fill_slots();  // admit-on-retire (continuous.rs:184-189)
+    }
+    if (rc == B2_OK && cancelled) {
+        // exactly one Done for every request still decoding or still waiting (continuous.rs:198-214)
+        for (auto& l : lanes) emit(l.req, 1, B2_FINISH_CANCELLED, (int)sched[l.req].generated.size());
+        for (int ri = next_req; ri < n; ri++) emit(ri, 1, sched[ri].finish == B2_FINISH_MAX_TOKENS ? B2_FINISH_MAX_TOKENS : B2_FINISH_CANCELLED, 0);
+    }
+    b2_pool_stats_t ps{};
+    b2_pool_stats(pool, &ps);
+    for (auto& l : lanes) retire(l);
+    lanes.clear();
+    st.peak_live_blocks = ps.peak_live_blocks;
+    st.device_ms = m->device_ms - dev0;
+    st.wall_ms = now_s() * 1e3;
+    st.h2d_bytes = m->h2d_bytes - h2d0;
+    st.d2h_bytes = m->d2h_bytes - d2h0;
+    st.kernel_launches = m->ctx->launches - launch0;
+    if (stats) *stats = st;
+    if (rc == B2_OK && outs)
+        for (int i = 0; i < n; i++)
+            fill_output(&outs[i], sched[i].generated, sched[i].finish == -1 ? B2_FINISH_CANCELLED : sched[i].finish);
+    b2_pool_free(pool);
+    return rc;
+}

@@ -1,0 +1,320 @@
+// One decoder forward over a ragged batch (decode tokens and prefill chunks of many sequences).
+//
+// Replaces CausalLm::decode_logits / decode_logits_per_seq (src/models/llama.rs:351-370, :530-558):
+// embed -> per layer [RMSNorm -> fused QKV projection -> (q/k norm) RoPE + KV append -> paged
+// attention -> o_proj + residual -> RMSNorm -> gate|up projection -> SwiGLU -> down_proj + residual]
+// -> last-token gather + final RMSNorm -> lm_head -> greedy argmax.  One host->device copy of the
+// step descriptors before, one device->host copy of the sampled ids (or logits) after.
+#include <algorithm>
+#include <cstring>
+
+#include "engine.h"
+
+int32_t b2_cache_reserve(b2_cache* c, int n);
+void b2_cache_commit(b2_cache* c, int n);
+int32_t b2_model_ensure_rope(b2_model* m, int positions);
+
+namespace {
+
+template <typename T>
+int32_t regrow(T*& p, size_t elems) {
+    if (p) B2_CUDA(cudaFree(p));
+    p = nullptr;
+    B2_CUDA(cudaMalloc((void**)&p, elems * sizeof(T)));
+    return B2_OK;
+}
+
+int32_t ensure_workspace(b2_model* m, int T, int B, int W, int P, size_t stage_ints) {
+    Workspace& w = m->ws;
+    const b2_model_config& c = m->cfg;
+    const bool grow_t = T > w.t_cap, grow_b = B > w.b_cap, grow_w = W > w.w_cap, grow_p = P > w.p_cap;
+    if (grow_t || grow_b || grow_w || grow_p) B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    if (grow_t) {
+        const size_t t = (size_t)std::max(T, 64) * 5 / 4;
+        const size_t qkv_w = (size_t)(c.num_heads + 2 * c.num_kv_heads) * c.head_dim;
+        B2_CHECK(regrow(w.x, t * c.hidden_size));
+        B2_CHECK(regrow(w.xn, t * c.hidden_size));
+        B2_CHECK(regrow(w.qkv, t * qkv_w));
+        B2_CHECK(regrow(w.q, t * c.num_heads * c.head_dim));
+        B2_CHECK(regrow(w.attn, t * c.num_heads * c.head_dim));
+        B2_CHECK(regrow(w.gu, t * 2 * c.intermediate_size));
+        B2_CHECK(regrow(w.act, t * c.intermediate_size));
+        B2_CHECK(regrow(w.ids, t));
+        w.t_cap = (int)t;
+    }
+    if (grow_b) {
+        const size_t b = (size_t)std::max(B, 16) * 5 / 4;
+        B2_CHECK(regrow(w.last, b * c.hidden_size));
+        B2_CHECK(regrow(w.logits, b * c.vocab_size));
+        B2_CHECK(regrow(w.argmax, b));
+        if (w.argmax_host) cudaFreeHost(w.argmax_host);
+        B2_CUDA(cudaHostAlloc((void**)&w.argmax_host, b * 4, cudaHostAllocDefault));
+        w.b_cap = (int)b;
+    }
+    if (grow_w) w.w_cap = std::max(W, 256) * 5 / 4;
+    if (grow_p) w.p_cap = std::max(P, 64) * 5 / 4;
+    if (grow_t || grow_b || grow_w || grow_p) {
+        B2_CHECK(regrow(w.meta, (size_t)b2_batch_metadata_elems(w.b_cap, w.t_cap, w.w_cap, w.p_cap)));
+        const size_t sb = b2_decode_attn_scratch_bytes(w.w_cap, c.num_heads, c.head_dim);
+        if (w.attn_scratch) cudaFree(w.attn_scratch);
+        B2_CUDA(cudaMalloc((void**)&w.attn_scratch, sb));
+        w.attn_scratch_bytes = sb;
+    }
+    if (stage_ints > w.stage_cap) {
+        B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        const size_t n = stage_ints * 5 / 4 + 1024;
+        B2_CHECK(regrow(w.stage_dev, n));
+        if (w.stage_host) cudaFreeHost(w.stage_host);
+        B2_CUDA(cudaHostAlloc((void**)&w.stage_host, n * 4, cudaHostAllocDefault));
+        w.stage_cap = n;
+    }
+    return B2_OK;
+}
+
+int32_t gemm(b2_model* m, const Proj& p, const uint16_t* x, int M, int ldx, uint16_t* out, int ldo, const uint16_t* res) {
+    GemmParams g{};
+    g.x = x;
+    g.w = p.w;
+    g.scales = p.scales;
+    g.biases = p.biases;
+    g.bits = p.bits;
+    g.group = 64;
+    g.M = M;
+    g.N = p.N;
+    g.K = p.K;
+    g.ldx = ldx;
+    g.ldo = ldo;
+    g.ldres = ldo;
+    g.epilogue = res ? EPI_BF16_RESADD : EPI_BF16;
+    g.out = out;
+    g.res = res;
+    return b2_gemm_launch(m->ctx, g);
+}
+
+int pick_chunk_tiles(long dec_ctx_sum, int hkv, int sm_count) {
+    // enough (chunk, kv head) CTAs for ~8 per SM, chunks between 128 and 1024 tokens
+    long target = (long)sm_count * 8;
+    long tok = dec_ctx_sum * hkv / std::max(1l, target);
+    int chunk = 128;
+    while (chunk < 1024 && chunk < tok) chunk *= 2;
+    return chunk / 16;
+}
+
+}  // namespace
+
+int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* logits_out, int32_t* argmax_out) {
+    b2_ctx* ctx = m->ctx;
+    const b2_model_config& c = m->cfg;
+    const int B = (int)seqs.size();
+    if (B == 0) return B2_OK;
+    B2_CUDA(cudaSetDevice(ctx->device));
+    b2_pool* pool = seqs[0].cache->pool;
+    int T = 0, max_pos = 0, n_logits = 0, n_dec = 0;
+    long dec_ctx_sum = 0;
+    for (auto& s : seqs) {
+        B2_REQUIRE(s.cache && s.cache->pool == pool, B2_ERR_MSG, "forward: all caches of a step must share one pool");
+        B2_REQUIRE(s.n > 0, B2_ERR_MSG, "forward: a sequence contributes no token");
+        T += s.n;
+        max_pos = std::max(max_pos, s.cache->len + s.n);
+        n_logits += s.want_logits ? 1 : 0;
+        if (s.n == 1) {
+            n_dec++;
+            dec_ctx_sum += s.cache->len + 1;
+        }
+    }
+    for (int i = 0; i < B; i++)
+        for (int j = i + 1; j < B && B <= 64; j++)
+            B2_REQUIRE(seqs[i].cache != seqs[j].cache, B2_ERR_MSG, "forward: a cache appears twice in one step");
+    B2_CHECK(b2_model_ensure_rope(m, max_pos));
+    // pages for the new tokens (host allocator), then the step descriptors
+    for (auto& s : seqs) B2_CHECK(b2_cache_reserve(s.cache, s.n));
+    const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, c.num_kv_heads, ctx->sm_count);
+    const int q_tile = 64;
+    int W = 0, P = 0;
+    for (auto& s : seqs) {
+        if (s.n == 1) {
+            const int tiles = (s.cache->len + 1 + 15) / 16;
+            W += (tiles + chunk_tiles - 1) / chunk_tiles;
+        } else {
+            P += (s.n + q_tile - 1) / q_tile;
+        }
+    }
+    const int U = (int)pool->upd_slot.size();
+    const size_t stage_ints = 4 * (size_t)B + 3 * (size_t)U + (size_t)T;
+    B2_CHECK(ensure_workspace(m, T, B, W, P, stage_ints));
+    Workspace& w = m->ws;
+    int32_t* sh = w.stage_host;
+    for (int i = 0; i < B; i++) {
+        sh[i] = seqs[i].cache->slot;
+        sh[B + i] = seqs[i].n;
+        sh[2 * B + i] = seqs[i].cache->len;
+        sh[3 * B + i] = seqs[i].want_logits ? 1 : 0;
+    }
+    if (U) {
+        memcpy(sh + 4 * B, pool->upd_slot.data(), (size_t)U * 4);
+        memcpy(sh + 4 * B + U, pool->upd_index.data(), (size_t)U * 4);
+        memcpy(sh + 4 * B + 2 * U, pool->upd_page.data(), (size_t)U * 4);
+    }
+    {
+        int32_t* ids = sh + 4 * B + 3 * U;
+        for (auto& s : seqs) {
+            memcpy(ids, s.ids, (size_t)s.n * 4);
+            ids += s.n;
+        }
+    }
+    cudaStream_t st = ctx->stream;
+    B2_CUDA(cudaEventRecord(m->ev0, st));
+    B2_CUDA(cudaMemcpyAsync(w.stage_dev, sh, stage_ints * 4, cudaMemcpyHostToDevice, st));
+    m->h2d_bytes += (int64_t)stage_ints * 4;
+    pool->upd_slot.clear();
+    pool->upd_index.clear();
+    pool->upd_page.clear();
+
+    BatchMetaIn in{};
+    const int32_t* d = w.stage_dev;
+    in.seq_slot = d;
+    in.q_len = d + B;
+    in.ctx_before = d + 2 * B;
+    in.want_logits = d + 3 * B;
+    in.upd_slot = d + 4 * B;
+    in.upd_index = d + 4 * B + U;
+    in.upd_page = d + 4 * B + 2 * U;
+    const int32_t* ids_dev = d + 4 * B + 3 * U;
+    in.B = B;
+    in.T = T;
+    in.U = U;
+    in.chunk_tiles = chunk_tiles;
+    in.q_tile = q_tile;
+    in.page_size = pool->block_size;
+    in.max_blocks = pool->max_blocks;
+    BatchMetaOut mo{};
+    mo.block_tables = pool->block_tables;
+    b2_batch_meta_carve(w.meta, B, T, W, P, mo);
+    B2_CHECK(b2_batch_meta_launch(ctx, in, mo));
+
+    const int H = c.hidden_size, hq = c.num_heads, hkv = c.num_kv_heads, hd = c.head_dim, I = c.intermediate_size;
+    const int qkv_w = (hq + 2 * hkv) * hd;
+    const float scale_log2 = powf((float)hd, -0.5f) * 1.4426950408889634f;  // attn_scale, config.rs:597-598
+    B2_CHECK(b2_embed_launch(ctx, m->embed, ids_dev, T, H, c.vocab_size, w.x));
+    for (int l = 0; l < c.num_layers; l++) {
+        const LayerW& L = m->layers[l];
+        B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.input_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
+        B2_CHECK(gemm(m, L.qkv, w.xn, T, H, w.qkv, qkv_w, nullptr));
+        RopeKvParams rp{};
+        rp.qkv = w.qkv;
+        rp.ld = qkv_w;
+        rp.positions = mo.positions;
+        rp.slot_mapping = mo.slot_mapping;
+        rp.cos_table = m->cos_tab;
+        rp.sin_table = m->sin_tab;
+        rp.q_norm = L.q_norm;
+        rp.k_norm = L.k_norm;
+        rp.eps = c.rms_norm_eps;
+        rp.T = T;
+        rp.hq = hq;
+        rp.hkv = hkv;
+        rp.hd = hd;
+        rp.page_size = pool->block_size;
+        rp.k_pool = pool->k_layer(l);
+        rp.v_pool = pool->v_layer(l);
+        rp.q_out = w.q;
+        B2_CHECK(b2_rope_kv_launch(ctx, rp));
+        if (n_dec > 0) {
+            DecodeAttnParams dp{};
+            dp.q = w.q;
+            dp.k_pool = pool->k_layer(l);
+            dp.v_pool = pool->v_layer(l);
+            dp.block_tables = pool->block_tables;
+            dp.max_blocks = pool->max_blocks;
+            dp.bt_rows = mo.dec_slot;
+            dp.q_rows = mo.dec_qrow;
+            dp.ctx_lens = mo.dec_ctx;
+            dp.work_seq = mo.dec_work_seq;
+            dp.work_chunk = mo.dec_work_chunk;
+            dp.seq_work_off = mo.dec_work_off;
+            dp.n_work = mo.counts + 2;
+            dp.chunk_tiles = chunk_tiles;
+            dp.hq = hq;
+            dp.hkv = hkv;
+            dp.page_tiles = pool->block_size / 16;
+            dp.scale_log2 = scale_log2;
+            dp.part_o = w.attn_scratch;
+            dp.part_ml = w.attn_scratch + (size_t)w.w_cap * hq * hd;
+            dp.out = w.attn;
+            B2_CHECK(b2_decode_attn_launch(ctx, dp, hd, W, n_dec));
+        }
+        if (P > 0) {
+            PrefillAttnParams pp{};
+            pp.q = w.q;
+            pp.k_pool = pool->k_layer(l);
+            pp.v_pool = pool->v_layer(l);
+            pp.block_tables = pool->block_tables;
+            pp.max_blocks = pool->max_blocks;
+            pp.seq_slot = in.seq_slot;
+            pp.cu_seqlens = mo.cu_seqlens;
+            pp.context_lens = mo.context_lens;
+            pp.pf_seq = mo.pf_seq;
+            pp.pf_qstart = mo.pf_qstart;
+            pp.n_work = mo.counts + 3;
+            pp.hq = hq;
+            pp.hkv = hkv;
+            pp.page_tiles = pool->block_size / 16;
+            pp.scale_log2 = scale_log2;
+            pp.out = w.attn;
+            B2_CHECK(b2_prefill_attn_launch(ctx, pp, hd, P));
+        }
+        B2_CHECK(gemm(m, L.o, w.attn, T, hq * hd, w.x, H, w.x));     // h = x + o_proj(attn)
+        B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.post_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
+        B2_CHECK(gemm(m, L.gu, w.xn, T, H, w.gu, 2 * I, nullptr));
+        B2_CHECK(b2_swiglu_launch(ctx, w.gu, T, I, w.act));
+        B2_CHECK(gemm(m, L.down, w.act, T, I, w.x, H, w.x));        // x = h + down(...)
+    }
+    if (n_logits > 0) {
+        B2_CHECK(b2_rms_norm_launch(ctx, w.x, m->norm, c.rms_norm_eps, n_logits, H, H, mo.logit_rows, w.last));
+        Proj head;
+        head.bits = 0;
+        head.N = c.vocab_size;
+        head.K = H;
+        head.w = m->lm_head;
+        B2_CHECK(gemm(m, head, w.last, n_logits, H, w.logits, c.vocab_size, nullptr));
+        B2_CHECK(b2_argmax_launch(ctx, w.logits, n_logits, c.vocab_size, w.argmax));
+        B2_CUDA(cudaMemcpyAsync(w.argmax_host, w.argmax, (size_t)n_logits * 4, cudaMemcpyDeviceToHost, st));
+        m->d2h_bytes += (int64_t)n_logits * 4;
+        if (logits_out) {
+            const size_t bytes = (size_t)n_logits * c.vocab_size * 2;
+            if (bytes > w.logits_host_cap) {
+                B2_CUDA(cudaStreamSynchronize(st));
+                if (w.logits_host) cudaFreeHost(w.logits_host);
+                B2_CUDA(cudaHostAlloc((void**)&w.logits_host, bytes, cudaHostAllocDefault));
+                w.logits_host_cap = bytes;
+            }
+            B2_CUDA(cudaMemcpyAsync(w.logits_host, w.logits, bytes, cudaMemcpyDeviceToHost, st));
+            m->d2h_bytes += (int64_t)bytes;
+        }
+    }
+    B2_CUDA(cudaEventRecord(m->ev1, st));
+    B2_CUDA(cudaStreamSynchronize(st));
+    B2_CUDA(cudaGetLastError());
+    float ms = 0.f;
+    B2_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    m->device_ms += ms;
+    if (n_logits > 0) {
+        if (argmax_out) memcpy(argmax_out, w.argmax_host, (size_t)n_logits * 4);
+        if (logits_out) memcpy(logits_out, w.logits_host, (size_t)n_logits * c.vocab_size * 2);
+    }
+    for (auto& s : seqs) b2_cache_commit(s.cache, s.n);
+    return B2_OK;
+}
+
+extern "C" int32_t b2_model_step(b2_model* m, const int32_t* ids_host, const int32_t* n_tokens, int32_t num_seqs, b2_cache** caches,
+                                 uint16_t* logits_host, int32_t* argmax_host) {
+    B2_REQUIRE(m && ids_host && n_tokens && caches, B2_ERR_MSG, "b2_model_step: null argument");
+    std::vector<SeqStep> seqs;
+    const int32_t* cur = ids_host;
+    for (int i = 0; i < num_seqs; i++) {
+        B2_REQUIRE(caches[i], B2_ERR_MSG, "b2_model_step: null cache");
+        seqs.push_back(SeqStep{caches[i], cur, n_tokens[i], true});
+        cur += n_tokens[i];
+    }
+    return b2_engine_forward(m, seqs, logits_host, argmax_host);
+}

@@ -280,11 +280,7 @@ __global__ void decode_worklist_kernel(const int32_t* ctx_lens, int num_seqs, in
 template <int HD>
 int32_t launch_decode(b2_ctx* ctx, const DecodeAttnParams& p, int grid_work, int num_seqs) {
     const int smem = kWarps * kStages * 2 * 16 * HD * 2;
-    static bool configured = false;
-    if (!configured) {
-        B2_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured = true;
-    }
+    B2_SMEM_ONCE(ctx, paged_attn_decode_kernel<HD>, smem);
     dim3 grid(grid_work, p.hkv);
     paged_attn_decode_kernel<HD><<<grid, kWarps * 32, smem, ctx->stream>>>(p);
     B2_LAUNCHED(ctx);

@@ -127,3 +127,51 @@ def make_paged_case(seed, ctx_lens, hq, hkv, hd, page, q_lens=None, pool_factor=
     cu[1:] = np.cumsum(q_lens)
     return dict(q=q, kpool=kpool, vpool=vpool, block_tables=bt, ctx_lens=ctx_lens, cu_seqlens=cu, max_blocks=max_blocks,
                 pool_pages=pool_pages, hq=hq, hkv=hkv, hd=hd, page=page, scale=float(hd) ** -0.5)
+
+
+def hf_weight_names(layer):
+    p = f"model.layers.{layer}."
+    return dict(q=p + "self_attn.q_proj.weight", k=p + "self_attn.k_proj.weight", v=p + "self_attn.v_proj.weight",
+                o=p + "self_attn.o_proj.weight", gate=p + "mlp.gate_proj.weight", up=p + "mlp.up_proj.weight",
+                down=p + "mlp.down_proj.weight", input_ln=p + "input_layernorm.weight",
+                post_ln=p + "post_attention_layernorm.weight", q_norm=p + "self_attn.q_norm.weight",
+                k_norm=p + "self_attn.k_norm.weight")
+
+
+def engine_config(eng, cfg=CONFIG0, quant_bits=0):
+    return eng.model_config(num_layers=cfg["layers"], hidden_size=cfg["hidden"], num_heads=cfg["heads"], num_kv_heads=cfg["kv_heads"],
+                            head_dim=cfg["head_dim"], intermediate_size=cfg["inter"], vocab_size=cfg["vocab"], rms_norm_eps=cfg["eps"],
+                            rope_theta=cfg["theta"], rope_kind=cfg["rope_kind"], rope_factor=cfg["rope_factor"],
+                            rope_low_freq_factor=cfg["rope_low"], rope_high_freq_factor=cfg["rope_high"],
+                            rope_original_context=cfg["rope_orig"], qk_norm=cfg.get("qk_norm", 0), quant_bits=quant_bits,
+                            quant_group=64 if quant_bits else 0)
+
+
+def build_engine_model(eng, ctx, cfg=CONFIG0, weights=None, quant=None):
+    """The same tiny weights as build_oracle_model, handed to the engine as f32 host tensors under
+    the Hugging Face key names CausalLm::from_weights reads (src/models/llama.rs:122-181, :245-281)."""
+    weights = weights or tiny_weights(cfg)
+    w = eng.Weights()
+    w.add("model.embed_tokens.weight", weights["embed"])
+    w.add("lm_head.weight", weights["lm_head"])
+    w.add("model.norm.weight", np.ones(cfg["hidden"], np.float32))
+    for l, lw in enumerate(weights["layers"]):
+        names = hf_weight_names(l)
+        for k, v in lw.items():
+            w.add(names[k], v)
+        w.add(names["input_ln"], np.ones(cfg["hidden"], np.float32))
+        w.add(names["post_ln"], np.ones(cfg["hidden"], np.float32))
+        if cfg.get("qk_norm"):
+            w.add(names["q_norm"], np.ones(cfg["head_dim"], np.float32))
+            w.add(names["k_norm"], np.ones(cfg["head_dim"], np.float32))
+    m = eng.CausalLm.from_weights(ctx, w, "", engine_config(eng, cfg), quant)
+    w.free()
+    return m
+
+
+def bf16_ulp_diff(a, b):
+    """Distance in bf16 ulps between two uint16 bf16 arrays (same-sign finite values)."""
+    def key(h):
+        h = h.astype(np.int32)
+        return np.where(h & 0x8000, 0x8000 - (h & 0x7FFF), 0x8000 + (h & 0x7FFF))
+    return np.abs(key(np.asarray(a)) - key(np.asarray(b)))

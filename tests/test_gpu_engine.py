@@ -1,0 +1,332 @@
+"""End-to-end parity of the engine (through the C ABI) against the CPU oracle on BASELINE
+configuration 0: tiny random-init Llama decoder (seed 0), 4 concurrent sequences with prompt lengths
+17/33/64/129, page size 16, greedy continuous-batch decode of 32 tokens each.
+
+The scenarios mirror the reference's own tests: tests/continuous.rs (Exact == batch-1, admit-on-retire
+with 5 requests / max_batch 2, cancel semantics, zero budget), tests/streaming.rs (max tokens,
+determinism, stop token excluded, empty prompt error), tests/paged.rs and the unit tests of
+src/primitives/paged_kv_cache.rs (block accounting, seeded prefixes, truncate, reset)."""
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    from mlx_llm_b200 import _lib, engine
+    from oracle import oracle as orc
+
+    ctx = _lib.Context(0)
+    weights = H.tiny_weights()
+    model = H.build_engine_model(engine, ctx, weights=weights)
+    omodel = H.build_oracle_model(orc, weights=weights)
+    yield ctx, engine, orc, model, omodel
+    model.free()
+    ctx.close()
+
+
+def logits_close(got_bf16, ref_f32):
+    """max-abs 2e-3 on the accumulation plus the rounding of the bf16 output itself."""
+    got = H.bf16_to_f32_np(got_bf16)
+    tol = 2e-3 + np.abs(ref_f32) * 2.0 ** -8
+    return (np.abs(got - ref_f32) <= tol).all(), float(np.abs(got - ref_f32).max())
+
+
+def test_prefill_logits_match_oracle(env):
+    ctx, eng, orc, model, omodel = env
+    prompts = H.config0_prompts()
+    pool = eng.BlockPool(ctx, model, 16, 64, 4, 16)
+    caches = [eng.PagedKvCache(pool) for _ in prompts]
+    logits, am = model.step(list(zip(prompts, caches)))
+    ocs = [orc.Cache(2, block_size=16) for _ in prompts]
+    ref, ref_f32 = omodel.forward([(p, c, 0) for p, c in zip(prompts, ocs)])
+    ok, err = logits_close(logits, ref_f32)
+    assert ok, f"prefill logits max-abs {err}"
+    assert [c.offset() for c in caches] == [17, 33, 64, 129]
+    assert [c.blocks() for c in caches] == [1, 2, 4, 8]
+    assert [c.reserved_tokens() for c in caches] == [32, 48, 64, 144]
+    # KV written to the pages equals what the reference's cache would hold
+    for c, oc in zip(caches, ocs):
+        for layer in range(2):
+            k, v = c.gather(layer, 2, 64)
+            ok_, ov_ = oc.gather(layer)
+            ok_ = ok_.reshape(-1, 2, 64).transpose(1, 0, 2)
+            ov_ = ov_.reshape(-1, 2, 64).transpose(1, 0, 2)
+            assert H.bf16_ulp_diff(k, ok_).max() <= 2 and (H.bf16_ulp_diff(k, ok_) > 0).mean() < 0.02
+            assert H.bf16_ulp_diff(v, ov_).max() <= 2 and (H.bf16_ulp_diff(v, ov_) > 0).mean() < 0.02
+    # one decode step over all four (decode_logits_per_seq)
+    feed = [[int(a)] for a in am]
+    logits2, am2 = model.step(list(zip(feed, caches)))
+    ref2, ref2_f32 = omodel.forward([(f, c, c.offset()) for f, c in zip(feed, ocs)])
+    ok, err = logits_close(logits2, ref2_f32)
+    assert ok, f"decode logits max-abs {err}"
+    for c in caches:
+        c.free()
+    pool.free()
+
+
+def top2_margins(omodel, orc, prompts, tokens):
+    """Smallest top-2 logit margin the oracle sees along the given token streams (diagnostic)."""
+    worst = 1e9
+    for p, toks in zip(prompts, tokens):
+        c = orc.Cache(2, block_size=16)
+        lg, _ = omodel.forward([(p, c, 0)])
+        for t in toks:
+            s = np.sort(lg[0])
+            worst = min(worst, float(s[-1] - s[-2]))
+            lg, _ = omodel.forward([([t], c, c.offset())])
+    return worst
+
+
+@pytest.mark.parametrize("mode", ["exact", "throughput", "chunked"])
+def test_config0_greedy_identity_and_block_tables(env, mode):
+    ctx, eng, orc, model, omodel = env
+    prompts = H.config0_prompts()
+    ref = omodel.generate_continuous(prompts, [32] * 4, max_batch=8, block_size=16)
+    reqs = [eng.BatchRequest(p.tolist(), 32) for p in prompts]
+    cfg = eng.ContinuousConfig(max_batch=8, block_size=16, exactness=eng.EXACT if mode == "exact" else eng.THROUGHPUT,
+                               prefill_chunk_tokens=48 if mode == "chunked" else 0)
+    events = []
+    outs, stats = eng.generate_continuous(model, reqs, cfg, on_event=lambda i, e: events.append((i,) + e), return_stats=True)
+    got = [o.tokens for o in outs]
+    if got != ref["tokens"]:
+        margin = top2_margins(omodel, orc, prompts, ref["tokens"])
+        pytest.fail(f"greedy streams differ (oracle min top-2 margin {margin:.3e}): {got} vs {ref['tokens']}")
+    assert [o.finish_reason for o in outs] == [eng.MAX_TOKENS] * 4
+    assert all(len(t) == 32 for t in got)
+    assert stats["peak_live_blocks"] == 22  # fill-order ids 0..21 of the reference's allocator
+    if mode != "chunked":
+        # same event order as the reference loop: (request, kind, a, b)
+        exp = [(r, "token" if k == 0 else "done", a, b) for r, k, a, b in ref["events"]]
+        assert events == exp
+    else:
+        # chunking interleaves requests differently but every request sees Token* then one Done
+        for r in range(4):
+            mine = [e for e in events if e[0] == r]
+            assert [e[1] for e in mine] == ["token"] * 32 + ["done"]
+            assert [e[3] for e in mine[:-1]] == list(range(32))
+
+
+def test_block_ids_match_reference_rules(env):
+    """Block ids are handed out when a block fills, in lane order: prompts 17/33/64/129 then 31 decode
+    steps give seq0 [0,15,19], seq1 [1,2,16,20], seq2 [3,4,5,6,18], seq3 [7..14,17,21]."""
+    ctx, eng, orc, model, omodel = env
+    prompts = H.config0_prompts()
+    pool = eng.BlockPool(ctx, model, 16, 64, 4, 16)
+    caches = [eng.PagedKvCache(pool) for _ in prompts]
+    feed = []
+    for p, c in zip(prompts, caches):  # admission order: one prefill each
+        _, am = model.step([(p, c)], want_logits=False)
+        feed.append([int(am[0])])
+    for _ in range(31):
+        _, am = model.step(list(zip(feed, caches)), want_logits=False)
+        feed = [[int(a)] for a in am]
+    assert [c.block_ids() for c in caches] == [[0, 15, 19], [1, 2, 16, 20], [3, 4, 5, 6, 18], [7, 8, 9, 10, 11, 12, 13, 14, 17, 21]]
+    assert [c.offset() for c in caches] == [48, 64, 95, 160]
+    st = pool.stats()
+    assert st["live_blocks"] == 22 and st["peak_live_blocks"] == 22 and st["reserved_tokens"] == 22 * 16
+    ref = omodel.generate_continuous(prompts, [32] * 4)
+    assert [c.block_ids() for c in caches] == ref["block_ids"]
+    for c in caches:
+        c.free()
+    assert pool.stats()["live_blocks"] == 0
+    pool.free()
+
+
+def test_admit_on_retire_matches_batch1(env):
+    """5 requests through 2 slots with budgets 4,8,6,10,12 (tests/continuous.rs:123-149): every row
+    equals its batch-1 generate() run, and the event stream equals the reference loop's."""
+    ctx, eng, orc, model, omodel = env
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 1024, size=n).astype(np.int32) for n in (9, 21, 16, 40, 5)]
+    budgets = [4, 8, 6, 10, 12]
+    reqs = [eng.BatchRequest(p.tolist(), b) for p, b in zip(prompts, budgets)]
+    events = []
+    outs = eng.generate_continuous(model, reqs, eng.ContinuousConfig(max_batch=2, block_size=16, exactness=eng.EXACT),
+                                   on_event=lambda i, e: events.append((i,) + e))
+    for p, b, o in zip(prompts, budgets, outs):
+        single = eng.generate(model, p.tolist(), b)
+        assert o.tokens == single.tokens and len(o.tokens) == b and o.finish_reason == eng.MAX_TOKENS
+    ref = omodel.generate_continuous(prompts, budgets, max_batch=2)
+    assert [o.tokens for o in outs] == ref["tokens"]
+    assert events == [(r, "token" if k == 0 else "done", a, b) for r, k, a, b in ref["events"]]
+    # determinism (tests/streaming.rs:118-130)
+    outs2 = eng.generate_continuous(model, reqs, eng.ContinuousConfig(max_batch=2, block_size=16, exactness=eng.THROUGHPUT))
+    assert [o.tokens for o in outs2] == [o.tokens for o in outs]
+
+
+def test_stop_token_excluded_and_zero_budget(env):
+    ctx, eng, orc, model, omodel = env
+    prompts = H.config0_prompts()[:2]
+    base = eng.generate(model, prompts[0].tolist(), 12)
+    stop = base.tokens[5]
+    first = base.tokens.index(stop)
+    out = eng.generate(model, prompts[0].tolist(), 12, stop_tokens=[stop])
+    assert out.tokens == base.tokens[:first] and out.finish_reason == eng.STOP_TOKEN
+    oref = omodel.generate(prompts[0], 12, stop=[stop])
+    assert out.tokens == oref["tokens"] and oref["reason"] == 0
+    events = []
+    reqs = [eng.BatchRequest(prompts[0].tolist(), 0), eng.BatchRequest(prompts[1].tolist(), 3, stop_tokens=[stop])]
+    outs = eng.generate_continuous(model, reqs, eng.ContinuousConfig(), on_event=lambda i, e: events.append((i,) + e))
+    assert outs[0].tokens == [] and outs[0].finish_reason == eng.MAX_TOKENS  # zero budget: Done{MaxTokens, 0}, no prefill
+    assert events[0] == (0, "done", eng.MAX_TOKENS, 0)
+    ref = omodel.generate_continuous(prompts, [0, 3], stops=[[], [stop]])
+    assert [o.tokens for o in outs] == ref["tokens"] and [o.finish_reason for o in outs] == ref["reasons"]
+
+
+def test_errors_and_cancel(env):
+    ctx, eng, orc, model, omodel = env
+    from mlx_llm_b200._lib import B2Error
+
+    prompts = H.config0_prompts()
+    with pytest.raises(B2Error) as e:
+        eng.generate_continuous(model, [], eng.ContinuousConfig())
+    assert e.value.code == -7
+    with pytest.raises(B2Error):
+        eng.generate_continuous(model, [eng.BatchRequest([], 4)], eng.ContinuousConfig())
+    with pytest.raises(B2Error):
+        eng.generate_continuous(model, [eng.BatchRequest([1, 2], 4)], eng.ContinuousConfig(max_batch=0))
+    with pytest.raises(B2Error):
+        eng.generate_continuous(model, [eng.BatchRequest([1, 2], 4)], eng.ContinuousConfig(block_size=0))
+    with pytest.raises(B2Error):
+        eng.generate(model, [], 4)
+    with pytest.raises(B2Error) as e:  # non-greedy sampling is not on the device path
+        eng.generate_continuous(model, [eng.BatchRequest([1, 2], 4, sampling=eng.SamplingParams(temperature=0.8))], eng.ContinuousConfig())
+    assert e.value.code == -5
+    # pre-set cancel is a typed error (continuous.rs:138-140)
+    flag = eng.CancelFlag()
+    flag.cancel()
+    with pytest.raises(B2Error) as e:
+        eng.generate_continuous(model, [eng.BatchRequest(prompts[0].tolist(), 4)], eng.ContinuousConfig(), cancel=flag)
+    assert e.value.code == -6
+    # mid-stream cancel: 6 requests, 2 slots; every request gets exactly one Done (continuous.rs:198-214)
+    flag = eng.CancelFlag()
+    events = []
+
+    def on_event(i, e):
+        events.append((i,) + e)
+        if sum(1 for x in events if x[1] == "token") >= 7:
+            flag.cancel()
+
+    reqs = [eng.BatchRequest(prompts[i % 4].tolist(), 0 if i == 5 else 20) for i in range(6)]
+    outs = eng.generate_continuous(model, reqs, eng.ContinuousConfig(max_batch=2), cancel=flag, on_event=on_event)
+    dones = [e for e in events if e[1] == "done"]
+    assert sorted(d[0] for d in dones) == list(range(6))
+    assert [o.finish_reason for o in outs[:5]] == [eng.CANCELLED] * 5
+    assert outs[5].finish_reason == eng.MAX_TOKENS and outs[5].tokens == []  # zero-budget request keeps MaxTokens
+    assert sum(len(o.tokens) for o in outs) <= 9  # stops within one step of the flag
+    # single-sequence loop: mid-stream cancel keeps the partial output (stream.rs:9-12)
+    flag = eng.CancelFlag()
+    seen = []
+
+    def on_ev(e):
+        seen.append(e)
+        if len(seen) == 3:
+            flag.cancel()
+
+    out = eng.generate(model, prompts[1].tolist(), 20, cancel=flag, on_event=on_ev)
+    assert out.finish_reason == eng.CANCELLED and len(out.tokens) == 3 and seen[-1] == ("done", eng.CANCELLED, 3)
+
+
+def test_seeded_prefix_truncate_reset(env):
+    """Copy-on-write prefix sharing, truncate and reset on real pages (paged_kv_cache.rs:642-787,
+    scaled to 16-token blocks)."""
+    ctx, eng, orc, model, omodel = env
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, 1024, size=40).astype(np.int32)
+    pool = eng.BlockPool(ctx, model, 16, 32, 4, 8)
+    a = eng.PagedKvCache(pool)
+    la, _ = model.step([(ids, a)])
+    assert (a.offset(), a.blocks(), a.reserved_tokens()) == (40, 2, 48)
+    assert pool.live_blocks() == 2 and pool.shared_blocks() == 0
+    shared = a.shareable_prefix_blocks(40)
+    assert shared == a.block_ids()[:2] and a.shareable_prefix_blocks(15) == []
+    b = eng.PagedKvCache.new_seeded(pool, shared)
+    assert b.offset() == 32 and pool.live_blocks() == 2 and pool.shared_blocks() == 2
+    lb, _ = model.step([(ids[32:], b)])  # recompute only the suffix
+    assert np.array_equal(lb, la), "seeded prefix + suffix must reproduce the cold run"
+    assert pool.shared_blocks() == 2, "divergence touches only the private tail"
+    for layer in range(2):
+        ka, va = a.gather(layer, 2, 64)
+        kb, vb = b.gather(layer, 2, 64)
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+    # truncate B into the shared second block: B must get a private copy, A stays intact
+    ka_before = a.gather(0, 2, 64)[0].copy()
+    b.truncate(20)
+    assert (b.offset(), b.blocks()) == (20, 1) and pool.shared_blocks() == 1
+    lb2, _ = model.step([(ids[20:], b)])
+    assert np.array_equal(lb2, la)
+    assert np.array_equal(a.gather(0, 2, 64)[0], ka_before)
+    b.free()
+    assert pool.shared_blocks() == 0 and pool.live_blocks() == 2
+    # truncate within the tail / onto a boundary / no-op / negative (paged_kv_cache.rs:743-768)
+    a.truncate(36)
+    assert (a.offset(), a.blocks()) == (36, 2)
+    a.truncate(20)
+    assert (a.offset(), a.blocks()) == (20, 1) and pool.live_blocks() == 1
+    a.truncate(16)
+    assert (a.offset(), a.blocks(), a.reserved_tokens()) == (16, 1, 16)
+    a.truncate(100)
+    assert a.offset() == 16
+    from mlx_llm_b200._lib import B2Error
+    with pytest.raises(B2Error):
+        a.truncate(-1)
+    la2, _ = model.step([(ids[16:], a)])  # rollback then replay gives the same logits
+    assert np.array_equal(la2, la)
+    with pytest.raises(B2Error):
+        a.retain_sequences([1])
+    a.retain_sequences([0])
+    assert a.offset() == 40
+    a.reset()
+    assert a.offset() == 0 and a.batch_size() == 0 and pool.live_blocks() == 0
+    a.retain_sequences([])
+    a.free()
+    st = pool.stats()
+    assert st["free_pages"] == st["total_pages"]
+    pool.free()
+
+
+def test_pool_exhaustion_is_an_error_not_a_fault(env):
+    ctx, eng, orc, model, omodel = env
+    from mlx_llm_b200._lib import B2Error
+
+    pool = eng.BlockPool(ctx, model, 16, 2, 1, 8)
+    c = eng.PagedKvCache(pool)
+    with pytest.raises(B2Error) as e:
+        model.step([(np.arange(40, dtype=np.int32), c)])
+    assert e.value.code == -8
+    with pytest.raises(B2Error):
+        eng.PagedKvCache(pool)  # no free block-table row
+    c.free()
+    pool.free()
+
+
+def test_quantize_on_load_q4_q8(env):
+    """Quantize-on-load (CausalLm::from_weights_with with a QuantSpec): generation through the Q4/Q8
+    projections equals the oracle run on the same quantized weights.  intermediate_size 688 is not a
+    multiple of the group size, so this uses a 640-wide variant of the tiny model."""
+    ctx, eng, orc, model, omodel = env
+    cfg = dict(H.CONFIG0, inter=640)
+    weights = H.tiny_weights(cfg, seed=7)
+    prompts = H.config0_prompts(seed=9)[:3]
+    for bits in (4, 8):
+        qm = H.build_engine_model(eng, ctx, cfg, weights, quant=eng.QuantSpec(64, bits))
+        assert qm.is_quantized()
+        om = H.build_oracle_model(orc, cfg, weights, quant_bits=bits)
+        pool = eng.BlockPool(ctx, qm, 16, 64, 4, 16)
+        caches = [eng.PagedKvCache(pool) for _ in prompts]
+        logits, _ = qm.step(list(zip(prompts, caches)))
+        ocs = [orc.Cache(2, block_size=16) for _ in prompts]
+        _, ref_f32 = om.forward([(p, c, 0) for p, c in zip(prompts, ocs)])
+        ok, err = logits_close(logits, ref_f32)
+        assert ok, f"Q{bits} logits max-abs {err}"
+        for c in caches:
+            c.free()
+        pool.free()
+        qm.free()
+    from mlx_llm_b200._lib import B2Error
+    with pytest.raises(B2Error):  # group size must divide the input dimension (688 % 64 != 0)
+        H.build_engine_model(eng, ctx, H.CONFIG0, H.tiny_weights(), quant=eng.QuantSpec(64, 4))
