@@ -130,6 +130,9 @@ int32_t b2_pool_new(b2_ctx* ctx, const b2_model* m, int32_t block_size, int64_t 
         return b2_fail(B2_ERR_CUDA, std::string("b2_pool_new: cudaMalloc of the block tables failed: ") + cudaGetErrorString(e));
     }
     cudaMemsetAsync(p->block_tables, 0, (size_t)max_seqs * max_blocks_per_seq * 4, ctx->stream);
+    // Masked positions of a partly filled page still enter the P.V product with weight zero, and
+    // 0 * NaN is NaN: the pool must never hold non-finite garbage.
+    cudaMemsetAsync(p->kv, 0, bytes, ctx->stream);
     p->free_pages.resize((size_t)max_pages);
     for (int64_t i = 0; i < max_pages; i++) p->free_pages[i] = (int32_t)(max_pages - 1 - i);  // page 0 goes out first
     p->page_ref.assign((size_t)max_pages, 0);

@@ -161,8 +161,9 @@ int32_t b2_model_ensure_rope(b2_model* m, int positions) {
     if (m->sin_tab) cudaFree(m->sin_tab);
     B2_CUDA(cudaMalloc((void**)&m->cos_tab, c.size() * 2));
     B2_CUDA(cudaMalloc((void**)&m->sin_tab, s.size() * 2));
-    B2_CUDA(cudaMemcpy(m->cos_tab, c.data(), c.size() * 2, cudaMemcpyHostToDevice));
-    B2_CUDA(cudaMemcpy(m->sin_tab, s.data(), s.size() * 2, cudaMemcpyHostToDevice));
+    B2_CUDA(cudaMemcpyAsync(m->cos_tab, c.data(), c.size() * 2, cudaMemcpyHostToDevice, m->ctx->stream));
+    B2_CUDA(cudaMemcpyAsync(m->sin_tab, s.data(), s.size() * 2, cudaMemcpyHostToDevice, m->ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(m->ctx->stream));  // ordered on the context stream; host buffers die here
     m->rope_positions = n;
     return B2_OK;
 }
@@ -373,7 +374,9 @@ static int32_t upload_bf16(b2_model* m, const b2_weights* w, const std::string& 
     const HostTensor& t = it->second;
     B2_REQUIRE(t.numel() == expect_elems, B2_ERR_CONFIG, "tensor `" + key + "` has an unexpected size");
     if (t.dtype == B2_DTYPE_BF16) {
-        B2_CUDA(cudaMemcpy(dst, t.ptr, (size_t)expect_elems * 2, cudaMemcpyHostToDevice));
+        // every copy goes through the context stream (a plain cudaMemcpy is not ordered against it)
+        B2_CUDA(cudaMemcpyAsync(dst, t.ptr, (size_t)expect_elems * 2, cudaMemcpyHostToDevice, m->ctx->stream));
+        B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
         return B2_OK;
     }
     B2_REQUIRE(t.dtype == B2_DTYPE_F32 || t.dtype == B2_DTYPE_F16, B2_ERR_CONFIG, "tensor `" + key + "` is not a floating-point tensor");
@@ -385,7 +388,8 @@ static int32_t upload_bf16(b2_model* m, const b2_weights* w, const std::string& 
         const uint16_t* h = (const uint16_t*)t.ptr;
         for (int64_t i = 0; i < expect_elems; i++) tmp[i] = h_f2bf(h_half2f(h[i]));
     }
-    B2_CUDA(cudaMemcpy(dst, tmp.data(), (size_t)expect_elems * 2, cudaMemcpyHostToDevice));
+    B2_CUDA(cudaMemcpyAsync(dst, tmp.data(), (size_t)expect_elems * 2, cudaMemcpyHostToDevice, m->ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
     return B2_OK;
 }
 
@@ -404,7 +408,9 @@ static int32_t load_proj_rows(b2_model* m, const b2_weights* w, const std::strin
         const size_t words = (size_t)N * K * dst.bits / 32;
         B2_REQUIRE(wt->second.dtype == B2_DTYPE_U32 && (size_t)wt->second.numel() == words, B2_ERR_CONFIG,
                    "tensor `" + key + "` is not a packed u32 weight of the expected size");
-        B2_CUDA(cudaMemcpy((uint32_t*)dst.w + (size_t)row0 * K * dst.bits / 32, wt->second.ptr, words * 4, cudaMemcpyHostToDevice));
+        B2_CUDA(cudaMemcpyAsync((uint32_t*)dst.w + (size_t)row0 * K * dst.bits / 32, wt->second.ptr, words * 4, cudaMemcpyHostToDevice,
+                                m->ctx->stream));
+        B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
         B2_CHECK(upload_bf16(m, w, base + ".scales", (int64_t)N * (K / 64), dst.scales + (size_t)row0 * (K / 64)));
         B2_CHECK(upload_bf16(m, w, base + ".biases", (int64_t)N * (K / 64), dst.biases + (size_t)row0 * (K / 64)));
         return B2_OK;

@@ -143,10 +143,17 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
             o[mt][2] *= a0;
             o[mt][3] *= a1;
         }
-        // P^T as the B operand (tokens on K, heads on N)
-        uint32_t pb[2];
-        pb[0] = movmatrix_trans(pack_bf2(p0, p1));
-        pb[1] = movmatrix_trans(pack_bf2(p2, p3));
+        // P^T as the B operand (tokens on K, heads on N).  P is split into a bf16 head and a bf16
+        // remainder so the product with V carries ~16 mantissa bits instead of 8.
+        uint32_t pb[2], pl[2];
+        {
+            const uint32_t h01 = pack_bf2(p0, p1), h23 = pack_bf2(p2, p3);
+            const uint32_t l01 = pack_bf2(p0 - bflo(h01), p1 - bfhi(h01)), l23 = pack_bf2(p2 - bflo(h23), p3 - bfhi(h23));
+            pb[0] = movmatrix_trans(h01);
+            pb[1] = movmatrix_trans(h23);
+            pl[0] = movmatrix_trans(l01);
+            pl[1] = movmatrix_trans(l23);
+        }
         // O^T[d, head] += V^T[d, token] P^T[token, head]
         {
             const int r = lr + (mi >> 1) * 8;
@@ -156,6 +163,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
                 uint32_t a[4];
                 ldmatrix_x4_trans(a[0], a[1], a[2], a[3], vb + r * ROWB + ((ch ^ (r & 7)) << 4));
                 mma_bf16_16816(o[mt], a, pb);
+                mma_bf16_16816(o[mt], a, pl);
             }
         }
         __syncwarp();

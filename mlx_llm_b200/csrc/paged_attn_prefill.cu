@@ -150,15 +150,19 @@ __global__ void __launch_bounds__(kThreads) paged_attn_prefill_kernel(const Pref
             o[i][2] *= a1;
             o[i][3] *= a1;
         }
-        uint32_t pa[KT / 16][4];
+        // P as the A operand, split into a bf16 head and a bf16 remainder (~16 mantissa bits)
+        uint32_t pa[KT / 16][4], pr[KT / 16][4];
 #pragma unroll
         for (int nt = 0; nt < KT / 8; nt++) {
             const float p0 = fast_exp2(s[nt][0] - mn0), p1 = fast_exp2(s[nt][1] - mn0);
             const float p2 = fast_exp2(s[nt][2] - mn1), p3 = fast_exp2(s[nt][3] - mn1);
             l0 += p0 + p1;
             l1 += p2 + p3;
-            pa[nt >> 1][(nt & 1) * 2] = pack_bf2(p0, p1);
-            pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf2(p2, p3);
+            const uint32_t h01 = pack_bf2(p0, p1), h23 = pack_bf2(p2, p3);
+            pa[nt >> 1][(nt & 1) * 2] = h01;
+            pa[nt >> 1][(nt & 1) * 2 + 1] = h23;
+            pr[nt >> 1][(nt & 1) * 2] = pack_bf2(p0 - bflo(h01), p1 - bfhi(h01));
+            pr[nt >> 1][(nt & 1) * 2 + 1] = pack_bf2(p2 - bflo(h23), p3 - bfhi(h23));
         }
         // O += P V
 #pragma unroll
@@ -172,6 +176,8 @@ __global__ void __launch_bounds__(kThreads) paged_attn_prefill_kernel(const Pref
                 const uint32_t b0[2] = {bv[0], bv[1]}, b1[2] = {bv[2], bv[3]};
                 mma_bf16_16816(o[2 * np], pa[kk], b0);
                 mma_bf16_16816(o[2 * np + 1], pa[kk], b1);
+                mma_bf16_16816(o[2 * np], pr[kk], b0);
+                mma_bf16_16816(o[2 * np + 1], pr[kk], b1);
             }
         }
         __syncthreads();

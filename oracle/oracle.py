@@ -221,8 +221,8 @@ def paged_attention(q, kpool, vpool, block_tables, cu_seqlens, ctx_lens, scale, 
     kpool = _c(kpool, np.uint16)
     vpool = _c(vpool, np.uint16)
     bt = _c(block_tables, np.int32)
-    cu = _c(cu_seqlens, np.int32)
     ctx = _c(ctx_lens, np.int32)
+    cu = _c(cu_seqlens if cu_seqlens is not None else np.arange(ctx.size + 1), np.int32)
     T, hq, hd = q.shape
     _, hkv, page, _ = kpool.shape
     out = np.empty((T, hq, hd), np.float32)

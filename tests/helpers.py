@@ -175,3 +175,25 @@ def bf16_ulp_diff(a, b):
         h = h.astype(np.int32)
         return np.where(h & 0x8000, 0x8000 - (h & 0x7FFF), 0x8000 + (h & 0x7FFF))
     return np.abs(key(np.asarray(a)) - key(np.asarray(b)))
+
+
+def close_bf16_out(got_bf16, ref_f32, abs_tol=2e-3):
+    """Parity rule for a bf16 output against an f32/f64 reference: max-abs `abs_tol` on the value that
+    is rounded, plus the rounding of the bf16 output itself (half an ulp is 2^-9 relative; 2^-8 covers
+    an upstream and a final rounding).  Returns (ok, worst absolute error)."""
+    got = bf16_to_f32_np(got_bf16)
+    err = np.abs(got - ref_f32)
+    tol = abs_tol + np.abs(ref_f32) * 2.0 ** -8
+    return bool(np.isfinite(got).all() and (err <= tol).all()), float(err.max())
+
+
+def weights_crc(w):
+    """Checksum of the tiny model's weights (detects a libm that draws different Box-Muller values)."""
+    import zlib
+
+    crc = zlib.crc32(np.ascontiguousarray(w["embed"]).tobytes())
+    crc = zlib.crc32(np.ascontiguousarray(w["lm_head"]).tobytes(), crc)
+    for lw in w["layers"]:
+        for k in ("q", "k", "v", "o", "gate", "up", "down"):
+            crc = zlib.crc32(np.ascontiguousarray(lw[k]).tobytes(), crc)
+    return int(crc)

@@ -2,8 +2,9 @@
 
 Integer outputs (unpacked codes, packer metadata, KV slots, argmax) and bf16 outputs whose
 arithmetic has no reduction (dequantized weights, RoPE, KV append, residual add) must be bit-exact.
-Outputs behind an f32 reduction (matmuls, RMSNorm) are compared on the unrounded f32 accumulation
-with max-abs <= 2e-3 and on the bf16 result within one bf16 ulp."""
+Outputs behind an f32 reduction are compared on the unrounded f32 accumulation with max-abs <= 2e-3
+(matmuls), and on the bf16 result with that bound plus the output's own rounding
+(helpers.close_bf16_out) or within one bf16 ulp (RMSNorm, SwiGLU)."""
 import numpy as np
 import pytest
 
@@ -82,7 +83,7 @@ def test_qmm_vs_oracle(env, bits, m):
     ctx.sync()
     rf, rb = orc.qmm(x, packed, scales, biases, 64, bits)
     assert np.abs(yf.download() - rf).max() <= 2e-3
-    assert H.bf16_ulp_diff(yb.download(), rb).max() <= 1
+    assert H.close_bf16_out(yb.download(), rf)[0]
 
 
 def test_qmm_reference_small_case(env):
@@ -113,7 +114,7 @@ def test_linear_vs_oracle(env, m, n, k):
     ctx.sync()
     rf, rb = orc.linear(x, w)
     assert np.abs(yf.download() - rf).max() <= 2e-3
-    assert H.bf16_ulp_diff(yb.download(), rb).max() <= 1
+    assert H.close_bf16_out(yb.download(), rf)[0]
 
 
 def test_linear_exact_small_ints(env):
@@ -297,9 +298,8 @@ def test_prefill_attention_vs_oracle(env, hq, hkv, hd):
     ctx.sync()
     ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"], case["ctx_lens"],
                               case["scale"])
-    got = H.bf16_to_f32_np(out.download())
-    assert np.isfinite(got).all()
-    assert np.abs(got - ref).max() <= 2e-3 * max(1.0, float(np.abs(ref).max()))
+    ok, err = H.close_bf16_out(out.download(), ref)
+    assert ok, f"max-abs {err}"
 
 
 def test_attention_reference_shapes_f64_host(env):

@@ -1,10 +1,9 @@
 """Parity of the CUDA paged-attention decode kernel (through the C ABI) against the CPU oracle.
 
-Tolerance: max-abs 2e-3 on the bf16 output against the oracle's f64-accumulated result (BASELINE's
-bound) wherever the outputs stay below 1 in magnitude, which includes every configuration-1 shaped
-case.  Very short contexts give outputs of magnitude 2-4, where one bf16 output ulp alone is up to
-1.6e-2; there the reference's own relative gate applies (max|diff| / max|ref| < 2e-3,
-src/primitives/attention.rs:445-449, :457-480)."""
+Tolerance: max-abs 2e-3 against the oracle's f64-accumulated result (BASELINE's bound), strictly, on
+every configuration-1 shaped case (contexts >= 128, outputs well below 1).  Very short contexts give
+outputs of magnitude 2-4, where the rounding of the bf16 OUTPUT alone is up to 7.8e-3; there the rule
+is 2e-3 plus that rounding (helpers.close_bf16_out)."""
 import numpy as np
 import pytest
 
@@ -44,11 +43,10 @@ def run_case(env, case, chunk_tokens=0, host_io=False, strict_abs=False):
         b.free()
     ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"],
                               case["ctx_lens"], case["scale"])
-    got = H.bf16_to_f32_np(out)
-    assert np.isfinite(got).all()
-    err = np.abs(got - ref).max()
-    tol = TOL * max(1.0, float(np.abs(ref).max())) if not strict_abs else TOL
-    assert err <= tol, f"max-abs {err} (tol {tol})"
+    ok, err = H.close_bf16_out(out, ref, TOL)
+    assert ok, f"max-abs {err}"
+    if strict_abs:
+        assert err <= TOL, f"max-abs {err}"
     return err
 
 
@@ -123,7 +121,7 @@ def test_decode_linearity_full_size(env):
         ctx.sync()
         outs.append(H.bf16_to_f32_np(o.download()))
         vp.free(); o.free()
-    assert np.abs(2.0 * outs[0] - outs[1]).max() <= 2 * TOL
+    assert np.abs(2.0 * outs[0] - outs[1]).max() <= 2 * TOL  # outputs here are < 0.5 in magnitude
     # spot-check 3 sequences against the oracle
     for i in (0, 31, 63):
         sub = dict(case)
