@@ -4,12 +4,20 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Prints ONE JSON line (rank 0).  Workloads:
-  paged_attn_decode      BASELINE configuration 1: paged-attention decode microbenchmark
-                         (64 sequences, 32 q / 8 kv heads, head_dim 128, page 16, ctx U[128,4096]).
-A "step" is one pass of the hot path over one synthetic batch.  `value` is timed on the device with
-inputs resident in HBM; `e2e` goes through the C ABI with HOST buffers (copies inside the timed
-region).  `--impl reference` times the CPU restatement of the reference's path (the reference itself
-is Rust + MLX/Metal and cannot run on this box) on a bounded sample of the same workload.
+  llama3_8b_q4_continuous  (default) BASELINE configuration 3: Llama-3-8B-architecture, Q4 group-64
+                           projections, bf16 embeddings / head / norms, 2048 synthetic requests, up to
+                           256 concurrent sequences, page 16, 512-token prefill chunks packed with the
+                           decode tokens of every live sequence in one ragged batch, greedy.  One
+                           independent replica per GPU, requests sharded id mod N, no collective.
+  paged_attn_decode        BASELINE configuration 1: paged-attention decode microbenchmark
+                           (64 sequences, 32 q / 8 kv heads, head_dim 128, page 16, ctx U[128,4096]).
+A "step" is one iteration of the serving loop (one ragged forward over one batch).  The engine is
+first rolled to its steady state (`ramp` iterations, untimed, all requests available at t = 0), then W
+warm-up and K timed iterations follow.  `value` = generated tokens / device time of the K forwards
+(CUDA events on the launching stream); `e2e` = the same K iterations by wall clock through the C ABI,
+host scheduling and the per-step host<->device copies included.  `--impl reference` times the CPU
+restatement of the reference's path (the reference itself is Rust + MLX/Metal and cannot run on this
+box) on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -81,6 +89,118 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
+# BASELINE configuration 3: Llama-3-8B-architecture Q4 continuous batching
+def continuous_setup(args, rank, world, local_rank):
+    from mlx_llm_b200 import _lib, engine as eng, workloads as wl
+
+    shape = dict(wl.LLAMA3_8B if args.layers <= 0 else dict(wl.LLAMA3_8B, num_layers=args.layers))
+    ctx = _lib.Context(local_rank)
+    cfg = eng.model_config(**shape, quant_bits=4, quant_group=64)
+    model = eng.CausalLm.synthetic(ctx, cfg, seed=0)
+    # weak scaling: every replica serves its own `requests` requests (ids r, r+N, r+2N, ... of N*requests)
+    prompts, outs, arrival = wl.serving_requests(n=args.requests * world, seed=0, rate=50.0 * world, vocab=shape["vocab_size"],
+                                                 poisson=args.arrivals == "poisson")
+    idx = [i for i in range(len(prompts)) if i % world == rank]
+    reqs = [eng.BatchRequest(prompts[i], int(outs[i]), arrival_s=float(arrival[i])) for i in idx]
+    ccfg = eng.ContinuousConfig(max_batch=args.max_batch, block_size=16, exactness=eng.THROUGHPUT, prefill_chunk_tokens=args.chunk,
+                                max_pages=args.max_pages, max_blocks_per_seq=(8192 + 512) // 16 + 2)
+    return ctx, model, reqs, ccfg, shape
+
+
+def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
+    from mlx_llm_b200 import engine as eng, workloads as wl
+
+    ctx, model, reqs, ccfg, shape = continuous_setup(args, rank, world, local_rank)
+    engine = eng.ContinuousEngine(model, reqs, ccfg)
+    done, st = engine.step(args.ramp)                 # untimed roll to the steady state
+    warm = max(args.warmup, 3)
+    done, st = engine.step(warm)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    s0 = st
+    t0 = time.perf_counter()
+    done, s1 = engine.step(args.steps)
+    ctx.sync()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    clocks = sampler.stop()
+    steps = s1["steps"] - s0["steps"]
+    gen = s1["decode_tokens"] - s0["decode_tokens"]
+    pre = s1["prefill_tokens"] - s0["prefill_tokens"]
+    dev_ms = s1["device_ms"] - s0["device_ms"]
+    launches = s1["kernel_launches"] - s0["kernel_launches"]
+    h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) / max(steps, 1)
+    d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) / max(steps, 1)
+    # per-kernel-class durations over further iterations of the same steady state (CUDA events
+    # between the classes on the launching stream)
+    eng.profile_enable(ctx, True)
+    p0 = engine.step(0)[1]
+    done, p1 = engine.step(args.profile_steps)
+    prof = eng.profile_read(ctx)
+    eng.profile_enable(ctx, False)
+    prof_steps = max(p1["steps"] - p0["steps"], 1)
+    all_gen, all_dev, all_wall = reduce_sum(gen), reduce_max(dev_ms), reduce_max(wall_ms)
+    peaks = measured_peaks()
+    gemm_ms = prof["ms"]["gemm"]
+    tfl = prof["gemm_flops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    total_prof_ms = sum(prof["ms"].values())
+    dec_ms = prof["ms"]["attn_decode"]
+    out = dict(
+        metric="continuous-batch decode tok/s, Llama-3-8B-arch Q4", value=all_gen / (all_dev * 1e-3), unit="tok/s", n_gpus=world,
+        steps=int(steps), warmup=warm, ms_per_step=all_dev / max(steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
+        dtype="bf16", data="synthetic",
+        config=dict(workload="llama3_8b_q4_continuous (BASELINE configuration 3)", layers=shape["num_layers"], requests=args.requests,
+                    arrivals=args.arrivals, max_batch=args.max_batch, page=16, prefill_chunk=args.chunk, ramp_steps=args.ramp,
+                    parallelism=f"replica x{world}, requests sharded id mod N", l2="per-step working set (weights 5 GB + KV) exceeds L2",
+                    prefill_tokens_per_step=pre / max(steps, 1), generated_tokens_per_step=gen / max(steps, 1)),
+        roofline=dict(bound="tensor", achieved=tfl, peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
+                      frac=tfl / peaks["bf16_tflops_sustained"], traffic=None, peak_source=peaks["source"] + " (sustained)",
+                      kernel="projection GEMMs (Q4 dequant fused) + bf16 lm_head", launches_per_step=prof["launches"]["gemm"] / prof_steps,
+                      ms_per_step=gemm_ms / prof_steps, share_of_step=gemm_ms / total_prof_ms if total_prof_ms else None,
+                      algorithmic_flops_per_step=prof["gemm_flops"] / prof_steps),
+        roofline_paged_attn_decode=dict(bound="hbm", achieved=(prof["attn_decode_bytes"] / (dec_ms * 1e-3) / 1e9) if dec_ms > 0 else None,
+                                        peak=peaks["hbm_gbs"], unit="GB/s",
+                                        frac=(prof["attn_decode_bytes"] / (dec_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if dec_ms > 0 else None,
+                                        ms_per_step=dec_ms / prof_steps, algorithmic_bytes_per_step=prof["attn_decode_bytes"] / prof_steps),
+        class_ms_per_step={k: v / prof_steps for k, v in prof["ms"].items()},
+        e2e=dict(value=all_gen / (all_wall * 1e-3), unit="tok/s", h2d_bytes_per_step=int(h2d), d2h_bytes_per_step=int(d2h)),
+        gpu_launches=int(launches), clocks=clocks,
+    )
+    engine.free()
+    model.free()
+    return out
+
+
+def cpu_baseline_continuous(args, seconds=20.0):
+    """The CPU restatement of the reference's loop (whole-prompt prefill at admission, batched decode)
+    on a bounded sample of the same workload: the same Q4 Llama-3-8B-shape model cut to `cpu_layers`
+    layers, `cpu_requests` requests with prompts clipped to 64 tokens and 8 new tokens each."""
+    from mlx_llm_b200 import workloads as wl
+    from oracle import oracle as orc
+
+    shape = dict(wl.LLAMA3_8B, num_layers=args.cpu_layers)
+    m = orc.Model(layers=shape["num_layers"], hidden=shape["hidden_size"], heads=shape["num_heads"], kv_heads=shape["num_kv_heads"],
+                  head_dim=shape["head_dim"], inter=shape["intermediate_size"], vocab=shape["vocab_size"], eps=1e-5, theta=500000.0,
+                  rope_kind=1, rope_factor=8.0, rope_low=1.0, rope_high=4.0, rope_orig=8192.0, qk_norm=0, quant_bits=4, group=64, f32_mode=0)
+    m.fill_synthetic(0)
+    prompts, outs, _ = wl.serving_requests(n=args.cpu_requests, seed=0, vocab=shape["vocab_size"], poisson=False)
+    prompts = [p[:64] for p in prompts]
+    t0 = time.perf_counter()
+    res = m.generate_continuous(prompts, [8] * len(prompts), max_batch=len(prompts), throughput=True)
+    dt = time.perf_counter() - t0
+    gen = sum(len(t) for t in res["tokens"])
+    # scale the layer cut back to the full depth (the per-layer work is identical; embeddings and the
+    # head are counted once)
+    full = dt * 32.0 / args.cpu_layers
+    m.free()
+    return dict(value=gen / full, unit="tok/s", cores=os.cpu_count(), kind="port",
+                sample=f"{len(prompts)} requests, prompts clipped to 64 tokens, 8 new tokens each, {args.cpu_layers} of 32 layers timed "
+                       f"({dt:.1f} s) and scaled to 32 layers", measured_seconds=dt)
+
+
+# ------------------------------------------------------------------------------------------------
+# BASELINE configuration 1: paged-attention decode microbenchmark
 def config1_case(n_seqs=64, seed=0):
     from tests import helpers as H
 
@@ -90,14 +210,15 @@ def config1_case(n_seqs=64, seed=0):
 
 
 def attn_alg_bytes(case):
-    """Algorithmic bytes of one decode-attention pass: every cached K and V byte once (the GQA group
-    shares it), q in, out back, block tables."""
+    """Every cached K and V byte once (the GQA group shares it), q in, out back, block tables."""
     ctx = case["ctx_lens"].astype(np.int64)
     kv = int(ctx.sum()) * case["hkv"] * case["hd"] * 2 * 2
     return kv + 2 * case["q"].nbytes + 4 * int(((ctx + case["page"] - 1) // case["page"]).sum())
 
 
-def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max):
+def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
+    import ctypes as C
+
     from mlx_llm_b200 import _lib, kernels
 
     ctx = _lib.Context(local_rank)
@@ -125,9 +246,7 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max):
     barrier()
     launches = ctx.launch_count() - l0
     t_dev = reduce_max(t_dev)
-    # e2e: host q in, host out back, through the host-buffer entry point
-    import ctypes as C
-    hq = C.c_void_p(); ho = C.c_void_p()
+    hq, ho = C.c_void_p(), C.c_void_p()
     lib = _lib.load()
     _lib.check(lib.b2_host_alloc_pinned(C.c_size_t(case["q"].nbytes), C.byref(hq)))
     _lib.check(lib.b2_host_alloc_pinned(C.c_size_t(case["q"].nbytes), C.byref(ho)))
@@ -137,28 +256,27 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max):
     for _ in range(3):
         e2e_call()
     barrier()
-    t0 = time.perf_counter()
+    t_e2e = 0.0
     for _ in range(args.steps):
         ctx.flush_l2()
+        ctx.sync()
+        t0 = time.perf_counter()
         e2e_call()
-    ctx.sync()
-    t_e2e = reduce_max((time.perf_counter() - t0) * 1e3)
+        t_e2e += (time.perf_counter() - t0) * 1e3
+    t_e2e = reduce_max(t_e2e)
     clocks = sampler.stop()
     barrier()
-
-    alg = attn_alg_bytes(case)
-    peaks = measured_peaks()
+    alg, peaks = attn_alg_bytes(case), measured_peaks()
     ms = t_dev / args.steps
     gbs = alg / (ms * 1e-3) / 1e9
-    toks = n * world / (ms * 1e-3)
     out = dict(
-        metric="paged-attention decode tokens/s (one token per sequence per step)", value=toks, unit="tok/s", n_gpus=world,
-        steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
-        dtype="bf16", data="synthetic",
+        metric="paged-attention decode tokens/s (one token per sequence per step)", value=n * world / (ms * 1e-3), unit="tok/s",
+        n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak",
+        vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload="paged_attn_decode (BASELINE configuration 1): 64 seqs, 32q/8kv heads, hd 128, page 16, ctx U[128,4096]",
-                    l2="flushed between timed iterations", parallelism=f"replica x{world}", chunk_tokens=args.chunk_tokens),
+                    l2="flushed between timed iterations", parallelism=f"replica x{world}", chunk_tokens=args.chunk_tokens or 512),
         roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"], traffic=None,
-                      peak_source=peaks["source"], algorithmic_bytes=alg, kernel="paged_attn_decode_kernel<128> (+worklist, merge)"),
+                      peak_source=peaks["source"], algorithmic_bytes=alg, kernel="paged_attn_decode_kernel<128> (+ work list, merge)"),
         e2e=dict(value=n * world / (t_e2e / args.steps * 1e-3), unit="tok/s", h2d_bytes_per_step=case["q"].nbytes,
                  d2h_bytes_per_step=case["q"].nbytes),
         gpu_launches=int(launches), clocks=clocks,
@@ -168,48 +286,58 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max):
     return out
 
 
-def cpu_baseline_paged_attn(case, sample=16):
+def cpu_baseline_paged_attn(case, sample=16, seconds=5.0):
     """Oracle paged attention (f32 accumulate, OpenMP over (sequence, kv head)) on the first `sample`
     sequences of the same batch."""
     from oracle import oracle as orc
 
-    sub = dict(case)
     n = min(sample, case["ctx_lens"].size)
-    orc.paged_attention(case["q"][:1], case["kpool"], case["vpool"], case["block_tables"][:1], None, case["ctx_lens"][:1],
-                        case["scale"], fast_decode=True)
-    t0 = time.perf_counter()
-    reps = 0
-    while time.perf_counter() - t0 < 5.0:
-        orc.paged_attention(case["q"][:n], case["kpool"], case["vpool"], case["block_tables"][:n], None, case["ctx_lens"][:n],
-                            case["scale"], fast_decode=True)
+    f = lambda k: orc.paged_attention(case["q"][:k], case["kpool"], case["vpool"], case["block_tables"][:k], None, case["ctx_lens"][:k],
+                                      case["scale"], fast_decode=True)
+    f(1)
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < seconds:
+        f(n)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
     return dict(value=n / dt, unit="tok/s", cores=os.cpu_count(), kind="port",
                 sample=f"first {n} of {case['ctx_lens'].size} sequences of the same batch, {reps} repetitions")
 
 
+# ------------------------------------------------------------------------------------------------
 def run_reference(args, rank, world):
-    """CPU restatement of the reference path on this box's host cores (rank 0 only)."""
+    """`--impl reference`: the CPU restatement of the reference path on this box's host cores (rank 0
+    only).  Every step is one bounded sample of the same workload."""
     if rank != 0:
         return None
-    case = config1_case()
-    from oracle import oracle as orc
+    if args.workload == "paged_attn_decode":
+        case = config1_case()
+        from oracle import oracle as orc
 
-    n = 16
-    f = lambda: orc.paged_attention(case["q"][:n], case["kpool"], case["vpool"], case["block_tables"][:n], None,
-                                    case["ctx_lens"][:n], case["scale"], fast_decode=True)
-    for _ in range(max(1, min(args.warmup, 3))):
-        f()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        f()
-    dt = (time.perf_counter() - t0) / args.steps
-    v = n / dt
-    sample = f"each step = first {n} of 64 sequences of the configuration-1 batch"
-    return dict(impl="reference", metric="paged-attention decode tokens/s (one token per sequence per step)", value=v, unit="tok/s",
-                n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak",
-                vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload="paged_attn_decode (BASELINE configuration 1)", parallelism="cpu"),
+        n = 16
+        f = lambda: orc.paged_attention(case["q"][:n], case["kpool"], case["vpool"], case["block_tables"][:n], None,
+                                        case["ctx_lens"][:n], case["scale"], fast_decode=True)
+        for _ in range(max(1, min(args.warmup, 3))):
+            f()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            f()
+        dt = (time.perf_counter() - t0) / args.steps
+        v, metric = n / dt, "paged-attention decode tokens/s (one token per sequence per step)"
+        sample = f"each step = first {n} of 64 sequences of the configuration-1 batch"
+        wl_name = "paged_attn_decode (BASELINE configuration 1)"
+    else:
+        steps = max(1, min(args.steps, 3))
+        runs = [cpu_baseline_continuous(args) for _ in range(steps)]
+        v = float(np.mean([r["value"] for r in runs]))
+        dt = float(np.mean([r["measured_seconds"] for r in runs]))
+        metric, sample = "continuous-batch decode tok/s, Llama-3-8B-arch Q4", runs[0]["sample"] + f"; {steps} such samples"
+        wl_name = "llama3_8b_q4_continuous (BASELINE configuration 3)"
+        args.steps = steps
+    return dict(impl="reference", metric=metric, value=v, unit="tok/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                config=dict(workload=wl_name, parallelism="host cores (OpenMP)",
+                            note="CPU restatement of the reference path; the reference itself (Rust + MLX/Metal) is unavailable on this box"),
                 cpu_baseline=dict(value=v, unit="tok/s", cores=os.cpu_count(), kind="port", sample=sample),
                 e2e=dict(value=v, unit="tok/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
 
@@ -217,11 +345,22 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="paged_attn_decode")
-    ap.add_argument("--chunk-tokens", dest="chunk_tokens", type=int, default=0)
+    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode"])
+    ap.add_argument("--chunk-tokens", dest="chunk_tokens", type=int, default=0, help="paged_attn_decode: split-K chunk")
+    ap.add_argument("--requests", type=int, default=2048)
+    ap.add_argument("--arrivals", default="saturated", choices=["saturated", "poisson"])
+    ap.add_argument("--max-batch", dest="max_batch", type=int, default=256)
+    ap.add_argument("--chunk", type=int, default=512, help="prefill chunk tokens per step")
+    ap.add_argument("--max-pages", dest="max_pages", type=int, default=49152, help="KV pool pages (2 MiB each for the 8B shape)")
+    ap.add_argument("--ramp", type=int, default=400, help="untimed iterations that roll the engine to its steady state")
+    ap.add_argument("--profile-steps", dest="profile_steps", type=int, default=20)
+    ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0 = the full 32); not a valid bench line")
+    ap.add_argument("--cpu-layers", dest="cpu_layers", type=int, default=2)
+    ap.add_argument("--cpu-requests", dest="cpu_requests", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -235,7 +374,7 @@ def main():
         return 0
 
     barrier = lambda: None
-    reduce_max = lambda x: x
+    reduce_max = reduce_sum = lambda x: x
     if world > 1:
         import torch
         import torch.distributed as dist
@@ -247,17 +386,26 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-        def reduce_max(x):
+        def _reduce(x, op):
             t = torch.tensor([float(x)], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(t, op=op)
             return float(t.item())
 
-    out = run_paged_attn(args, rank, world, local_rank, barrier, reduce_max)
+        reduce_max = lambda x: _reduce(x, dist.ReduceOp.MAX)
+        reduce_sum = lambda x: _reduce(x, dist.ReduceOp.SUM)
+
+    if args.workload == "paged_attn_decode":
+        out = run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
+    else:
+        out = run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
+        if rank == 0 and args.cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline_continuous(args)
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         import torch.distributed as dist
 
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

@@ -282,6 +282,29 @@ int32_t b2_generate(b2_model* m, const b2_request* req, const volatile int32_t* 
 int32_t b2_generate_continuous(b2_model* m, const b2_request* reqs, int32_t n, const b2_continuous_config* cfg,
                                const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_gen_output* outs,
                                b2_run_stats* stats);
+/* The same loop one iteration at a time (one iteration == one pass of continuous.rs:167-190), so a
+ * caller can time exactly K iterations.  `reqs` and the arrays it points to must outlive the engine.
+ * b2_continuous_step runs up to max_steps iterations; *done_out is 1 when no work is left.  stats
+ * are cumulative since b2_continuous_new. */
+typedef struct b2_continuous b2_continuous;
+int32_t b2_continuous_new(b2_model* m, const b2_request* reqs, int32_t n, const b2_continuous_config* cfg,
+                          const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_continuous** out);
+int32_t b2_continuous_step(b2_continuous* e, int32_t max_steps, int32_t* done_out, b2_run_stats* stats);
+int32_t b2_continuous_finish(b2_continuous* e, b2_gen_output* outs, b2_run_stats* stats);
+int32_t b2_continuous_free(b2_continuous* e);
+
+/* ---- per-kernel-class timing (CUDA events on the launching stream; off by default) -------------
+ * classes: 0 projections (GEMM), 1 paged-attention decode, 2 paged-attention prefill, 3 RoPE + KV
+ * append, 4 norm / activation / embedding / argmax, 5 packer + step copies.  The algorithmic work of
+ * the same launches is accumulated beside the times: GEMM flops (2*M*N*K) and weight bytes, decode
+ * attention K/V bytes (each cached byte once per layer), prefill attention flops. */
+typedef struct {
+    double ms[8];
+    int64_t launches[8];
+    double gemm_flops, gemm_weight_bytes, attn_decode_bytes, attn_prefill_flops;
+} b2_profile_t;
+int32_t b2_profile_enable(b2_ctx* ctx, int32_t on);   /* also resets the accumulators */
+int32_t b2_profile_read(b2_ctx* ctx, b2_profile_t* out);
 
 #ifdef __cplusplus
 }

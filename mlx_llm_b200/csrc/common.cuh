@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/b200llm.h"
 
@@ -43,7 +44,22 @@ struct b2_ctx {
     // staging for the *_host entry points
     void* stage = nullptr;
     size_t stage_bytes = 0;
+    // optional per-kernel-class timing with CUDA events on the launching stream
+    bool profile = false;
+    std::vector<cudaEvent_t> prof_ev;
+    std::vector<int> prof_cls;
+    std::vector<int64_t> prof_launch;
+    size_t prof_used = 0;
+    double class_ms[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int64_t class_launches[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    double gemm_flops = 0, gemm_weight_bytes = 0, attn_decode_bytes = 0, attn_prefill_flops = 0;
 };
+// kernel classes for the profile
+enum { B2_CLS_GEMM = 0, B2_CLS_ATTN_DECODE = 1, B2_CLS_ATTN_PREFILL = 2, B2_CLS_ROPE_KV = 3, B2_CLS_ELEMENTWISE = 4, B2_CLS_META = 5 };
+// Marks the start of a stretch of launches of class `cls` (-1 closes the last stretch).
+void b2_prof_mark(b2_ctx* ctx, int cls);
+// After the stream has been synchronised: folds the recorded stretches into class_ms.
+void b2_prof_collect(b2_ctx* ctx);
 int32_t b2_ctx_scratch(b2_ctx* ctx, size_t bytes, void** out);
 int32_t b2_ctx_stage(b2_ctx* ctx, size_t bytes, void** out);
 #define B2_LAUNCHED(ctx) ((ctx)->launches++)

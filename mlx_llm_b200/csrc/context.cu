@@ -128,7 +128,61 @@ int32_t b2_launch_count(b2_ctx* ctx, int64_t* out) {
     return B2_OK;
 }
 
+int32_t b2_profile_enable(b2_ctx* ctx, int32_t on) {
+    B2_REQUIRE(ctx, B2_ERR_MSG, "b2_profile_enable: null context");
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->profile = on != 0;
+    ctx->prof_used = 0;
+    ctx->prof_cls.clear();
+    ctx->prof_launch.clear();
+    for (int i = 0; i < 8; i++) {
+        ctx->class_ms[i] = 0;
+        ctx->class_launches[i] = 0;
+    }
+    ctx->gemm_flops = ctx->gemm_weight_bytes = ctx->attn_decode_bytes = ctx->attn_prefill_flops = 0;
+    return B2_OK;
+}
+
+int32_t b2_profile_read(b2_ctx* ctx, b2_profile_t* out) {
+    B2_REQUIRE(ctx && out, B2_ERR_MSG, "b2_profile_read: null argument");
+    for (int i = 0; i < 8; i++) {
+        out->ms[i] = ctx->class_ms[i];
+        out->launches[i] = ctx->class_launches[i];
+    }
+    out->gemm_flops = ctx->gemm_flops;
+    out->gemm_weight_bytes = ctx->gemm_weight_bytes;
+    out->attn_decode_bytes = ctx->attn_decode_bytes;
+    out->attn_prefill_flops = ctx->attn_prefill_flops;
+    return B2_OK;
+}
+
 }  // extern "C"
+
+void b2_prof_mark(b2_ctx* ctx, int cls) {
+    if (!ctx->profile) return;
+    if (ctx->prof_used == ctx->prof_ev.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return;
+        ctx->prof_ev.push_back(e);
+    }
+    cudaEventRecord(ctx->prof_ev[ctx->prof_used++], ctx->stream);
+    ctx->prof_cls.push_back(cls);
+    ctx->prof_launch.push_back(ctx->launches);
+}
+
+void b2_prof_collect(b2_ctx* ctx) {
+    if (!ctx->profile) return;
+    for (size_t i = 0; i + 1 < ctx->prof_used; i++) {
+        const int cls = ctx->prof_cls[i];
+        if (cls < 0 || cls >= 8) continue;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, ctx->prof_ev[i], ctx->prof_ev[i + 1]) == cudaSuccess) ctx->class_ms[cls] += ms;
+        ctx->class_launches[cls] += ctx->prof_launch[i + 1] - ctx->prof_launch[i];
+    }
+    ctx->prof_used = 0;
+    ctx->prof_cls.clear();
+    ctx->prof_launch.clear();
+}
 
 int32_t b2_ctx_scratch(b2_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->scratch_bytes) {

@@ -131,7 +131,9 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, c.num_kv_heads, ctx->sm_count);
     const int q_tile = 64;
     int W = 0, P = 0;
+    double pf_flops = 0;  // 4*hd*hq flops per (query, visible key) pair
     for (auto& s : seqs) {
+        if (s.n > 1) pf_flops += 4.0 * c.head_dim * c.num_heads * ((double)s.n * s.cache->len + 0.5 * (double)s.n * (s.n + 1));
         if (s.n == 1) {
             const int tiles = (s.cache->len + 1 + 15) / 16;
             W += (tiles + chunk_tiles - 1) / chunk_tiles;
@@ -164,6 +166,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     }
     cudaStream_t st = ctx->stream;
     B2_CUDA(cudaEventRecord(m->ev0, st));
+    b2_prof_mark(ctx, B2_CLS_META);
     B2_CUDA(cudaMemcpyAsync(w.stage_dev, sh, stage_ints * 4, cudaMemcpyHostToDevice, st));
     m->h2d_bytes += (int64_t)stage_ints * 4;
     pool->upd_slot.clear();
@@ -195,10 +198,13 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     const int H = c.hidden_size, hq = c.num_heads, hkv = c.num_kv_heads, hd = c.head_dim, I = c.intermediate_size;
     const int qkv_w = (hq + 2 * hkv) * hd;
     const float scale_log2 = powf((float)hd, -0.5f) * 1.4426950408889634f;  // attn_scale, config.rs:597-598
+    b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
     B2_CHECK(b2_embed_launch(ctx, m->embed, ids_dev, T, H, c.vocab_size, w.x));
     for (int l = 0; l < c.num_layers; l++) {
         const LayerW& L = m->layers[l];
+        b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.input_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
+        b2_prof_mark(ctx, B2_CLS_GEMM);
         B2_CHECK(gemm(m, L.qkv, w.xn, T, H, w.qkv, qkv_w, nullptr));
         RopeKvParams rp{};
         rp.qkv = w.qkv;
@@ -218,6 +224,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
         rp.k_pool = pool->k_layer(l);
         rp.v_pool = pool->v_layer(l);
         rp.q_out = w.q;
+        b2_prof_mark(ctx, B2_CLS_ROPE_KV);
         B2_CHECK(b2_rope_kv_launch(ctx, rp));
         if (n_dec > 0) {
             DecodeAttnParams dp{};
@@ -241,7 +248,9 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
             dp.part_o = w.attn_scratch;
             dp.part_ml = w.attn_scratch + (size_t)w.w_cap * hq * hd;
             dp.out = w.attn;
+            b2_prof_mark(ctx, B2_CLS_ATTN_DECODE);
             B2_CHECK(b2_decode_attn_launch(ctx, dp, hd, W, n_dec));
+            ctx->attn_decode_bytes += (double)dec_ctx_sum * hkv * hd * 2 * 2;
         }
         if (P > 0) {
             PrefillAttnParams pp{};
@@ -261,23 +270,34 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
             pp.page_tiles = pool->block_size / 16;
             pp.scale_log2 = scale_log2;
             pp.out = w.attn;
+            b2_prof_mark(ctx, B2_CLS_ATTN_PREFILL);
             B2_CHECK(b2_prefill_attn_launch(ctx, pp, hd, P));
+            ctx->attn_prefill_flops += pf_flops;
         }
+        b2_prof_mark(ctx, B2_CLS_GEMM);
         B2_CHECK(gemm(m, L.o, w.attn, T, hq * hd, w.x, H, w.x));     // h = x + o_proj(attn)
+        b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.post_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
+        b2_prof_mark(ctx, B2_CLS_GEMM);
         B2_CHECK(gemm(m, L.gu, w.xn, T, H, w.gu, 2 * I, nullptr));
+        b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_swiglu_launch(ctx, w.gu, T, I, w.act));
+        b2_prof_mark(ctx, B2_CLS_GEMM);
         B2_CHECK(gemm(m, L.down, w.act, T, I, w.x, H, w.x));        // x = h + down(...)
     }
     if (n_logits > 0) {
+        b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_rms_norm_launch(ctx, w.x, m->norm, c.rms_norm_eps, n_logits, H, H, mo.logit_rows, w.last));
         Proj head;
         head.bits = 0;
         head.N = c.vocab_size;
         head.K = H;
         head.w = m->lm_head;
+        b2_prof_mark(ctx, B2_CLS_GEMM);
         B2_CHECK(gemm(m, head, w.last, n_logits, H, w.logits, c.vocab_size, nullptr));
+        b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_argmax_launch(ctx, w.logits, n_logits, c.vocab_size, w.argmax));
+        b2_prof_mark(ctx, B2_CLS_META);
         B2_CUDA(cudaMemcpyAsync(w.argmax_host, w.argmax, (size_t)n_logits * 4, cudaMemcpyDeviceToHost, st));
         m->d2h_bytes += (int64_t)n_logits * 4;
         if (logits_out) {
@@ -292,9 +312,11 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
             m->d2h_bytes += (int64_t)bytes;
         }
     }
+    b2_prof_mark(ctx, -1);
     B2_CUDA(cudaEventRecord(m->ev1, st));
     B2_CUDA(cudaStreamSynchronize(st));
     B2_CUDA(cudaGetLastError());
+    b2_prof_collect(ctx);
     float ms = 0.f;
     B2_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->device_ms += ms;

@@ -262,6 +262,8 @@ int32_t dispatch_bm(b2_ctx* ctx, const GemmParams& p) {
 int32_t b2_gemm_launch(b2_ctx* ctx, const GemmParams& p) {
     B2_REQUIRE(p.M >= 0 && p.N > 0 && p.K > 0, B2_ERR_MSG, "gemm: bad shape");
     if (p.M == 0) return B2_OK;
+    ctx->gemm_flops += 2.0 * p.M * (double)p.N * p.K;
+    ctx->gemm_weight_bytes += p.bits ? (double)p.N * p.K * p.bits / 8 + (double)p.N * (p.K / 64) * 4 : (double)p.N * p.K * 2;
     B2_REQUIRE(p.K % 8 == 0, B2_ERR_UNSUPPORTED, "gemm: K must be a multiple of 8");
     B2_REQUIRE(p.ldx % 8 == 0, B2_ERR_UNSUPPORTED, "gemm: activation row stride must be a multiple of 8 elements");
     if (p.bits == 0) return dispatch_bm<0>(ctx, p);

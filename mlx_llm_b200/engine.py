@@ -420,3 +420,76 @@ def generate(model, prompt_ids, max_new_tokens=256, stop_tokens=(), cancel: Opti
     if err:
         raise err[0]
     return GenerationOutput(buf[: out.n_tokens].tolist(), int(out.finish_reason))
+
+
+class CProfile(C.Structure):
+    _fields_ = [("ms", C.c_double * 8), ("launches", C.c_int64 * 8), ("gemm_flops", C.c_double), ("gemm_weight_bytes", C.c_double),
+                ("attn_decode_bytes", C.c_double), ("attn_prefill_flops", C.c_double)]
+
+
+PROFILE_CLASSES = ["gemm", "attn_decode", "attn_prefill", "rope_kv", "elementwise", "meta_copies"]
+
+
+def profile_enable(ctx, on=True):
+    check(load().b2_profile_enable(ctx.h, int(bool(on))))
+
+
+def profile_read(ctx):
+    p = CProfile()
+    check(load().b2_profile_read(ctx.h, C.byref(p)))
+    out = {"ms": {k: p.ms[i] for i, k in enumerate(PROFILE_CLASSES)}, "launches": {k: int(p.launches[i]) for i, k in enumerate(PROFILE_CLASSES)}}
+    for k in ("gemm_flops", "gemm_weight_bytes", "attn_decode_bytes", "attn_prefill_flops"):
+        out[k] = getattr(p, k)
+    return out
+
+
+class ContinuousEngine:
+    """generate_continuous one iteration at a time (b2_continuous_*): step(k) runs up to k iterations
+    of the loop and returns (done, cumulative stats)."""
+
+    def __init__(self, model, requests, config: ContinuousConfig, cancel: Optional[CancelFlag] = None, on_event=None):
+        self.requests = requests
+        self._arr, self._keep = _c_requests(requests)
+        self._err = []
+
+        def _cb(_user, req, kind, a, b):
+            try:
+                if on_event:
+                    on_event(req, ("token", a, b) if kind == 0 else ("done", a, b))
+            except Exception as e:
+                self._err.append(e)
+
+        self._cb = EVENT_CB(_cb) if on_event else C.cast(None, EVENT_CB)
+        self._cancel = cancel
+        cfg = CContinuousConfig(config.max_batch, config.block_size, config.exactness, config.prefill_chunk_tokens, config.max_pages,
+                                config.max_blocks_per_seq)
+        self.h = C.c_void_p()
+        check(load().b2_continuous_new(model.h, self._arr, len(requests), C.byref(cfg), C.byref(cancel.v) if cancel else None, self._cb,
+                                       None, C.byref(self.h)))
+
+    def step(self, max_steps=1):
+        done = C.c_int32(0)
+        stats = CRunStats()
+        check(load().b2_continuous_step(self.h, int(max_steps), C.byref(done), C.byref(stats)))
+        if self._err:
+            raise self._err[0]
+        return bool(done.value), {k: getattr(stats, k) for k, _ in CRunStats._fields_}
+
+    def finish(self):
+        n = len(self.requests)
+        outs = (CGenOutput * max(n, 1))()
+        bufs = []
+        for i, r in enumerate(self.requests):
+            b = np.zeros(max(r.max_new_tokens, 1), np.int32)
+            bufs.append(b)
+            outs[i].tokens = b.ctypes.data_as(C.POINTER(C.c_int32))
+            outs[i].capacity = b.size
+        stats = CRunStats()
+        check(load().b2_continuous_finish(self.h, outs, C.byref(stats)))
+        return [GenerationOutput(bufs[i][: outs[i].n_tokens].tolist(), int(outs[i].finish_reason)) for i in range(n)], \
+            {k: getattr(stats, k) for k, _ in CRunStats._fields_}
+
+    def free(self):
+        if self.h:
+            load().b2_continuous_free(self.h)
+            self.h = C.c_void_p()
