@@ -44,7 +44,10 @@ int32_t b2_version(void);
 /* ---- context and raw device memory (plumbing for callers without a CUDA runtime of their own) -- */
 int32_t b2_ctx_create(int32_t device, b2_ctx** out);
 int32_t b2_ctx_free(b2_ctx* ctx);
-int32_t b2_ctx_sync(b2_ctx* ctx);
+int32_t b2_ctx_sync(b2_ctx* ctx);   /* also reports B2_ERR_TIMEOUT raised by a bounded device-side wait */
+/* Projection path: 1 = tcgen05 / TMEM kernel for steps with more than 64 tokens (default), 0 = the
+ * warp-level mma.sync kernel for every size (kept for comparison). */
+int32_t b2_ctx_set_tensor_path(b2_ctx* ctx, int32_t use_tcgen05);
 int32_t b2_device_count(int32_t* out);
 int32_t b2_malloc(b2_ctx* ctx, size_t bytes, void** out_dev);
 int32_t b2_free(b2_ctx* ctx, void* dev);

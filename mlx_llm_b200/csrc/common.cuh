@@ -44,6 +44,11 @@ struct b2_ctx {
     // staging for the *_host entry points
     void* stage = nullptr;
     size_t stage_bytes = 0;
+    // tcgen05 GEMM: split-K partial sums and the device error word its bounded waits raise
+    float* tc_partial = nullptr;
+    size_t tc_partial_bytes = 0;
+    int* dev_err = nullptr;
+    bool use_tc = true;
     // optional per-kernel-class timing with CUDA events on the launching stream
     bool profile = false;
     std::vector<cudaEvent_t> prof_ev;

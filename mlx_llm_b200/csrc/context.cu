@@ -56,6 +56,9 @@ int32_t b2_ctx_free(b2_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->stage) cudaFree(ctx->stage);
+    if (ctx->tc_partial) cudaFree(ctx->tc_partial);
+    if (ctx->dev_err) cudaFree(ctx->dev_err);
+    for (auto e : ctx->prof_ev) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);
     cudaStreamDestroy(ctx->stream);
@@ -66,6 +69,22 @@ int32_t b2_ctx_free(b2_ctx* ctx) {
 int32_t b2_ctx_sync(b2_ctx* ctx) {
     B2_CUDA(cudaStreamSynchronize(ctx->stream));
     B2_CUDA(cudaGetLastError());
+    if (ctx->dev_err) {  // raised by a bounded device-side wait that gave up
+        int e = 0;
+        B2_CUDA(cudaMemcpyAsync(&e, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (e != 0) {
+            B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+            return b2_fail(B2_ERR_TIMEOUT, "a device-side wait (tcgen05 GEMM pipeline) timed out");
+        }
+    }
+    return B2_OK;
+}
+
+// Selects the projection path: 1 = tcgen05/TMEM for large token counts (default), 0 = warp-level mma.sync only.
+int32_t b2_ctx_set_tensor_path(b2_ctx* ctx, int32_t use_tcgen05) {
+    B2_REQUIRE(ctx, B2_ERR_MSG, "b2_ctx_set_tensor_path: null context");
+    ctx->use_tc = use_tcgen05 != 0;
     return B2_OK;
 }
 
