@@ -71,8 +71,9 @@ int32_t ensure_workspace(b2_model* m, int T, int B, int W, int P, size_t stage_i
     return B2_OK;
 }
 
-int32_t gemm(b2_model* m, const Proj& p, const uint16_t* x, int M, int ldx, uint16_t* out, int ldo, const uint16_t* res) {
+int32_t gemm(b2_model* m, const Proj& p, const uint16_t* x, int M, int ldx, uint16_t* out, int ldo, const uint16_t* res, int x_rows_cap) {
     GemmParams g{};
+    g.x_rows_cap = x_rows_cap;
     g.x = x;
     g.w = p.w;
     g.scales = p.scales;
@@ -205,7 +206,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.input_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
         b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, L.qkv, w.xn, T, H, w.qkv, qkv_w, nullptr));
+        B2_CHECK(gemm(m, L.qkv, w.xn, T, H, w.qkv, qkv_w, nullptr, w.t_cap));
         RopeKvParams rp{};
         rp.qkv = w.qkv;
         rp.ld = qkv_w;
@@ -275,15 +276,15 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
             ctx->attn_prefill_flops += pf_flops;
         }
         b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, L.o, w.attn, T, hq * hd, w.x, H, w.x));     // h = x + o_proj(attn)
+        B2_CHECK(gemm(m, L.o, w.attn, T, hq * hd, w.x, H, w.x, w.t_cap));     // h = x + o_proj(attn)
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.post_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
         b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, L.gu, w.xn, T, H, w.gu, 2 * I, nullptr));
+        B2_CHECK(gemm(m, L.gu, w.xn, T, H, w.gu, 2 * I, nullptr, w.t_cap));
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_swiglu_launch(ctx, w.gu, T, I, w.act));
         b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, L.down, w.act, T, I, w.x, H, w.x));        // x = h + down(...)
+        B2_CHECK(gemm(m, L.down, w.act, T, I, w.x, H, w.x, w.t_cap));        // x = h + down(...)
     }
     if (n_logits > 0) {
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
@@ -294,7 +295,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
         head.K = H;
         head.w = m->lm_head;
         b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, head, w.last, n_logits, H, w.logits, c.vocab_size, nullptr));
+        B2_CHECK(gemm(m, head, w.last, n_logits, H, w.logits, c.vocab_size, nullptr, w.b_cap));
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_argmax_launch(ctx, w.logits, n_logits, c.vocab_size, w.argmax));
         b2_prof_mark(ctx, B2_CLS_META);

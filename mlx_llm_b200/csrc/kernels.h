@@ -40,6 +40,7 @@ struct GemmParams {
     int group;               // 64
     int M, N, K;
     int ldx, ldo, ldres;
+    int x_rows_cap;          // rows of the x allocation (0: M); lets a TMA descriptor outlive a change of M
     int epilogue;
     uint16_t* out;           // bf16 output (EPI_BF16 / EPI_BF16_RESADD)
     const uint16_t* res;     // residual input (may alias out)
