@@ -86,6 +86,26 @@ int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host, const uin
                                   const int32_t* ctx_lens_dev, int32_t num_seqs, int32_t hq, int32_t hkv, int32_t head_dim,
                                   int32_t page_size, float scale, int32_t chunk_tokens, uint16_t* out_host);
 
+/* Decode attention that allocates nothing.  No counterpart in the reference: it exists for hosts that
+ * cannot call the device allocator when they need attention (all of HBM already handed to the KV pool,
+ * a latency-critical thread, an embedding runtime that owns the allocator).  Same arguments, meaning and
+ * results as b2_paged_attn_decode, except that there is no context: the kernels are enqueued on `stream`
+ * (a cudaStream_t, or NULL for the legacy default stream) of the CURRENT device and the call returns
+ * without synchronising; chunk_tokens == 0 means 512.
+ * The split-K scratch is a fixed 16 MiB array that lives in the library's device image, one copy per GPU.
+ * A batch whose scratch need,
+ *     ceil(max_blocks*page_size / chunk_tokens) * num_seqs * (hq*(head_dim+2)*4 + 8) + (num_seqs+2)*4  bytes,
+ * exceeds 16 MiB is rejected with B2_ERR_MSG and a text that names both sizes; nothing is launched then.
+ * (Llama-3-8B shapes, 16 K-token tables, chunk 512: up to 31 sequences; chunk 2048: up to 125.)
+ * The first call on each device looks the array's address up and sets the kernels' shared-memory limit;
+ * make that call before any stream capture begins.  All calls on one device share the array and it keeps
+ * whatever the last call left: two calls that may run at the same time (different streams, different
+ * host threads) race on it, so order them on one stream or with events. */
+int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_dev, const uint16_t* k_pool_dev, const uint16_t* v_pool_dev,
+                                    const int32_t* block_tables_dev, int32_t max_blocks, const int32_t* ctx_lens_dev,
+                                    int32_t num_seqs, int32_t hq, int32_t hkv, int32_t head_dim, int32_t page_size, float scale,
+                                    int32_t chunk_tokens, uint16_t* out_dev);
+
 /* Chunked-prefill paged attention over a ragged batch (replaces the whole-prompt prefill attention,
  * src/decode/continuous.rs:255 -> src/models/llama.rs:837-852 -> attention.rs:68-102).  Sequence i
  * owns query rows cu_seqlens[i]..cu_seqlens[i+1]; ctx_lens[i] counts the cached positions including

@@ -392,3 +392,107 @@ extern "C" int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host
     B2_CUDA(cudaStreamSynchronize(ctx->stream));
     return B2_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts of this library cannot reach cudaMalloc at the moment they need attention: a serving
+// loop that has handed every free byte of HBM to its KV pool, a thread that runs under a real-time
+// deadline, or an embedding runtime that owns the allocator and forbids foreign allocations.  For
+// them the split-K scratch (partial outputs, running max / sum, the work list) lives in the fixed
+// array below, which every GPU that loads this library carries until the process exits.
+constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB per device
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of g_decode_scratch per device.  In host code the array's name is only a handle
+// for the runtime, not an address a kernel could use, so it is resolved once per device with
+// cudaGetSymbolAddress while that device is current.
+unsigned char* g_scratch_addr[64] = {};
+bool g_static_smem_set[64][2] = {};
+}  // namespace
+
+extern "C" int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_dev, const uint16_t* k_pool_dev,
+                                               const uint16_t* v_pool_dev, const int32_t* block_tables_dev, int32_t max_blocks,
+                                               const int32_t* ctx_lens_dev, int32_t num_seqs, int32_t hq, int32_t hkv, int32_t head_dim,
+                                               int32_t page_size, float scale, int32_t chunk_tokens, uint16_t* out_dev) {
+    B2_REQUIRE(q_dev && k_pool_dev && v_pool_dev && block_tables_dev && ctx_lens_dev && out_dev, B2_ERR_MSG,
+               "b2_paged_attn_decode_static: null argument");
+    B2_REQUIRE(num_seqs >= 0 && max_blocks > 0, B2_ERR_MSG, "b2_paged_attn_decode_static: bad sizes");
+    B2_REQUIRE(page_size > 0 && page_size % 16 == 0, B2_ERR_UNSUPPORTED, "b2_paged_attn_decode_static: page_size must be a multiple of 16");
+    B2_REQUIRE(hkv > 0 && hq % hkv == 0, B2_ERR_MSG, "b2_paged_attn_decode_static: hq must be a multiple of hkv");
+    const int group = hq / hkv;
+    B2_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8, B2_ERR_UNSUPPORTED,
+               "b2_paged_attn_decode_static: q heads per kv head must be 1, 2, 4 or 8");
+    B2_REQUIRE(head_dim == 64 || head_dim == 128, B2_ERR_UNSUPPORTED, "b2_paged_attn_decode_static: head_dim must be 64 or 128");
+    if (num_seqs == 0) return B2_OK;
+    if (chunk_tokens <= 0) chunk_tokens = 512;
+    B2_REQUIRE(chunk_tokens % 16 == 0 && chunk_tokens <= 2048, B2_ERR_MSG, "b2_paged_attn_decode_static: chunk_tokens must be a multiple of 16, at most 2048");
+    const int chunk_tiles = chunk_tokens / 16, page_tiles = page_size / 16;
+    const long per_seq = ((long)max_blocks * page_tiles + chunk_tiles - 1) / chunk_tiles;
+    const long max_work = per_seq * num_seqs;
+    size_t part_bytes = (size_t)max_work * hq * (head_dim + 2) * sizeof(float);
+    part_bytes = (part_bytes + 255) & ~(size_t)255;
+    const size_t list_bytes = ((size_t)max_work * 2 + num_seqs + 2) * sizeof(int32_t);
+    B2_REQUIRE(part_bytes + list_bytes <= kStaticScratchBytes, B2_ERR_MSG,
+               "b2_paged_attn_decode_static: this batch needs " + std::to_string(part_bytes + list_bytes) +
+                   " bytes of split-K scratch, the fixed array holds " + std::to_string(kStaticScratchBytes) +
+                   " (raise chunk_tokens, lower max_blocks, or use b2_paged_attn_decode)");
+    int dev = 0;
+    B2_CUDA(cudaGetDevice(&dev));
+    B2_REQUIRE(dev >= 0 && dev < 64, B2_ERR_UNSUPPORTED, "b2_paged_attn_decode_static: device index above 63");
+    if (!g_scratch_addr[dev]) {
+        unsigned char* ptr = nullptr;
+        B2_CUDA(cudaGetSymbolAddress((void**)&ptr, g_decode_scratch));
+        g_scratch_addr[dev] = ptr;
+    }
+    const int smem = kWarps * kStages * 2 * 16 * head_dim * 2;
+    if (!g_static_smem_set[dev][head_dim == 128]) {
+        if (head_dim == 128)
+            B2_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        else
+            B2_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        g_static_smem_set[dev][head_dim == 128] = true;
+    }
+    unsigned char* scratch = g_scratch_addr[dev];
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    DecodeAttnParams p{};
+    p.q = q_dev;
+    p.k_pool = k_pool_dev;
+    p.v_pool = v_pool_dev;
+    p.block_tables = block_tables_dev;
+    p.max_blocks = max_blocks;
+    p.ctx_lens = ctx_lens_dev;
+    p.chunk_tiles = chunk_tiles;
+    p.hq = hq;
+    p.hkv = hkv;
+    p.page_tiles = page_tiles;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.part_o = reinterpret_cast<float*>(scratch);
+    p.part_ml = p.part_o + (size_t)max_work * hq * head_dim;
+    int32_t* lists = reinterpret_cast<int32_t*>(scratch + part_bytes);
+    int32_t* work_seq = lists;
+    int32_t* work_chunk = lists + max_work;
+    int32_t* seq_off = lists + 2 * max_work;
+    int32_t* n_work = seq_off + num_seqs + 1;
+    p.work_seq = work_seq;
+    p.work_chunk = work_chunk;
+    p.seq_work_off = seq_off;
+    p.n_work = n_work;
+    p.out = out_dev;
+    // Nothing in the array has to start at zero: the work list (and its count) is rewritten by the
+    // first kernel of every call, and every partial the merge reads is written by this call's decode
+    // kernel first.
+    decode_worklist_kernel<<<1, 1024, 0, st>>>(ctx_lens_dev, num_seqs, chunk_tiles, work_seq, work_chunk, seq_off, n_work);
+    const dim3 grid((unsigned)max_work, hkv);
+    int threads = group * head_dim > 1024 ? 1024 : group * head_dim;
+    if (head_dim == 128) {
+        paged_attn_decode_kernel<128><<<grid, kWarps * 32, smem, st>>>(p);
+        paged_attn_merge_kernel<128><<<dim3(num_seqs, hkv), threads, 0, st>>>(p);
+    } else {
+        paged_attn_decode_kernel<64><<<grid, kWarps * 32, smem, st>>>(p);
+        paged_attn_merge_kernel<64><<<dim3(num_seqs, hkv), threads, 0, st>>>(p);
+    }
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
