@@ -119,10 +119,14 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     sampler.start()
     barrier()
     s0 = st
+    if args.profiler_range:
+        ctx.profiler_range(True)
     t0 = time.perf_counter()
     done, s1 = engine.step(args.steps)
     ctx.sync()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    if args.profiler_range:
+        ctx.profiler_range(False)
     barrier()
     clocks = sampler.stop()
     steps = s1["steps"] - s0["steps"]
@@ -237,12 +241,16 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     l0 = ctx.launch_count()
     barrier()
     t_dev = 0.0
+    if args.profiler_range:
+        ctx.profiler_range(True)
     for _ in range(args.steps):
         ctx.flush_l2()
         ctx.timer_start()
         call()
         t_dev += ctx.timer_stop_ms()
     ctx.sync()
+    if args.profiler_range:
+        ctx.profiler_range(False)
     barrier()
     launches = ctx.launch_count() - l0
     t_dev = reduce_max(t_dev)
@@ -360,6 +368,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0 = the full 32); not a valid bench line")
     ap.add_argument("--cpu-layers", dest="cpu_layers", type=int, default=2)
     ap.add_argument("--cpu-requests", dest="cpu_requests", type=int, default=4)
+    ap.add_argument("--profiler-range", dest="profiler_range", action="store_true",
+                    help="bracket the timed region with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
 

@@ -61,6 +61,9 @@ int32_t b2_timer_start(b2_ctx* ctx);
 int32_t b2_timer_stop_ms(b2_ctx* ctx, float* ms_out);
 /* Overwrite a buffer larger than L2 so the next kernel starts cold. */
 int32_t b2_flush_l2(b2_ctx* ctx);
+/* Open (on != 0) or close the range an external profiler started with "--profile-from-start off"
+ * looks at (cudaProfilerStart / cudaProfilerStop); the stream is drained first.  No effect otherwise. */
+int32_t b2_profiler_range(b2_ctx* ctx, int32_t on);
 /* Number of this library's kernels launched on the context since creation. */
 int32_t b2_launch_count(b2_ctx* ctx, int64_t* out);
 

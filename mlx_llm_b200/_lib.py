@@ -115,6 +115,9 @@ class Context:
     def flush_l2(self):
         check(load().b2_flush_l2(self.h))
 
+    def profiler_range(self, on):
+        check(load().b2_profiler_range(self.h, C.c_int32(1 if on else 0)))
+
     def launch_count(self):
         n = C.c_int64(0)
         check(load().b2_launch_count(self.h, C.byref(n)))

@@ -2,6 +2,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <cuda_profiler_api.h>
+
 #include "common.cuh"
 
 static thread_local std::string g_last_error;
@@ -139,6 +141,16 @@ int32_t b2_flush_l2(b2_ctx* ctx) {
         ctx->flush_bytes = bytes;
     }
     B2_CUDA(cudaMemsetAsync(ctx->flush_buf, 1, ctx->flush_bytes, ctx->stream));
+    return B2_OK;
+}
+
+int32_t b2_profiler_range(b2_ctx* ctx, int32_t on) {
+    B2_REQUIRE(ctx, B2_ERR_MSG, "b2_profiler_range: null context");
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (on)
+        B2_CUDA(cudaProfilerStart());
+    else
+        B2_CUDA(cudaProfilerStop());
     return B2_OK;
 }
 
