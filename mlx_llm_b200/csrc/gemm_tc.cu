@@ -1,4 +1,4 @@
-// Large-M projection GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a only.
+// Large-M projection GEMM on the 5th-generation tensor cores, CTA-pair form (tcgen05 cta_group::2).
 //
 //   y[M, N] = x[M, K] . W[N, K]^T,   W dense bf16 or MLX-format group-64 affine Q4 / Q8
 //
@@ -7,21 +7,33 @@
 // takes over once a step carries enough tokens for the tensor pipe to be the bound (prefill chunks
 // packed with decode tokens).
 //
-// CTA tile: 128 output features (UMMA M, operand A = W) x 256 tokens (UMMA N, operand B = x) x
-// K/splits.  Both operands sit in shared memory K-major with the 128-byte swizzle of the canonical
-// UMMA layout (row = 64 bf16 = 128 B, 8-row groups 1024 B apart, 16-byte chunk c of row r stored
-// at c ^ (r & 7)).
-//   warps 0-15 weight producers: packed codes prefetched four stages ahead into registers,
-//              dequantised (w = bf16(code*scale+bias), one rounding) and stored with st.shared in
-//              the swizzled layout; then a generic->async proxy fence and an mbarrier arrive
-//   warp  16   one thread drives TMA (cp.async.bulk.tensor, 128B swizzle, no multicast): the x
-//              tile of every stage, and the W tile too when the weights are dense bf16
-//   warp  17   one thread issues tcgen05.mma (4 x K=16 per stage) into a 128-lane x 256-column
-//              f32 accumulator in TMEM and releases stages with tcgen05.commit (4-stage ring)
-//   warps 0-15 epilogue: tcgen05.ld 32 lanes x 32 columns at a time (warp w owns TMEM lanes
-//              32*(w%4).. and every 4th column block), then bf16 / residual-add / f32 split-K stores
-// Every mbarrier wait is bounded: on expiry the kernel raises an error word, drains and frees its
-// TMEM columns instead of spinning forever.
+// Why pairs.  With W as the UMMA A operand a CTA dequantises 128 feature rows per 64-wide K slab; the
+// only way to spread that cost (and the L2 -> SM traffic of the activation tile, which every feature
+// tile re-reads) over more math is more tokens per slab.  A cluster of two CTAs issues one
+// 256-feature x N-token MMA whose B operand is split between the two CTAs' shared memories, so each CTA
+// holds 128 features x up to 512 tokens of f32 accumulator (all 512 TMEM columns) while loading only
+// half of the tokens: one dequantised weight element feeds up to 512 MACs, and the activation bytes
+// per MAC are a quarter of a 128 x 256 single-CTA tile.
+//
+// Work split.  The output is cut along (feature pair-tile, token) into one contiguous run of columns
+// per CTA pair ("pieces" of at most 512 tokens of one 256-feature tile).  Runs are equal to within one
+// column, so every SM finishes together whatever N and M are, and no piece shares an output element
+// with another: there is no split-K, no partial sums and no reduction pass.
+//
+// Roles per CTA (576 threads):
+//   warps 0-15  weight producers: packed codes prefetched into registers, dequantised
+//               (w = bf16(code*scale+bias), one rounding), stored in the 128B-swizzled K-major UMMA
+//               layout, generic->async proxy fence, one mbarrier arrive per warp on the LEADER CTA's
+//               "full" barrier (a remote arrive from the second CTA); afterwards the epilogue:
+//               tcgen05.ld 32 lanes x 32 columns, bf16 / residual-add / f32 stores
+//   warp 16     one thread drives TMA (cp.async.bulk.tensor, cta_group::2 form, no multicast): this
+//               CTA's half of the token rows of every stage (32-row boxes), plus the W tile when the
+//               weights are dense bf16; completion bytes land on the leader's "full" barrier
+//   warp 17     leader CTA only: one thread issues tcgen05.mma.cta_group::2 (two instructions per
+//               K=16 step when the piece is wider than 256 tokens) and releases stages / publishes
+//               the accumulator with tcgen05.commit multicast to both CTAs' barriers
+// Every mbarrier wait is bounded: on expiry the kernel raises an error word, stops producing and
+// falls through to the common exit, where the TMEM columns are freed.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -29,48 +41,83 @@
 
 namespace {
 
-constexpr int TM = 128;         // features per CTA (UMMA M)
-constexpr int TN = 256;         // tokens per CTA (UMMA N)
-constexpr int TK = 64;          // K per stage (one 128-byte swizzled row, one quant group)
-constexpr int STAGES = 4;
-constexpr int A_BYTES = TM * TK * 2, B_BYTES = TN * TK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TM = 128;          // features per CTA (half of the UMMA M = 256)
+constexpr int PAIR_F = 2 * TM;   // features per CTA pair
+constexpr int TN_MAX = 512;      // tokens per piece (all TMEM columns)
+constexpr int TK = 64;           // K per slab (one 128-byte swizzled row, one quant group)
+constexpr int GROUPS = 4;        // producer groups (4 warps each); group g dequantises every 4th K slab
+constexpr int MAX_STAGES = 6;
+constexpr int RING_BYTES = 192 * 1024;  // 4 stages of (A + 2 units) for two-block pieces, 6 of (A + 1 unit) otherwise
+constexpr int BOX_BIG = 128, BOX_SMALL = 32;  // token rows per TMA box (one big box, or up to two small ones)
+constexpr int A_BYTES = TM * TK * 2, UNIT_BYTES = 128 * TK * 2;  // unit: 128 token rows x 64 K, one MMA instruction's B half
 constexpr int kProducerWarps = 16, kProducerThreads = kProducerWarps * 32;
 constexpr int kTmaWarp = kProducerWarps, kMmaWarp = kProducerWarps + 1, kThreads = kProducerThreads + 64;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t kSpinLimit = 64;  // try_wait attempts between two looks at the clock
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count));
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+__device__ __forceinline__ void mbar_arrive_local(uint32_t addr) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(addr) : "memory");
 }
-// Bounded wait; returns false when the limit ran out.
+// arrive on a barrier anywhere in the cluster (shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(addr), "r"(bytes) : "memory");
+}
+// Bounded wait on a barrier of this CTA (cluster-scope acquire: the arrivals come from both CTAs and
+// from the tensor core's commit); false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; i++) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (ok) return true;
+    long long start = 0;
+    while (true) {
+        for (uint32_t i = 0; i < kSpinLimit; i++) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}\n"
+                : "=r"(ok)
+                : "r"(addr), "r"(parity)
+                : "memory");
+            if (ok) return true;
+        }
+        const long long now = clock64();
+        if (start == 0) start = now;
+        if (now - start > 4000000000ll) return false;  // ~2 s: give up instead of hanging
     }
-    return false;
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t mbar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+// arrive (once the MMAs issued so far have completed) on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void tc_commit_pair(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(mbar),
+                 "h"((uint16_t)3)
+                 : "memory");
 }
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
         "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -86,13 +133,25 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+// 2-D tiled TMA load, CTA-pair form without multicast: the box lands in THIS CTA's shared memory, the
+// completion bytes on `mbar`, a shared::cluster address that may name the peer CTA's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(mbar)
+        : "memory");
+}
 
 // K-major, 128-byte swizzle, rows of 128 B, 8-row groups 1024 B apart (SBO = 64 x 16 B), LBO unused (1),
 // descriptor version 1 (bit 46), layout type 2 = SWIZZLE_128B (bits 61-63).
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-// instruction descriptor: f32 accumulate (bit 4), bf16 x bf16 (bits 7, 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+// instruction descriptor: f32 accumulate (bit 4), bf16 x bf16 (bits 7, 10), both K-major, N >> 3 at bit 17,
+// M >> 4 at bit 24 (M = 256 across the pair)
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(PAIR_F >> 4) << 24);
+}
 
 __device__ __forceinline__ uint32_t sub_bf2(uint32_t a, uint32_t b) {
     uint32_t d;
@@ -132,226 +191,357 @@ __device__ __forceinline__ void dequant4_q8(uint32_t w, float s, float b, uint32
     out[1] = pack_bf2(__fmaf_rn(c2, s, b), __fmaf_rn(c3, s, b));
 }
 
-struct TcExtra {
-    int splits;
-    int tile_tokens;  // tokens per CTA (UMMA N), a multiple of 16, <= 256
-    float* partial;   // [splits, M, N] f32 when splits > 1
-    int* err;         // device error word
+// The output is cut into blocks of 256 tokens of one 256-feature tile (block index = tile * blocks_per_tile
+// + token block).  A tcgen05.mma of the pair costs the same for any N up to 256, so a block is the unit
+// of cost; every pair gets a contiguous run of blocks, equal to within one.
+struct PairPlan {
+    int n_pairs;          // CTA pairs launched
+    int blocks_per_tile;  // ceil(M / 256)
+    int total_blocks;     // ceil(N / 256) * blocks_per_tile
+    int splits;           // K ranges per block (> 1 only when the blocks alone cannot occupy the pairs)
+    float* partial;       // [splits, M, N] f32 partial sums when splits > 1
+    int* err;             // device error word
 };
 
-__device__ __forceinline__ bool mbar_wait_timed(uint32_t addr, uint32_t parity) {
-    const long long start = clock64();
-    while (true) {
-        if (mbar_wait(addr, parity)) return true;
-        if (clock64() - start > 4000000000ll) return false;  // ~2 s: give up instead of hanging
+// One piece: one or two consecutive token blocks of 256-feature tile `fp`.
+struct Piece {
+    int fp, t0, cnt;  // cnt tokens starting at t0
+    int n0, n1;       // UMMA N of the two instructions (n1 == 0 for a single block); multiples of 16
+    int blocks;       // 1 or 2
+    int k0, nk;       // first K slab and number of K slabs
+    int split;        // index of the K range
+};
+// Ring geometry of a piece: two-block pieces use 4 stages of 48 KB (A slab + two B units), one-block pieces
+// 6 stages of 32 KB; both fill the same 192 KB.
+__device__ __forceinline__ int ring_stages(const Piece& pc) { return pc.blocks == 2 ? 4 : 6; }
+__device__ __forceinline__ uint32_t ring_stage_bytes(const Piece& pc) { return pc.blocks == 2 ? 48u * 1024u : 32u * 1024u; }
+// Phase bookkeeping: bit s of `par` is the parity of the next use of stage s.  After a piece with KT slabs on
+// NS stages, stage s has been used ceil((KT - s) / NS) more times.
+__device__ __forceinline__ uint32_t ring_advance(uint32_t par, int KT, int NS) {
+    for (int st = 0; st < NS; st++) {
+        const int uses = KT > st ? (KT - st + NS - 1) / NS : 0;
+        par ^= (uint32_t)(uses & 1) << st;
     }
+    return par;
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(addr), "r"(bytes) : "memory");
-}
-// 2-D tiled TMA load (no multicast): box lands at `dst`, completion bytes on `mbar`.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
-        "l"(map), "r"(x), "r"(y), "r"(mbar)
-        : "memory");
+// Work units are numbered block-major: unit = block * splits + K range.  Without split-K two consecutive
+// token blocks of a tile are taken together when the pair owns both.
+__device__ __forceinline__ Piece piece_at(int unit, int unit_end, int bpt, int M, int KT, int splits) {
+    Piece pc;
+    const int blk = unit / splits;
+    pc.split = unit - blk * splits;
+    pc.k0 = (int)((long)pc.split * KT / splits);
+    pc.nk = (int)((long)(pc.split + 1) * KT / splits) - pc.k0;
+    pc.fp = blk / bpt;
+    const int tb = blk % bpt;
+    pc.blocks = (splits == 1 && tb + 1 < bpt && unit + 1 < unit_end) ? 2 : 1;
+    pc.t0 = tb * 256;
+    int cnt = M - pc.t0;
+    if (cnt > 256 * pc.blocks) cnt = 256 * pc.blocks;
+    pc.cnt = cnt;
+    const int padded = (cnt + 15) & ~15;
+    pc.n0 = padded < 256 ? padded : 256;
+    pc.n1 = padded - pc.n0;
+    return pc;
 }
 
 template <int WK, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
-    gemm_tc_kernel(const GemmParams p, const TcExtra ex, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    gemm_tc_pair_kernel(const GemmParams p, const PairPlan plan, const __grid_constant__ CUtensorMap map_x,
+                        const __grid_constant__ CUtensorMap map_x_small, const __grid_constant__ CUtensorMap map_w) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t bar = base + STAGES * STAGE_BYTES;
-    auto full = [&](int s) { return bar + 8u * s; };
-    auto empty = [&](int s) { return bar + 8u * (STAGES + s); };
-    const uint32_t accum = bar + 8u * (2 * STAGES);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (accum + 8 - raw));
+    const uint32_t base = (raw + 1023u) & ~1023u;  // operand ring: stage s at base + s * stage bytes, A slab first
+    const uint32_t bar = base + RING_BYTES;
+    auto full = [&](int s) { return bar + 8u * s; };                  // used in the leader CTA only
+    auto empty = [&](int s) { return bar + 8u * (MAX_STAGES + s); };  // one per CTA, armed by the leader's commit
+    const uint32_t accum_full = bar + 8u * (2 * MAX_STAGES);          // one per CTA
+    const uint32_t accum_empty = accum_full + 8u;                     // leader only
+    const uint32_t slot_addr = accum_empty + 8u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tn = ex.tile_tokens;
-    const int n0 = blockIdx.x * TM, t0 = blockIdx.y * tn, split = blockIdx.z;
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
     const int M = p.M, N = p.N, K = p.K;
     const int KT = K / TK;
-    const int kb_begin = (int)((long)split * KT / ex.splits), kb_end = (int)((long)(split + 1) * KT / ex.splits);
-    const int n_it = kb_end - kb_begin;
-    // arrivals per stage: every dequantising thread, plus the TMA thread's expect_tx arrive
-    constexpr uint32_t kFullCount = (WK != 0 ? kProducerThreads : 0) + 1;
+    const int bpt = plan.blocks_per_tile;
+    const int splits = plan.splits;
+    const int total_units = plan.total_blocks * splits;
+    const int blk_begin = (int)((long)pair * total_units / plan.n_pairs);  // first work unit of this pair
+    const int blk_end = (int)((long)(pair + 1) * total_units / plan.n_pairs);
+    // arrivals per stage on the leader's "full" barrier: the four warps that fill the A slab in each CTA
+    // (quantised weights only) plus the leader's TMA thread (arrive.expect_tx for both CTAs' bytes)
+    constexpr uint32_t kFullCount = (WK != 0 ? 2 * (kProducerWarps / GROUPS) : 0) + 1;
+    const uint32_t leader_accum_empty = map_to_cta(accum_empty, 0);
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < MAX_STAGES; s++) {
             mbar_init(full(s), kFullCount);
             mbar_init(empty(s), 1);
         }
-        mbar_init(accum, 1);
+        mbar_init(accum_full, 1);
+        mbar_init(accum_empty, 2 * kProducerWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == kMmaWarp) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(accum + 8), "r"(TN) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot_addr), "r"(TN_MAX) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anyone arrives remotely
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < kProducerWarps) {
-        if (WK != 0) {
-            // ---------------- weight producers: thread = (feature row, quarter of the 64-wide K slab) ----------------
-            constexpr int PREFETCH = 4;
-            const int row = tid >> 2, quarter = tid & 3;
-            const int gn = n0 + row;
-            const int groups = K / 64;
-            const uint32_t* wq = reinterpret_cast<const uint32_t*>(p.w) + (size_t)gn * (K * WK / 32);
-            uint4 qa[PREFETCH];
-            uint32_t sb[PREFETCH];
-            auto load_codes = [&](int it, uint4& a, uint32_t& scale_bias) {
-                const int kb = kb_begin + it;
-                if (WK == 4) {  // 16 codes = 8 bytes
-                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(wq + kb * 8 + quarter * 2));
-                    a = make_uint4(v.x, v.y, 0, 0);
-                } else {        // 16 codes = 16 bytes
-                    a = __ldg(reinterpret_cast<const uint4*>(wq + kb * 16 + quarter * 4));
-                }
-                scale_bias = (uint32_t)__ldg(p.scales + (size_t)gn * groups + kb) | ((uint32_t)__ldg(p.biases + (size_t)gn * groups + kb) << 16);
-            };
+        // Four groups of four warps; group g dequantises every 4th K slab, one thread per feature row (64
+        // codes, one scale and one bias per slab).  While one group waits for its slot or for its barrier
+        // arrive to travel to the leader CTA, the other three keep dequantising.
+        static_assert(kProducerWarps == 4 * GROUPS, "four warps per producer group");
+        const int grp = warp >> 2, row = tid & 127;
+        const int groups = K / 64;
+        const int lane_grp = warp & 3, col_grp = warp >> 2;
+        const uint32_t leader_full0 = leader ? full(0) : map_to_cta(full(0), 0);
+        uint32_t it_global = 0;  // K slabs issued before this piece (all roles count the same)
+        uint32_t par = 0;        // per-stage phase parities (all roles keep the same)
+        uint32_t n_piece = 0;
+        bool alive = true;
+        for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
+            const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
+            blk += pc.blocks;
+            const int NS = ring_stages(pc);
+            const uint32_t SB = ring_stage_bytes(pc);
+            if (WK != 0) {
+                const int gn = pc.fp * PAIR_F + (int)rank * TM + row;
+                const bool row_ok = gn < N;  // rows past N contribute exact zeros
+                const uint4* wq = reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p.w) + (size_t)(row_ok ? gn : 0) * (K * WK / 32));
+                const uint16_t* sc_row = p.scales + (size_t)(row_ok ? gn : 0) * groups;
+                const uint16_t* bi_row = p.biases + (size_t)(row_ok ? gn : 0) * groups;
+                constexpr int NQ = WK == 4 ? 2 : 4;  // 16-byte loads per 64 codes
+                uint4 q[NQ];
+                uint32_t sb = 0;
+                auto load_codes = [&](int kb) {
 #pragma unroll
-            for (int j = 0; j < PREFETCH; j++) {
-                qa[j] = make_uint4(0, 0, 0, 0);
-                sb[j] = 0;
-                if (j < n_it) load_codes(j, qa[j], sb[j]);
-            }
-            bool alive = true;
-            for (int it0 = 0; it0 < n_it && alive; it0 += PREFETCH) {
+                    for (int i = 0; i < NQ; i++) q[i] = row_ok ? __ldg(wq + kb * NQ + i) : make_uint4(0, 0, 0, 0);
+                    sb = row_ok ? ((uint32_t)__ldg(sc_row + kb) | ((uint32_t)__ldg(bi_row + kb) << 16)) : 0u;
+                };
+                // first K slab of this piece that belongs to this group
+                int kb = (int)((grp + GROUPS - (it_global % GROUPS)) % GROUPS);  // slab index within the piece
+                if (kb < pc.nk) load_codes(pc.k0 + kb);
+                const uint32_t sw = (uint32_t)(row & 7);
+                for (; kb < pc.nk; kb += GROUPS) {
+                    const int st = kb % NS;
+                    const uint32_t ph = ((par >> st) ^ (uint32_t)(kb / NS)) & 1u;
+                    const uint32_t sA = base + st * SB + row * 128;
+                    uint4 cd[NQ];
 #pragma unroll
-                for (int jj = 0; jj < PREFETCH; jj++) {
-                    const int it = it0 + jj;
-                    if (it >= n_it || !alive) break;
-                    const int s = it % STAGES;
-                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                    const uint32_t sA = base + s * STAGE_BYTES + row * 128;
-                    const uint4 c = qa[jj];
-                    const uint32_t csc = sb[jj] & 0xffffu, cbi = sb[jj] >> 16;
-                    if (it + PREFETCH < n_it) load_codes(it + PREFETCH, qa[jj], sb[jj]);
-                    if (!mbar_wait_timed(empty(s), ph ^ 1u)) {
+                    for (int i = 0; i < NQ; i++) cd[i] = q[i];
+                    const uint32_t csc = sb & 0xffffu, cbi = sb >> 16;
+                    if (kb + GROUPS < pc.nk) load_codes(pc.k0 + kb + GROUPS);
+                    // the verdict is taken warp-wide so that no lane leaves the others at the __syncwarp below
+                    if (!__all_sync(0xffffffffu, mbar_wait(empty(st), ph ^ 1u))) {
                         alive = false;
                         break;
                     }
                     if (WK == 4) {
                         const uint32_t s2 = csc * 0x10001u, b2 = cbi * 0x10001u;
-                        uint32_t o[4];
-                        dequant8_q4(c.x, s2, b2, o);
-                        sts128(sA + (((quarter * 2) ^ (row & 7)) << 4), o[0], o[1], o[2], o[3]);
-                        dequant8_q4(c.y, s2, b2, o);
-                        sts128(sA + (((quarter * 2 + 1) ^ (row & 7)) << 4), o[0], o[1], o[2], o[3]);
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            const uint32_t w4[4] = {cd[i].x, cd[i].y, cd[i].z, cd[i].w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint32_t o[4];
+                                dequant8_q4(w4[j], s2, b2, o);
+                                sts128(sA + ((((uint32_t)(i * 4 + j)) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+                            }
+                        }
                     } else {
                         const float sf = __uint_as_float(csc << 16), bf = __uint_as_float(cbi << 16);
-                        uint32_t lo[2], hi[2];
-                        dequant4_q8(c.x, sf, bf, lo);
-                        dequant4_q8(c.y, sf, bf, hi);
-                        sts128(sA + (((quarter * 2) ^ (row & 7)) << 4), lo[0], lo[1], hi[0], hi[1]);
-                        dequant4_q8(c.z, sf, bf, lo);
-                        dequant4_q8(c.w, sf, bf, hi);
-                        sts128(sA + (((quarter * 2 + 1) ^ (row & 7)) << 4), lo[0], lo[1], hi[0], hi[1]);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            uint32_t lo[2], hi[2];
+                            dequant4_q8(cd[i].x, sf, bf, lo);
+                            dequant4_q8(cd[i].y, sf, bf, hi);
+                            sts128(sA + ((((uint32_t)(i * 2)) ^ sw) << 4), lo[0], lo[1], hi[0], hi[1]);
+                            dequant4_q8(cd[i].z, sf, bf, lo);
+                            dequant4_q8(cd[i].w, sf, bf, hi);
+                            sts128(sA + ((((uint32_t)(i * 2 + 1)) ^ sw) << 4), lo[0], lo[1], hi[0], hi[1]);
+                        }
                     }
                     fence_proxy_async();
-                    mbar_arrive(full(s));
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (leader)
+                            mbar_arrive_local(leader_full0 + 8u * st);
+                        else
+                            mbar_arrive_cluster(leader_full0 + 8u * st);
+                    }
                 }
+            }
+            it_global += (uint32_t)pc.nk;
+            par = ring_advance(par, pc.nk, NS);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            // ---------------- epilogue of this piece ----------------
+            bool ok = mbar_wait(accum_full, n_piece & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            const int f = pc.fp * PAIR_F + (int)rank * TM + lane_grp * 32 + lane;
+#pragma unroll 1
+            for (int j = col_grp; j * 32 < pc.cnt; j += kProducerWarps / 4) {
+                uint32_t v[32];
+                tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(j * 32), v);
+                if (f < N) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        if (j * 32 + i >= pc.cnt) break;
+                        const int t = pc.t0 + j * 32 + i;
+                        const float a = __uint_as_float(v[i]);
+                        if (splits > 1) {
+                            plan.partial[((size_t)pc.split * M + t) * N + f] = a;
+                        } else if (EPI == EPI_F32) {
+                            p.out_f32[(size_t)t * p.ldo + f] = a;
+                        } else if (EPI == EPI_BF16) {
+                            p.out[(size_t)t * p.ldo + f] = f2bf(a);
+                        } else {
+                            p.out[(size_t)t * p.ldo + f] = f2bf(bf2f(p.res[(size_t)t * p.ldres + f]) + rbf(a));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_accum_empty);  // this warp's TMEM reads of the piece are done
+        }
+        if (!alive) {
+            *abort_flag = 1;
+            atomicExch(plan.err, 1);
+        }
+    } else if (warp == kTmaWarp) {
+        if (lane == 0) {
+            uint32_t par = 0, n_piece = 0;
+            int prev_blocks = 0;
+            bool alive = true;
+            const uint32_t leader_full0 = map_to_cta(full(0), 0);
+            for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
+                const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
+                blk += pc.blocks;
+                const int NS = ring_stages(pc);
+                const uint32_t SB = ring_stage_bytes(pc);
+                if (prev_blocks != 0 && prev_blocks != pc.blocks) {
+                    // the ring is carved differently for this piece: every MMA of the previous one must be done
+                    if (!mbar_wait(accum_full, (n_piece - 1) & 1u)) {
+                        alive = false;
+                        break;
+                    }
+                }
+                prev_blocks = pc.blocks;
+                const int h0 = pc.n0 >> 1, h1 = pc.n1 >> 1;  // token rows this CTA holds per MMA instruction
+                // one 128-row box, or one or two 32-row boxes when the CTA holds at most 64 rows
+                const bool big0 = h0 > 2 * BOX_SMALL, big1 = h1 > 2 * BOX_SMALL;
+                const int nb0 = big0 ? 1 : (h0 + BOX_SMALL - 1) / BOX_SMALL, nb1 = big1 ? 1 : (h1 + BOX_SMALL - 1) / BOX_SMALL;
+                const uint32_t bb0 = (uint32_t)(big0 ? BOX_BIG : BOX_SMALL) * 128u, bb1 = (uint32_t)(big1 ? BOX_BIG : BOX_SMALL) * 128u;
+                const CUtensorMap* m0 = big0 ? &map_x : &map_x_small;
+                const CUtensorMap* m1 = big1 ? &map_x : &map_x_small;
+                const int y0 = pc.t0 + (int)rank * h0, y1 = pc.t0 + 256 + (int)rank * h1;
+                const uint32_t tx = 2u * ((uint32_t)nb0 * bb0 + (uint32_t)nb1 * bb1 + (WK == 0 ? (uint32_t)A_BYTES : 0u));
+                for (int kb = 0; kb < pc.nk; kb++) {
+                    const int st = kb % NS;
+                    const uint32_t ph = ((par >> st) ^ (uint32_t)(kb / NS)) & 1u;
+                    if (!mbar_wait(empty(st), ph ^ 1u)) {
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t sA = base + st * SB, sB = sA + A_BYTES;
+                    const uint32_t fb = leader_full0 + 8u * st;
+                    if (leader) mbar_expect_tx(full(st), tx);
+                    const int kx = (pc.k0 + kb) * TK;
+                    for (int b = 0; b < nb0; b++) tma_load_2d_pair(sB + b * bb0, m0, kx, y0 + b * BOX_SMALL, fb);
+                    for (int b = 0; b < nb1; b++) tma_load_2d_pair(sB + UNIT_BYTES + b * bb1, m1, kx, y1 + b * BOX_SMALL, fb);
+                    if (WK == 0) tma_load_2d_pair(sA, &map_w, kx, pc.fp * PAIR_F + (int)rank * TM, fb);
+                }
+                par = ring_advance(par, pc.nk, NS);
             }
             if (!alive) {
                 *abort_flag = 1;
-                atomicExch(ex.err, 1);
-            }
-        }
-    } else if (warp == kTmaWarp) {
-        // ---------------- TMA: x tile (and the W tile of dense weights) ----------------
-        if (lane == 0) {
-            for (int it = 0; it < n_it; it++) {
-                const int s = it % STAGES;
-                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (!mbar_wait_timed(empty(s), ph ^ 1u)) {
-                    *abort_flag = 1;
-                    atomicExch(ex.err, 1);
-                    break;
-                }
-                const uint32_t sA = base + s * STAGE_BYTES, sB = sA + A_BYTES;
-                const int kx = (kb_begin + it) * TK;
-                mbar_expect_tx(full(s), (uint32_t)(B_BYTES + (WK == 0 ? A_BYTES : 0)));
-                tma_load_2d(sB, &map_x, kx, t0, full(s));
-                if (WK == 0) tma_load_2d(sA, &map_w, kx, n0, full(s));
+                atomicExch(plan.err, 1);
             }
         }
         __syncwarp();
     } else {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            for (int it = 0; it < n_it; it++) {
-                const int s = it % STAGES;
-                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (!mbar_wait_timed(full(s), ph)) {
-                    *abort_flag = 1;
-                    atomicExch(ex.err, 1);
-                    break;
+        // ---------------- MMA issuer (leader CTA) ----------------
+        if (leader && lane == 0) {
+            uint32_t par = 0, n_piece = 0;
+            bool alive = true;
+            for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
+                const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
+                blk += pc.blocks;
+                const int NS = ring_stages(pc);
+                const uint32_t SB = ring_stage_bytes(pc);
+                if (n_piece > 0) {
+                    // both CTAs' epilogue warps have drained the previous accumulator
+                    if (!mbar_wait(accum_empty, (n_piece - 1) & 1u)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
                 }
-                tc_fence_after();
-                const uint32_t sA = base + s * STAGE_BYTES, sB = sA + A_BYTES;
+                const uint32_t id0 = umma_idesc(pc.n0), id1 = umma_idesc(pc.n1 > 0 ? pc.n1 : 16);
+                const bool two = pc.n1 > 0;
+                // descriptors advance by whole stages (SB >> 4) and by 32 bytes (2) per K=16 step; the stage
+                // index and its phase are carried, not recomputed, to keep this thread's instruction count low
+                const uint64_t dA0 = umma_desc(base), dB0 = umma_desc(base + A_BYTES), dB1 = umma_desc(base + A_BYTES + UNIT_BYTES);
+                const uint64_t dstep = (uint64_t)(SB >> 4);
+                int st = 0;
+                uint32_t flip = 0;  // toggles each time the stage index wraps
+                uint64_t dA = dA0, dB = dB0, dC = dB1;
+                for (int kb = 0; kb < pc.nk; kb++) {
+                    const uint32_t ph = ((par >> st) ^ flip) & 1u;
+                    if (!mbar_wait(full(st), ph)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < TK / 16; k++)
-                    tc_mma(tmem_base, umma_desc(sA + k * 32), umma_desc(sB + k * 32), idesc, (it > 0 || k > 0) ? 1u : 0u);
-                tc_commit(empty(s));
+                    for (int k = 0; k < TK / 16; k++) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        tc_mma_pair(tmem_base, dA + 2 * k, dB + 2 * k, id0, acc);
+                        if (two) tc_mma_pair(tmem_base + 256u, dA + 2 * k, dC + 2 * k, id1, acc);
+                    }
+                    tc_commit_pair(empty(st));
+                    st++;
+                    dA += dstep, dB += dstep, dC += dstep;
+                    if (st == NS) st = 0, flip ^= 1u, dA = dA0, dB = dB0, dC = dB1;
+                }
+                par = ring_advance(par, pc.nk, NS);
+                if (alive) tc_commit_pair(accum_full);
             }
-            tc_commit(accum);
+            if (!alive) {
+                *abort_flag = 1;
+                atomicExch(plan.err, 1);
+            }
         }
         __syncwarp();
     }
 
-    if (warp < kProducerWarps) {
-        // ---------------- epilogue ----------------
-        bool ok = mbar_wait_timed(accum, 0);
-        if (!ok) {
-            *abort_flag = 1;
-            atomicExch(ex.err, 1);
-        }
-        tc_fence_after();
-        ok = ok && (*abort_flag == 0) && n_it > 0;
-        const int lane_grp = warp & 3, col_grp = warp >> 2;
-        const int f = n0 + lane_grp * 32 + lane;
-        if (ok) {
-#pragma unroll 1
-            for (int j = col_grp; j * 32 < tn; j += kProducerWarps / 4) {
-                if (t0 + j * 32 >= M) break;
-                uint32_t v[32];
-                tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(j * 32), v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int t = t0 + j * 32 + i;
-                    if (t >= M || j * 32 + i >= tn) break;
-                    const float a = __uint_as_float(v[i]);
-                    if (ex.splits > 1) {
-                        ex.partial[((size_t)split * M + t) * N + f] = a;
-                    } else if (EPI == EPI_F32) {
-                        p.out_f32[(size_t)t * p.ldo + f] = a;
-                    } else if (EPI == EPI_BF16) {
-                        p.out[(size_t)t * p.ldo + f] = f2bf(a);
-                    } else {
-                        p.out[(size_t)t * p.ldo + f] = f2bf(bf2f(p.res[(size_t)t * p.ldres + f]) + rbf(a));
-                    }
-                }
-            }
-        }
-    }
+    // common exit: nobody leaves while the peer may still signal this CTA's barriers or read its operands
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();
     if (warp == kMmaWarp) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TN_MAX) : "memory");
     }
 }
 
-// out = epilogue(sum over splits of partial)
+// out = epilogue(sum over K ranges of partial)
 template <int EPI>
 __global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict__ partial, int splits) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -415,68 +605,27 @@ int32_t get_map(b2_ctx* ctx, const void* ptr, uint64_t rows, uint64_t k, uint64_
 }
 
 template <int WK, int EPI>
-int32_t launch_tc(b2_ctx* ctx, const GemmParams& p, int splits, float* partial, int* err) {
-    B2_SMEM_ONCE(ctx, (gemm_tc_kernel<WK, EPI>), SMEM_BYTES);
-    // token tiles of equal size (a multiple of 16, at most 256) so no CTA runs a mostly empty tile
-    const int n_tiles = (p.M + TN - 1) / TN;
-    const int tile_tokens = (((p.M + n_tiles - 1) / n_tiles) + 15) / 16 * 16;
-    TcExtra ex{splits, tile_tokens, partial, err};
-    const CUtensorMap *mx = nullptr, *mw = nullptr;
-    const uint64_t x_rows = p.x_rows_cap > p.M ? (uint64_t)p.x_rows_cap : (uint64_t)p.M;
-    B2_CHECK(get_map(ctx, p.x, x_rows, (uint64_t)p.K, (uint64_t)p.ldx, TN, &mx));
-    CUtensorMap map_x = *mx, map_w = *mx;
-    if (WK == 0) {
-        B2_CHECK(get_map(ctx, p.w, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, TM, &mw));
-        map_w = *mw;
-    }
-    dim3 grid(p.N / TM, n_tiles, splits);
-    gemm_tc_kernel<WK, EPI><<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, map_x, map_w);
-    B2_LAUNCHED(ctx);
-    if (splits > 1) {
-        const size_t total = (size_t)p.M * p.N;
-        splitk_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, partial, splits);
-        B2_LAUNCHED(ctx);
-    }
-    B2_CUDA(cudaGetLastError());
-    return B2_OK;
-}
-
-template <int WK>
-int32_t dispatch_tc(b2_ctx* ctx, const GemmParams& p, int splits, float* partial, int* err) {
-    switch (p.epilogue) {
-        case EPI_BF16: return launch_tc<WK, EPI_BF16>(ctx, p, splits, partial, err);
-        case EPI_BF16_RESADD: return launch_tc<WK, EPI_BF16_RESADD>(ctx, p, splits, partial, err);
-        case EPI_F32: return launch_tc<WK, EPI_F32>(ctx, p, splits, partial, err);
-    }
-    return b2_fail(B2_ERR_MSG, "gemm: bad epilogue");
-}
-
-}  // namespace
-
-bool b2_gemm_tc_eligible(const GemmParams& p) {
-    return p.M > 64 && p.N % TM == 0 && p.K % TK == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 &&
-           (p.bits == 4 || p.bits == 8 || (p.bits == 0 && ((uintptr_t)p.w & 15) == 0));
-}
-
-int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p) {
-    // Split K only when the (feature, token) tiles cannot even fill one wave of SMs (o_proj / down_proj
-    // at a few hundred tokens): the f32 partial sums cost a write and a read of splits*M*N*4 bytes, which
-    // wipes out the gain as soon as the plain grid already covers the machine.
-    const int tiles = (p.N / TM) * ((p.M + TN - 1) / TN);
+int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
+    B2_SMEM_ONCE(ctx, (gemm_tc_pair_kernel<WK, EPI>), SMEM_BYTES);
+    PairPlan plan{};
+    plan.blocks_per_tile = (p.M + 255) / 256;
+    plan.total_blocks = ((p.N + PAIR_F - 1) / PAIR_F) * plan.blocks_per_tile;
+    const int max_pairs = ctx->sm_count / 2;
+    // Split K only when the blocks cannot occupy the pairs (down_proj at a few hundred tokens).  Cost model in K
+    // slabs, fitted to measurements: a piece costs its slabs plus about 16 (prologue, first fill, epilogue), the
+    // reduction pass about 20.
     const int KT = p.K / TK;
     int best = 1;
-    if (tiles * 10 <= ctx->sm_count * 7) {
-        double best_eff = (double)tiles / ctx->sm_count;
-        for (int s = 2; s <= 4 && s * 16 <= KT; s++) {
-            const int ctas = tiles * s;
-            const double eff = (double)ctas / (((ctas + ctx->sm_count - 1) / ctx->sm_count) * ctx->sm_count);
-            if (eff > best_eff + 0.1) {
-                best_eff = eff;
-                best = s;
-            }
+    if (plan.total_blocks * 10 <= max_pairs * 7) {
+        long best_cost = (long)((plan.total_blocks + max_pairs - 1) / max_pairs) * (KT + 16);
+        for (int sp = 2; sp <= 4 && sp * 16 <= KT; sp++) {
+            const int units = plan.total_blocks * sp;
+            const long cost = (long)((units + max_pairs - 1) / max_pairs) * (KT / sp + 16) + 20;
+            if (cost < best_cost) best_cost = cost, best = sp;
         }
     }
-    float* partial = nullptr;
+    plan.splits = best;
+    plan.partial = nullptr;
     if (best > 1) {
         const size_t bytes = (size_t)best * p.M * p.N * sizeof(float);
         if (bytes > ctx->tc_partial_bytes) {
@@ -486,13 +635,55 @@ int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p) {
             B2_CUDA(cudaMalloc((void**)&ctx->tc_partial, bytes + (bytes >> 2)));
             ctx->tc_partial_bytes = bytes + (bytes >> 2);
         }
-        partial = ctx->tc_partial;
+        plan.partial = ctx->tc_partial;
     }
+    const int units = plan.total_blocks * best;
+    plan.n_pairs = units < max_pairs ? units : max_pairs;
+    plan.err = err;
+    const CUtensorMap *mx = nullptr, *ms = nullptr, *mw = nullptr;
+    const uint64_t x_rows = p.x_rows_cap > p.M ? (uint64_t)p.x_rows_cap : (uint64_t)p.M;
+    B2_CHECK(get_map(ctx, p.x, x_rows, (uint64_t)p.K, (uint64_t)p.ldx, BOX_BIG, &mx));
+    CUtensorMap map_x = *mx;  // copied before the next lookup may move the cache
+    B2_CHECK(get_map(ctx, p.x, x_rows, (uint64_t)p.K, (uint64_t)p.ldx, BOX_SMALL, &ms));
+    CUtensorMap map_s = *ms, map_w = *ms;
+    if (WK == 0) {
+        B2_CHECK(get_map(ctx, p.w, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, TM, &mw));
+        map_w = *mw;
+    }
+    gemm_tc_pair_kernel<WK, EPI><<<2 * plan.n_pairs, kThreads, SMEM_BYTES, ctx->stream>>>(p, plan, map_x, map_s, map_w);
+    B2_LAUNCHED(ctx);
+    if (best > 1) {
+        const size_t total = (size_t)p.M * p.N;
+        splitk_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, plan.partial, best);
+        B2_LAUNCHED(ctx);
+    }
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+template <int WK>
+int32_t dispatch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
+    switch (p.epilogue) {
+        case EPI_BF16: return launch_pair<WK, EPI_BF16>(ctx, p, err);
+        case EPI_BF16_RESADD: return launch_pair<WK, EPI_BF16_RESADD>(ctx, p, err);
+        case EPI_F32: return launch_pair<WK, EPI_F32>(ctx, p, err);
+    }
+    return b2_fail(B2_ERR_MSG, "gemm: bad epilogue");
+}
+
+}  // namespace
+
+bool b2_gemm_tc_eligible(const GemmParams& p) {
+    return p.M > 64 && p.N % TM == 0 && p.K % TK == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 &&
+           ((uintptr_t)p.w & 15) == 0 && (p.bits == 0 || p.bits == 4 || p.bits == 8);
+}
+
+int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p) {
     if (!ctx->dev_err) {
         B2_CUDA(cudaMalloc((void**)&ctx->dev_err, 16));
         B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, 16, ctx->stream));
     }
-    if (p.bits == 0) return dispatch_tc<0>(ctx, p, best, partial, ctx->dev_err);
-    if (p.bits == 4) return dispatch_tc<4>(ctx, p, best, partial, ctx->dev_err);
-    return dispatch_tc<8>(ctx, p, best, partial, ctx->dev_err);
+    if (p.bits == 0) return dispatch_pair<0>(ctx, p, ctx->dev_err);
+    if (p.bits == 4) return dispatch_pair<4>(ctx, p, ctx->dev_err);
+    return dispatch_pair<8>(ctx, p, ctx->dev_err);
 }

@@ -47,7 +47,7 @@ struct GemmParams {
     float* out_f32;          // EPI_F32
 };
 int32_t b2_gemm_launch(b2_ctx* ctx, const GemmParams& p);
-// tcgen05 / TMEM path (gemm_tc.cu): taken by b2_gemm_launch when eligible.
+// tcgen05 / TMEM path, CTA-pair form (gemm_tc.cu): taken by b2_gemm_launch when eligible.
 bool b2_gemm_tc_eligible(const GemmParams& p);
 int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p);
 

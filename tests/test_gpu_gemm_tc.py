@@ -32,7 +32,10 @@ def quant_case(seed, n, k, bits):
 
 
 @pytest.mark.parametrize("bits", [4, 8, 0])
-@pytest.mark.parametrize("m,n,k", [(65, 128, 64), (100, 256, 512), (256, 128, 4096), (300, 384, 1024), (700, 256, 2048)])
+@pytest.mark.parametrize("m,n,k", [(65, 128, 64), (100, 256, 512), (256, 128, 4096), (300, 384, 1024), (700, 256, 2048),
+                                   # more 256-token blocks than CTA pairs: several pieces per pair, two-block pieces,
+                                   # a ragged last block, and an output width that is an odd multiple of 128
+                                   (700, 20480, 256), (530, 19072, 128), (1100, 9984, 192)])
 def test_tc_gemm_vs_oracle(env, bits, m, n, k):
     ctx, K, orc, _lib = env
     rng = np.random.default_rng(m + n + k)
