@@ -92,15 +92,16 @@ class ClockSampler:
 # BASELINE configuration 3: Llama-3-8B-architecture Q4 continuous batching
 def continuous_setup(args, rank, world, local_rank):
     from mlx_llm_b200 import _lib, engine as eng, workloads as wl
+    from mlx_llm_b200.replica import shard_indices, weak_scaled_requests
 
     shape = dict(wl.LLAMA3_8B if args.layers <= 0 else dict(wl.LLAMA3_8B, num_layers=args.layers))
     ctx = _lib.Context(local_rank)
     cfg = eng.model_config(**shape, quant_bits=4, quant_group=64)
     model = eng.CausalLm.synthetic(ctx, cfg, seed=0)
     # weak scaling: every replica serves its own `requests` requests (ids r, r+N, r+2N, ... of N*requests)
-    prompts, outs, arrival = wl.serving_requests(n=args.requests * world, seed=0, rate=50.0 * world, vocab=shape["vocab_size"],
-                                                 poisson=args.arrivals == "poisson")
-    idx = [i for i in range(len(prompts)) if i % world == rank]
+    prompts, outs, arrival = weak_scaled_requests(args.requests, world, 50.0, seed=0, vocab=shape["vocab_size"],
+                                                  poisson=args.arrivals == "poisson")
+    idx = shard_indices(len(prompts), rank, world)
     reqs = [eng.BatchRequest(prompts[i], int(outs[i]), arrival_s=float(arrival[i])) for i in idx]
     ccfg = eng.ContinuousConfig(max_batch=args.max_batch, block_size=16, exactness=eng.THROUGHPUT, prefill_chunk_tokens=args.chunk,
                                 max_pages=args.max_pages, max_blocks_per_seq=(8192 + 512) // 16 + 2)
@@ -383,26 +384,10 @@ def main():
             print(json.dumps(out), flush=True)
         return 0
 
-    barrier = lambda: None
-    reduce_max = reduce_sum = lambda x: x
-    if world > 1:
-        import torch
-        import torch.distributed as dist
+    from mlx_llm_b200.replica import ReplicaGroup
 
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-        def barrier():
-            dist.barrier()
-            torch.cuda.synchronize()
-
-        def _reduce(x, op):
-            t = torch.tensor([float(x)], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=op)
-            return float(t.item())
-
-        reduce_max = lambda x: _reduce(x, dist.ReduceOp.MAX)
-        reduce_sum = lambda x: _reduce(x, dist.ReduceOp.SUM)
+    group = ReplicaGroup()
+    barrier, reduce_max, reduce_sum = group.barrier, group.reduce_max, group.reduce_sum
 
     if args.workload == "paged_attn_decode":
         out = run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
@@ -412,11 +397,7 @@ def main():
             out["cpu_baseline"] = cpu_baseline_continuous(args)
     if rank == 0:
         print(json.dumps(out), flush=True)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
     return 0
 
 

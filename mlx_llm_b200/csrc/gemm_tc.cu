@@ -26,12 +26,12 @@
 //               layout, generic->async proxy fence, one mbarrier arrive per warp on the LEADER CTA's
 //               "full" barrier (a remote arrive from the second CTA); afterwards the epilogue:
 //               tcgen05.ld 32 lanes x 32 columns, bf16 / residual-add / f32 stores
-//   warp 16     one thread drives TMA (cp.async.bulk.tensor, cta_group::2 form, no multicast): this
+//   warp 16     one thread drives TMA (tiled bulk-tensor loads, cta_group::2 form, each CTA fetching its own rows): this
 //               CTA's half of the token rows of every stage (32-row boxes), plus the W tile when the
 //               weights are dense bf16; completion bytes land on the leader's "full" barrier
 //   warp 17     leader CTA only: one thread issues tcgen05.mma.cta_group::2 (two instructions per
 //               K=16 step when the piece is wider than 256 tokens) and releases stages / publishes
-//               the accumulator with tcgen05.commit multicast to both CTAs' barriers
+//               the accumulator with one tcgen05.commit that arrives on both CTAs' barriers
 // Every mbarrier wait is bounded: on expiry the kernel raises an error word, stops producing and
 // falls through to the common exit, where the TMEM columns are freed.
 #include <cuda.h>
@@ -133,7 +133,7 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
-// 2-D tiled TMA load, CTA-pair form without multicast: the box lands in THIS CTA's shared memory, the
+// 2-D tiled TMA load, CTA-pair form, one destination CTA: the box lands in THIS CTA's shared memory, the
 // completion bytes on `mbar`, a shared::cluster address that may name the peer CTA's barrier.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
     asm volatile(
