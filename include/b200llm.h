@@ -230,6 +230,31 @@ int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* pref
 /* Random-init model generated on the device from a counter-based recipe (benchmark / parity helper;
  * no counterpart in the reference). cfg->quant_bits selects dense / Q4 / Q8 projections. */
 int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t seed, b2_model** out);
+
+/* ---- tensor parallelism over KV heads (no counterpart in the reference, which runs on one device) --------
+ * Rank r of `world` owns KV heads [r*n_kv/world, (r+1)*n_kv/world) with their q heads: the matching rows of
+ * q/k/v and gate/up, the matching COLUMNS of o_proj and down_proj (cut on multiples of the quantization
+ * group), and pages that hold only its heads.  o_proj and down_proj then yield f32 partial sums of the hidden
+ * state, which are added over the group with an NCCL all-reduce on the context's stream before the residual
+ * add (src/models/llama.rs:823-831 and :1040-1045 are the two results that become partial).  Embedding,
+ * norms and lm_head are replicated, every rank runs the same schedule on the same requests and gets the same
+ * tokens.  One process per GPU: rank 0 draws the id, the host program hands its 128 bytes to the other ranks
+ * (any channel: a file, MPI, torch.distributed), then every rank creates its group.  world == 1 is a no-op
+ * group (id may be NULL).  NCCL (libnccl.so.2) is bound at run time; without it a group of more than one
+ * rank fails with B2_ERR_UNSUPPORTED.  A model keeps a pointer to its group: free the model first. */
+typedef struct b2_tp_group b2_tp_group;
+int32_t b2_tp_unique_id(uint8_t* out128);
+int32_t b2_tp_group_create(b2_ctx* ctx, const uint8_t* id128, int32_t rank, int32_t world, b2_tp_group** out);
+int32_t b2_tp_group_free(b2_tp_group* g);
+int32_t b2_tp_group_info(const b2_tp_group* g, int32_t* rank, int32_t* world);
+/* In-place sum of an f32 device buffer over the group, enqueued on the context's stream. */
+int32_t b2_tp_all_reduce_f32(b2_tp_group* g, float* buf_dev, int64_t n);
+/* The two constructors with a group (NULL: the whole model, as without the suffix).  b2_model_get_config
+ * still reports the WHOLE model's dimensions. */
+int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,
+                                 const b2_quant_spec* quant /* nullable */, b2_tp_group* tp, b2_model** out);
+int32_t b2_model_synthetic_tp(b2_ctx* ctx, const b2_model_config* cfg, uint64_t seed, b2_tp_group* tp, b2_model** out);
+
 int32_t b2_model_free(b2_model* m);
 int32_t b2_model_get_config(const b2_model* m, b2_model_config* out);      /* CausalLm::config */
 int32_t b2_model_is_quantized(const b2_model* m);                          /* CausalLm::is_quantized */
@@ -319,6 +344,7 @@ int32_t b2_continuous_step(b2_continuous* e, int32_t max_steps, int32_t* done_ou
 int32_t b2_continuous_finish(b2_continuous* e, b2_gen_output* outs, b2_run_stats* stats);
 int32_t b2_continuous_free(b2_continuous* e);
 
+/* class index 6 = collectives (tensor-parallel all-reduce) */
 /* ---- per-kernel-class timing (CUDA events on the launching stream; off by default) -------------
  * classes: 0 projections (GEMM), 1 paged-attention decode, 2 paged-attention prefill, 3 RoPE + KV
  * append, 4 norm / activation / embedding / argmax, 5 packer + step copies.  The algorithmic work of

@@ -60,7 +60,7 @@ struct b2_ctx {
     double gemm_flops = 0, gemm_weight_bytes = 0, attn_decode_bytes = 0, attn_prefill_flops = 0;
 };
 // kernel classes for the profile
-enum { B2_CLS_GEMM = 0, B2_CLS_ATTN_DECODE = 1, B2_CLS_ATTN_PREFILL = 2, B2_CLS_ROPE_KV = 3, B2_CLS_ELEMENTWISE = 4, B2_CLS_META = 5 };
+enum { B2_CLS_GEMM = 0, B2_CLS_ATTN_DECODE = 1, B2_CLS_ATTN_PREFILL = 2, B2_CLS_ROPE_KV = 3, B2_CLS_ELEMENTWISE = 4, B2_CLS_META = 5, B2_CLS_COLLECTIVE = 6 };
 // Marks the start of a stretch of launches of class `cls` (-1 closes the last stretch).
 void b2_prof_mark(b2_ctx* ctx, int cls);
 // After the stream has been synchronised: folds the recorded stretches into class_ms.

@@ -32,6 +32,15 @@ struct b2_weights {
     std::vector<MappedFile> maps;
 };
 
+// ---- Tensor-parallel group (tp.cu): rank r of `world` owns KV heads [r*hkv/world, (r+1)*hkv/world) ----
+struct b2_tp_group {
+    b2_ctx* ctx = nullptr;
+    int rank = 0, world = 1;
+    void* comm = nullptr;  // ncclComm_t
+};
+// In-place sum over the group of an f32 device buffer, enqueued on the context's stream.
+int32_t b2_tp_all_reduce_sum_f32(b2_tp_group* g, float* buf, size_t n);
+
 // ---- Model (src/models/llama.rs: CausalLm, LlamaLayer, LlamaAttention, LlamaMlp) ------------------
 struct Proj {  // Projection::{Dense,Quantized} (src/primitives/projection.rs:34-47)
     int bits = 0, N = 0, K = 0;
@@ -50,6 +59,7 @@ struct Workspace {
     int t_cap = 0, b_cap = 0, w_cap = 0, p_cap = 0;
     uint16_t *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *act = nullptr;
     uint16_t *last = nullptr, *logits = nullptr;
+    float* tp_part = nullptr;  // [t_cap, hidden] f32 partial sums of o_proj / down_proj (tensor-parallel only)
     int32_t* argmax = nullptr;
     int32_t* ids = nullptr;
     int32_t* meta = nullptr;      // packer outputs (b2_batch_meta_carve layout)
@@ -66,7 +76,10 @@ struct Workspace {
 };
 struct b2_model {
     b2_ctx* ctx = nullptr;
-    b2_model_config cfg{};
+    b2_model_config cfg{};  // the WHOLE model's dimensions, also under tensor parallelism
+    // this rank's share (== cfg's values without tensor parallelism)
+    b2_tp_group* tp = nullptr;
+    int hq_l = 0, hkv_l = 0, inter_l = 0;
     uint16_t* embed = nullptr;
     uint16_t* lm_head = nullptr;
     uint16_t* norm = nullptr;

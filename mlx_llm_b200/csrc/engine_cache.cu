@@ -114,7 +114,7 @@ int32_t b2_pool_new(b2_ctx* ctx, const b2_model* m, int32_t block_size, int64_t 
     p->max_seqs = max_seqs;
     p->max_blocks = max_blocks_per_seq;
     p->layers = m->cfg.num_layers;
-    p->hkv = m->cfg.num_kv_heads;
+    p->hkv = m->hkv_l;  // pages hold this rank's KV heads only
     p->hd = m->cfg.head_dim;
     p->page_elems = (size_t)p->hkv * block_size * p->hd;
     const size_t bytes = (size_t)p->layers * 2 * (size_t)max_pages * p->page_elems * 2;

@@ -66,20 +66,29 @@ __device__ inline float synth_normal(uint64_t seed, uint64_t idx) {
     }
     return __fmul_rn(__fsub_rn((float)sum, 393210.0f), 1.0f / 65536.0f);
 }
-__global__ void synth_codes_kernel(uint64_t seed, int64_t n, uint32_t* out) {
+// A slice [r0, r0+rows) x [c0, c0+cols) of a row-major tensor with `full_cols` columns: element i of the
+// slice is element src(i) of the whole tensor, so a tensor-parallel rank draws exactly the values the
+// whole model would hold at those positions.
+struct Slice {
+    int64_t rows, cols, full_cols, r0, c0;
+    __host__ __device__ int64_t n() const { return rows * cols; }
+    __device__ uint64_t src(int64_t i) const { return (uint64_t)((r0 + i / cols) * full_cols + c0 + i % cols); }
+};
+__global__ void synth_codes_kernel(uint64_t seed, Slice sl, uint32_t* out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = (uint32_t)(synth_u64(seed, (uint64_t)i) >> 16);
+    if (i < sl.n()) out[i] = (uint32_t)(synth_u64(seed, sl.src(i)) >> 16);
 }
-__global__ void synth_sb_kernel(uint64_t seed_s, uint64_t seed_b, int64_t n, float mul, float mid, uint16_t* scales, uint16_t* biases) {
+__global__ void synth_sb_kernel(uint64_t seed_s, uint64_t seed_b, Slice sl, float mul, float mid, uint16_t* scales, uint16_t* biases) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const uint16_t s = f2bf(__fmul_rn(fabsf(synth_normal(seed_s, (uint64_t)i)), mul));
+    if (i >= sl.n()) return;
+    const uint64_t g = sl.src(i);
+    const uint16_t s = f2bf(__fmul_rn(fabsf(synth_normal(seed_s, g)), mul));
     scales[i] = s;
-    biases[i] = f2bf(__fmaf_rn(synth_normal(seed_b, (uint64_t)i), 1e-3f, __fmul_rn(-mid, bf2f(s))));
+    biases[i] = f2bf(__fmaf_rn(synth_normal(seed_b, g), 1e-3f, __fmul_rn(-mid, bf2f(s))));
 }
-__global__ void synth_dense_kernel(uint64_t seed, int64_t n, float std_, uint16_t* out) {
+__global__ void synth_dense_kernel(uint64_t seed, Slice sl, float std_, uint16_t* out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = f2bf(__fmul_rn(synth_normal(seed, (uint64_t)i), std_));
+    if (i < sl.n()) out[i] = f2bf(__fmul_rn(synth_normal(seed, sl.src(i)), std_));
 }
 __global__ void fill_bf16_kernel(uint16_t v, int64_t n, uint16_t* out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -135,6 +144,23 @@ int32_t validate_cfg(const b2_model_config& c) {
                "model config: hidden and intermediate sizes must be multiples of 8");
     B2_REQUIRE(c.quant_bits == 0 || c.quant_bits == 4 || c.quant_bits == 8, B2_ERR_UNSUPPORTED, "model config: quantization bits must be 4 or 8");
     B2_REQUIRE(c.quant_bits == 0 || c.quant_group == 64, B2_ERR_UNSUPPORTED, "model config: quantization group size must be 64");
+    return B2_OK;
+}
+
+// This rank's share of the heads and of the MLP width (the whole model without a group).
+int32_t set_local_dims(b2_model* m, b2_tp_group* tp) {
+    const b2_model_config& c = m->cfg;
+    const int world = tp ? tp->world : 1;
+    B2_REQUIRE(!tp || tp->ctx == m->ctx, B2_ERR_MSG, "tensor-parallel group belongs to another context");
+    B2_REQUIRE(c.num_kv_heads % world == 0, B2_ERR_UNSUPPORTED, "tensor parallelism: the group size must divide num_kv_heads");
+    B2_REQUIRE(c.intermediate_size % (64 * world) == 0, B2_ERR_UNSUPPORTED,
+               "tensor parallelism: every rank's slice of the MLP width must be a multiple of the quantization group (64)");
+    B2_REQUIRE((c.num_heads / world * c.head_dim) % 64 == 0, B2_ERR_UNSUPPORTED,
+               "tensor parallelism: every rank's slice of the attention width must be a multiple of 64");
+    m->tp = world > 1 ? tp : nullptr;
+    m->hq_l = c.num_heads / world;
+    m->hkv_l = c.num_kv_heads / world;
+    m->inter_l = c.intermediate_size / world;
     return B2_OK;
 }
 
@@ -429,8 +455,48 @@ static int32_t load_proj_rows(b2_model* m, const b2_weights* w, const std::strin
     return rc;
 }
 
-int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,
-                              const b2_quant_spec* quant, b2_model** out) {
+// Tensor-parallel load: rows [r0, r0+nr) x columns [c0, c0+nc) of one logical projection go to rows
+// dst_row0.. of `dst` (whose K is nc).  The whole projection is staged on the device (and quantized there
+// when the snapshot is dense: groups run along the input dimension, so slicing after quantization equals
+// quantizing the slice), then the slice is copied out with strided copies.
+static int32_t load_proj_slice(b2_model* m, const b2_weights* w, const std::string& key, Proj& dst, int dst_row0, int N, int K, int r0,
+                               int nr, int c0, int nc, const b2_quant_spec* quant) {
+    if (r0 == 0 && nr == N && c0 == 0 && nc == K) return load_proj_rows(m, w, key, dst, dst_row0, N, K, quant);
+    Proj full;
+    full.N = N;
+    full.K = K;
+    full.bits = dst.bits;
+    const int bits = dst.bits;
+    cudaStream_t st = m->ctx->stream;
+    int32_t rc = B2_OK;
+    if (cudaMalloc(&full.w, bits ? (size_t)N * K * bits / 8 : (size_t)N * K * 2) != cudaSuccess) rc = b2_fail(B2_ERR_CUDA, "out of device memory while staging `" + key + "`");
+    if (rc == B2_OK && bits) {
+        if (cudaMalloc((void**)&full.scales, (size_t)N * (K / 64) * 2) != cudaSuccess || cudaMalloc((void**)&full.biases, (size_t)N * (K / 64) * 2) != cudaSuccess)
+            rc = b2_fail(B2_ERR_CUDA, "out of device memory while staging `" + key + "`");
+    }
+    if (rc == B2_OK) rc = load_proj_rows(m, w, key, full, 0, N, K, quant);
+    auto copy2d = [&](void* d, size_t dpitch, const void* s_, size_t spitch, size_t width) {
+        if (rc == B2_OK && cudaMemcpy2DAsync(d, dpitch, s_, spitch, width, (size_t)nr, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+            rc = b2_fail(B2_ERR_CUDA, "strided copy of `" + key + "` failed");
+    };
+    if (bits == 0) {
+        copy2d((uint16_t*)dst.w + (size_t)dst_row0 * nc, (size_t)nc * 2, (const uint16_t*)full.w + (size_t)r0 * K + c0, (size_t)K * 2, (size_t)nc * 2);
+    } else {
+        const size_t fw = (size_t)K * bits / 8, sw = (size_t)nc * bits / 8;  // bytes of codes per row
+        copy2d((uint8_t*)dst.w + (size_t)dst_row0 * sw, sw, (const uint8_t*)full.w + (size_t)r0 * fw + (size_t)c0 * bits / 8, fw, sw);
+        const size_t fg = (size_t)(K / 64) * 2, sg = (size_t)(nc / 64) * 2;
+        copy2d((uint8_t*)dst.scales + (size_t)dst_row0 * sg, sg, (const uint8_t*)full.scales + (size_t)r0 * fg + (size_t)(c0 / 64) * 2, fg, sg);
+        copy2d((uint8_t*)dst.biases + (size_t)dst_row0 * sg, sg, (const uint8_t*)full.biases + (size_t)r0 * fg + (size_t)(c0 / 64) * 2, fg, sg);
+    }
+    cudaStreamSynchronize(st);
+    if (full.w) cudaFree(full.w);
+    if (full.scales) cudaFree(full.scales);
+    if (full.biases) cudaFree(full.biases);
+    return rc;
+}
+
+int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,
+                                 const b2_quant_spec* quant, b2_tp_group* tp, b2_model** out) {
     B2_REQUIRE(ctx && w && cfg && out, B2_ERR_MSG, "b2_model_from_weights: null argument");
     B2_CUDA(cudaSetDevice(ctx->device));
     b2_model_config c = *cfg;
@@ -463,6 +529,8 @@ int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* pref
         int32_t rc__ = (x);             \
         if (rc__ != B2_OK) return fail(rc__); \
     } while (0)
+    TRY(set_local_dims(m, tp));
+    const int rank = m->tp ? m->tp->rank : 0, world = m->tp ? m->tp->world : 1;
     const int H = c.hidden_size, V = c.vocab_size, hd = c.head_dim;
     TRY(dev_alloc(m, (size_t)V * H * 2, (void**)&m->embed));
     TRY(upload_bf16(m, w, P("embed_tokens.weight"), (int64_t)V * H, m->embed));
@@ -489,17 +557,18 @@ int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* pref
             TRY(dev_alloc(m, (size_t)hd * 2, (void**)&L.k_norm));
             TRY(upload_bf16(m, w, LP("self_attn.k_norm.weight"), hd, L.k_norm));
         }
-        TRY(alloc_proj(m, L.qkv, qd + 2 * kvd, H, bits));
-        TRY(load_proj_rows(m, w, LP("self_attn.q_proj.weight"), L.qkv, 0, qd, H, quant));
-        TRY(load_proj_rows(m, w, LP("self_attn.k_proj.weight"), L.qkv, qd, kvd, H, quant));
-        TRY(load_proj_rows(m, w, LP("self_attn.v_proj.weight"), L.qkv, qd + kvd, kvd, H, quant));
-        TRY(alloc_proj(m, L.o, H, qd, bits));
-        TRY(load_proj_rows(m, w, LP("self_attn.o_proj.weight"), L.o, 0, H, qd, quant));
-        TRY(alloc_proj(m, L.gu, 2 * I, H, bits));
-        TRY(load_proj_rows(m, w, LP("mlp.gate_proj.weight"), L.gu, 0, I, H, quant));
-        TRY(load_proj_rows(m, w, LP("mlp.up_proj.weight"), L.gu, I, I, H, quant));
-        TRY(alloc_proj(m, L.down, H, I, bits));
-        TRY(load_proj_rows(m, w, LP("mlp.down_proj.weight"), L.down, 0, H, I, quant));
+        const int qd_l = qd / world, kvd_l = kvd / world, I_l = I / world;  // this rank's rows / columns
+        TRY(alloc_proj(m, L.qkv, qd_l + 2 * kvd_l, H, bits));
+        TRY(load_proj_slice(m, w, LP("self_attn.q_proj.weight"), L.qkv, 0, qd, H, rank * qd_l, qd_l, 0, H, quant));
+        TRY(load_proj_slice(m, w, LP("self_attn.k_proj.weight"), L.qkv, qd_l, kvd, H, rank * kvd_l, kvd_l, 0, H, quant));
+        TRY(load_proj_slice(m, w, LP("self_attn.v_proj.weight"), L.qkv, qd_l + kvd_l, kvd, H, rank * kvd_l, kvd_l, 0, H, quant));
+        TRY(alloc_proj(m, L.o, H, qd_l, bits));
+        TRY(load_proj_slice(m, w, LP("self_attn.o_proj.weight"), L.o, 0, H, qd, 0, H, rank * qd_l, qd_l, quant));
+        TRY(alloc_proj(m, L.gu, 2 * I_l, H, bits));
+        TRY(load_proj_slice(m, w, LP("mlp.gate_proj.weight"), L.gu, 0, I, H, rank * I_l, I_l, 0, H, quant));
+        TRY(load_proj_slice(m, w, LP("mlp.up_proj.weight"), L.gu, I_l, I, H, rank * I_l, I_l, 0, H, quant));
+        TRY(alloc_proj(m, L.down, H, I_l, bits));
+        TRY(load_proj_slice(m, w, LP("mlp.down_proj.weight"), L.down, 0, H, I, 0, H, rank * I_l, I_l, quant));
     }
     TRY(finish_model(m));
 #undef TRY
@@ -508,7 +577,12 @@ int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* pref
     return B2_OK;
 }
 
-int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t seed, b2_model** out) {
+int32_t b2_model_from_weights(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,
+                              const b2_quant_spec* quant, b2_model** out) {
+    return b2_model_from_weights_tp(ctx, w, prefix, cfg, quant, nullptr, out);
+}
+
+int32_t b2_model_synthetic_tp(b2_ctx* ctx, const b2_model_config* cfg, uint64_t seed, b2_tp_group* tp, b2_model** out) {
     B2_REQUIRE(ctx && cfg && out, B2_ERR_MSG, "b2_model_synthetic: null argument");
     B2_CUDA(cudaSetDevice(ctx->device));
     b2_model_config c = *cfg;
@@ -527,10 +601,12 @@ int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t see
         int32_t rc__ = (x);             \
         if (rc__ != B2_OK) return fail(rc__); \
     } while (0)
+    TRY(set_local_dims(m, tp));
+    const int rank = m->tp ? m->tp->rank : 0, world = m->tp ? m->tp->world : 1;
     cudaStream_t st = ctx->stream;
     auto blocks = [](int64_t n) { return (unsigned)((n + 255) / 256); };
     auto dense = [&](uint16_t* dst, int64_t n, int layer, int which) {
-        synth_dense_kernel<<<blocks(n), 256, 0, st>>>(synth_tensor_seed(seed, layer, which), n, 0.02f, dst);
+        synth_dense_kernel<<<blocks(n), 256, 0, st>>>(synth_tensor_seed(seed, layer, which), Slice{1, n, n, 0, 0}, 0.02f, dst);
     };
     auto ones = [&](uint16_t* dst, int64_t n) { fill_bf16_kernel<<<blocks(n), 256, 0, st>>>(0x3f80, n, dst); };
     const int H = c.hidden_size, V = c.vocab_size, hd = c.head_dim, I = c.intermediate_size;
@@ -543,20 +619,23 @@ int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t see
     m->layers.resize(c.num_layers);
     const int bits = c.quant_bits;
     const float mul = bits == 4 ? 0.02f / 7.5f : 0.02f / 127.5f, mid = bits == 4 ? 8.f : 128.f;
-    auto fill_rows = [&](Proj& p, int row0, int layer, int which) {
+    // rows [r0, r0+nr) x columns [c0, c0+nc) of logical projection `which`, written to rows dst_row0.. of p
+    auto fill = [&](Proj& p, int dst_row0, int layer, int which, int r0, int nr, int c0, int nc) {
         int N, K;
         proj_dims(c, which, N, K);
         const uint64_t ts = synth_tensor_seed(seed, layer, which);
         if (bits == 0) {
-            synth_dense_kernel<<<blocks((int64_t)N * K), 256, 0, st>>>(ts, (int64_t)N * K, 0.02f, (uint16_t*)p.w + (size_t)row0 * K);
+            synth_dense_kernel<<<blocks((int64_t)nr * nc), 256, 0, st>>>(ts, Slice{nr, nc, K, r0, c0}, 0.02f, (uint16_t*)p.w + (size_t)dst_row0 * nc);
         } else {
-            const int64_t words = (int64_t)N * K * bits / 32, ng = (int64_t)N * (K / 64);
-            synth_codes_kernel<<<blocks(words), 256, 0, st>>>(ts, words, (uint32_t*)p.w + (size_t)row0 * K * bits / 32);
-            synth_sb_kernel<<<blocks(ng), 256, 0, st>>>(ts + 1, ts + 2, ng, mul, mid, p.scales + (size_t)row0 * (K / 64),
-                                                       p.biases + (size_t)row0 * (K / 64));
+            const Slice words{nr, (int64_t)nc * bits / 32, (int64_t)K * bits / 32, r0, (int64_t)c0 * bits / 32};
+            const Slice grp{nr, nc / 64, K / 64, r0, c0 / 64};
+            synth_codes_kernel<<<blocks(words.n()), 256, 0, st>>>(ts, words, (uint32_t*)p.w + (size_t)dst_row0 * words.cols);
+            synth_sb_kernel<<<blocks(grp.n()), 256, 0, st>>>(ts + 1, ts + 2, grp, mul, mid, p.scales + (size_t)dst_row0 * grp.cols,
+                                                            p.biases + (size_t)dst_row0 * grp.cols);
         }
     };
     const int qd = c.num_heads * hd, kvd = c.num_kv_heads * hd;
+    const int qd_l = qd / world, kvd_l = kvd / world, I_l = I / world;
     for (int l = 0; l < c.num_layers; l++) {
         LayerW& L = m->layers[l];
         TRY(dev_alloc(m, (size_t)H * 2, (void**)&L.input_ln));
@@ -569,17 +648,17 @@ int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t see
             TRY(dev_alloc(m, (size_t)hd * 2, (void**)&L.k_norm));
             ones(L.k_norm, hd);
         }
-        TRY(alloc_proj(m, L.qkv, qd + 2 * kvd, H, bits));
-        fill_rows(L.qkv, 0, l, 0);
-        fill_rows(L.qkv, qd, l, 1);
-        fill_rows(L.qkv, qd + kvd, l, 2);
-        TRY(alloc_proj(m, L.o, H, qd, bits));
-        fill_rows(L.o, 0, l, 3);
-        TRY(alloc_proj(m, L.gu, 2 * I, H, bits));
-        fill_rows(L.gu, 0, l, 4);
-        fill_rows(L.gu, I, l, 5);
-        TRY(alloc_proj(m, L.down, H, I, bits));
-        fill_rows(L.down, 0, l, 6);
+        TRY(alloc_proj(m, L.qkv, qd_l + 2 * kvd_l, H, bits));  // this rank's heads: rows of q, k, v
+        fill(L.qkv, 0, l, 0, rank * qd_l, qd_l, 0, H);
+        fill(L.qkv, qd_l, l, 1, rank * kvd_l, kvd_l, 0, H);
+        fill(L.qkv, qd_l + kvd_l, l, 2, rank * kvd_l, kvd_l, 0, H);
+        TRY(alloc_proj(m, L.o, H, qd_l, bits));                // ... and the matching columns of o_proj
+        fill(L.o, 0, l, 3, 0, H, rank * qd_l, qd_l);
+        TRY(alloc_proj(m, L.gu, 2 * I_l, H, bits));            // rows of gate and up
+        fill(L.gu, 0, l, 4, rank * I_l, I_l, 0, H);
+        fill(L.gu, I_l, l, 5, rank * I_l, I_l, 0, H);
+        TRY(alloc_proj(m, L.down, H, I_l, bits));              // columns of down_proj
+        fill(L.down, 0, l, 6, 0, H, rank * I_l, I_l);
     }
     TRY(finish_model(m));
 #undef TRY
@@ -587,6 +666,10 @@ int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t see
     B2_CUDA(cudaGetLastError());
     *out = m;
     return B2_OK;
+}
+
+int32_t b2_model_synthetic(b2_ctx* ctx, const b2_model_config* cfg, uint64_t seed, b2_model** out) {
+    return b2_model_synthetic_tp(ctx, cfg, seed, nullptr, out);
 }
 
 int32_t b2_model_free(b2_model* m) {

@@ -31,14 +31,15 @@ int32_t ensure_workspace(b2_model* m, int T, int B, int W, int P, size_t stage_i
     if (grow_t || grow_b || grow_w || grow_p) B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
     if (grow_t) {
         const size_t t = (size_t)std::max(T, 64) * 5 / 4;
-        const size_t qkv_w = (size_t)(c.num_heads + 2 * c.num_kv_heads) * c.head_dim;
+        const size_t qkv_w = (size_t)(m->hq_l + 2 * m->hkv_l) * c.head_dim;
         B2_CHECK(regrow(w.x, t * c.hidden_size));
         B2_CHECK(regrow(w.xn, t * c.hidden_size));
         B2_CHECK(regrow(w.qkv, t * qkv_w));
-        B2_CHECK(regrow(w.q, t * c.num_heads * c.head_dim));
-        B2_CHECK(regrow(w.attn, t * c.num_heads * c.head_dim));
-        B2_CHECK(regrow(w.gu, t * 2 * c.intermediate_size));
-        B2_CHECK(regrow(w.act, t * c.intermediate_size));
+        B2_CHECK(regrow(w.q, t * m->hq_l * c.head_dim));
+        B2_CHECK(regrow(w.attn, t * m->hq_l * c.head_dim));
+        B2_CHECK(regrow(w.gu, t * 2 * m->inter_l));
+        B2_CHECK(regrow(w.act, t * m->inter_l));
+        if (m->tp && m->tp->world > 1) B2_CHECK(regrow(w.tp_part, t * c.hidden_size));
         B2_CHECK(regrow(w.ids, t));
         w.t_cap = (int)t;
     }
@@ -55,7 +56,7 @@ int32_t ensure_workspace(b2_model* m, int T, int B, int W, int P, size_t stage_i
     if (grow_p) w.p_cap = std::max(P, 64) * 5 / 4;
     if (grow_t || grow_b || grow_w || grow_p) {
         B2_CHECK(regrow(w.meta, (size_t)b2_batch_metadata_elems(w.b_cap, w.t_cap, w.w_cap, w.p_cap)));
-        const size_t sb = b2_decode_attn_scratch_bytes(w.w_cap, c.num_heads, c.head_dim);
+        const size_t sb = b2_decode_attn_scratch_bytes(w.w_cap, m->hq_l, c.head_dim);
         if (w.attn_scratch) cudaFree(w.attn_scratch);
         B2_CUDA(cudaMalloc((void**)&w.attn_scratch, sb));
         w.attn_scratch_bytes = sb;
@@ -90,6 +91,34 @@ int32_t gemm(b2_model* m, const Proj& p, const uint16_t* x, int M, int ldx, uint
     g.out = out;
     g.res = res;
     return b2_gemm_launch(m->ctx, g);
+}
+
+// x += proj(a) where every tensor-parallel rank holds a slice of the input dimension: f32 partial
+// products, a sum over the ranks, then the residual add with the fused epilogue's roundings.
+int32_t gemm_reduce_residual(b2_model* m, const Proj& p, const uint16_t* a, int M, int lda, uint16_t* x, int H, int x_rows_cap) {
+    b2_ctx* ctx = m->ctx;
+    GemmParams g{};
+    g.x_rows_cap = x_rows_cap;
+    g.x = a;
+    g.w = p.w;
+    g.scales = p.scales;
+    g.biases = p.biases;
+    g.bits = p.bits;
+    g.group = 64;
+    g.M = M;
+    g.N = p.N;
+    g.K = p.K;
+    g.ldx = lda;
+    g.ldo = H;
+    g.ldres = H;
+    g.epilogue = EPI_F32;
+    g.out_f32 = m->ws.tp_part;
+    b2_prof_mark(ctx, B2_CLS_GEMM);
+    B2_CHECK(b2_gemm_launch(ctx, g));
+    b2_prof_mark(ctx, B2_CLS_COLLECTIVE);
+    B2_CHECK(b2_tp_all_reduce_sum_f32(m->tp, m->ws.tp_part, (size_t)M * H));
+    b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
+    return b2_residual_add_f32_launch(ctx, m->ws.tp_part, (int64_t)M * H, x);
 }
 
 int pick_chunk_tiles(long dec_ctx_sum, int hkv, int sm_count) {
@@ -129,12 +158,12 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     B2_CHECK(b2_model_ensure_rope(m, max_pos));
     // pages for the new tokens (host allocator), then the step descriptors
     for (auto& s : seqs) B2_CHECK(b2_cache_reserve(s.cache, s.n));
-    const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, c.num_kv_heads, ctx->sm_count);
+    const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, m->hkv_l, ctx->sm_count);
     const int q_tile = 64;
     int W = 0, P = 0;
     double pf_flops = 0;  // 4*hd*hq flops per (query, visible key) pair
     for (auto& s : seqs) {
-        if (s.n > 1) pf_flops += 4.0 * c.head_dim * c.num_heads * ((double)s.n * s.cache->len + 0.5 * (double)s.n * (s.n + 1));
+        if (s.n > 1) pf_flops += 4.0 * c.head_dim * m->hq_l * ((double)s.n * s.cache->len + 0.5 * (double)s.n * (s.n + 1));
         if (s.n == 1) {
             const int tiles = (s.cache->len + 1 + 15) / 16;
             W += (tiles + chunk_tiles - 1) / chunk_tiles;
@@ -196,7 +225,8 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     b2_batch_meta_carve(w.meta, B, T, W, P, mo);
     B2_CHECK(b2_batch_meta_launch(ctx, in, mo));
 
-    const int H = c.hidden_size, hq = c.num_heads, hkv = c.num_kv_heads, hd = c.head_dim, I = c.intermediate_size;
+    const int H = c.hidden_size, hq = m->hq_l, hkv = m->hkv_l, hd = c.head_dim, I = m->inter_l;  // this rank's heads / columns
+    const bool tp = m->tp && m->tp->world > 1;
     const int qkv_w = (hq + 2 * hkv) * hd;
     const float scale_log2 = powf((float)hd, -0.5f) * 1.4426950408889634f;  // attn_scale, config.rs:597-598
     b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
@@ -275,16 +305,24 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
             B2_CHECK(b2_prefill_attn_launch(ctx, pp, hd, P));
             ctx->attn_prefill_flops += pf_flops;
         }
-        b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, L.o, w.attn, T, hq * hd, w.x, H, w.x, w.t_cap));     // h = x + o_proj(attn)
+        if (tp) {
+            B2_CHECK(gemm_reduce_residual(m, L.o, w.attn, T, hq * hd, w.x, H, w.t_cap));
+        } else {
+            b2_prof_mark(ctx, B2_CLS_GEMM);
+            B2_CHECK(gemm(m, L.o, w.attn, T, hq * hd, w.x, H, w.x, w.t_cap));  // h = x + o_proj(attn)
+        }
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_rms_norm_launch(ctx, w.x, L.post_ln, c.rms_norm_eps, T, H, H, nullptr, w.xn));
         b2_prof_mark(ctx, B2_CLS_GEMM);
         B2_CHECK(gemm(m, L.gu, w.xn, T, H, w.gu, 2 * I, nullptr, w.t_cap));
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_swiglu_launch(ctx, w.gu, T, I, w.act));
-        b2_prof_mark(ctx, B2_CLS_GEMM);
-        B2_CHECK(gemm(m, L.down, w.act, T, I, w.x, H, w.x, w.t_cap));        // x = h + down(...)
+        if (tp) {
+            B2_CHECK(gemm_reduce_residual(m, L.down, w.act, T, I, w.x, H, w.t_cap));
+        } else {
+            b2_prof_mark(ctx, B2_CLS_GEMM);
+            B2_CHECK(gemm(m, L.down, w.act, T, I, w.x, H, w.x, w.t_cap));  // x = h + down(...)
+        }
     }
     if (n_logits > 0) {
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);

@@ -115,6 +115,23 @@ __global__ void add_kernel(const uint16_t* __restrict__ a, const uint16_t* __res
     if (i < n) out[i] = f2bf(bf2f(a[i]) + bf2f(b[i]));
 }
 
+// x = bf16(x + bf16(y)): the residual add of a projection whose f32 result arrives from a reduction
+// over tensor-parallel ranks (same two roundings as the fused GEMM epilogue).
+__global__ void residual_add_f32_kernel(const float* __restrict__ y, int64_t n, uint16_t* __restrict__ x) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 v = *reinterpret_cast<const float4*>(y + i);
+        uint2 xv = *reinterpret_cast<const uint2*>(x + i);
+        const float a0 = bf2f((uint16_t)(xv.x & 0xffff)) + rbf(v.x), a1 = bf2f((uint16_t)(xv.x >> 16)) + rbf(v.y);
+        const float a2 = bf2f((uint16_t)(xv.y & 0xffff)) + rbf(v.z), a3 = bf2f((uint16_t)(xv.y >> 16)) + rbf(v.w);
+        xv.x = pack_bf2(a0, a1);
+        xv.y = pack_bf2(a2, a3);
+        *reinterpret_cast<uint2*>(x + i) = xv;
+    } else {
+        for (int64_t j = i; j < n; j++) x[j] = f2bf(bf2f(x[j]) + rbf(y[j]));
+    }
+}
+
 // Greedy argmax over bf16 logits, first maximum wins (src/primitives/sampler.rs:221-241).
 __global__ void argmax_kernel(const uint16_t* __restrict__ logits, int vocab, int32_t* __restrict__ out) {
     const uint16_t* row = logits + (size_t)blockIdx.x * vocab;
@@ -266,6 +283,14 @@ int32_t b2_swiglu2_launch(b2_ctx* ctx, const uint16_t* gate, const uint16_t* up,
 int32_t b2_add_launch(b2_ctx* ctx, const uint16_t* a, const uint16_t* b, int64_t n, uint16_t* out) {
     if (n <= 0) return B2_OK;
     add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(a, b, n, out);
+    B2_LAUNCHED(ctx);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+int32_t b2_residual_add_f32_launch(b2_ctx* ctx, const float* y, int64_t n, uint16_t* x) {
+    if (n <= 0) return B2_OK;
+    const int64_t quads = (n + 3) / 4;
+    residual_add_f32_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, ctx->stream>>>(y, n, x);
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     return B2_OK;

@@ -60,6 +60,8 @@ int32_t b2_embed_launch(b2_ctx* ctx, const uint16_t* table, const int32_t* ids, 
 int32_t b2_swiglu_launch(b2_ctx* ctx, const uint16_t* gate_up, int rows, int inter, uint16_t* out);
 int32_t b2_swiglu2_launch(b2_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t n, uint16_t* out);
 int32_t b2_add_launch(b2_ctx* ctx, const uint16_t* a, const uint16_t* b, int64_t n, uint16_t* out);
+// x = bf16(x + bf16(y)), y f32 (n a multiple of 4 for the vector path; any n works)
+int32_t b2_residual_add_f32_launch(b2_ctx* ctx, const float* y, int64_t n, uint16_t* x);
 // Greedy argmax per row over bf16 logits, ties -> lowest index.
 int32_t b2_argmax_launch(b2_ctx* ctx, const uint16_t* logits, int rows, int vocab, int32_t* out);
 int32_t b2_dequantize_launch(b2_ctx* ctx, const uint32_t* packed, const uint16_t* scales, const uint16_t* biases, int64_t rows,

@@ -14,7 +14,7 @@ from typing import List, Optional
 
 import numpy as np
 
-from ._lib import B2Error, Context, check, load
+from ._lib import B2Error, Context, check, load, ptr
 
 # FinishReason (src/decode/stream.rs:31-46)
 STOP_TOKEN, MAX_TOKENS, CANCELLED, STOPPED = 0, 1, 2, 3
@@ -141,18 +141,19 @@ class CausalLm:
         self.ctx, self.h = ctx, handle
 
     @classmethod
-    def from_weights(cls, ctx, weights, prefix, config, quant: Optional[QuantSpec] = None):
+    def from_weights(cls, ctx, weights, prefix, config, quant: Optional[QuantSpec] = None, tp=None):
         h = C.c_void_p()
         q = C.byref(CQuantSpec(quant.group_size, quant.bits)) if quant else None
-        check(load().b2_model_from_weights(ctx.h, weights.h, (prefix or "").encode(), C.byref(config), q, C.byref(h)))
+        check(load().b2_model_from_weights_tp(ctx.h, weights.h, (prefix or "").encode(), C.byref(config), q,
+                                              tp.h if tp is not None else None, C.byref(h)))
         return cls(ctx, h)
 
     from_weights_with = from_weights
 
     @classmethod
-    def synthetic(cls, ctx, config, seed=0):
+    def synthetic(cls, ctx, config, seed=0, tp=None):
         h = C.c_void_p()
-        check(load().b2_model_synthetic(ctx.h, C.byref(config), C.c_uint64(seed), C.byref(h)))
+        check(load().b2_model_synthetic_tp(ctx.h, C.byref(config), C.c_uint64(seed), tp.h if tp is not None else None, C.byref(h)))
         return cls(ctx, h)
 
     def config(self):
@@ -188,6 +189,31 @@ class CausalLm:
     def free(self):
         if self.h:
             load().b2_model_free(self.h)
+            self.h = C.c_void_p()
+
+
+class TpGroup:
+    """Tensor-parallel group of one rank per GPU (b2_tp_group_*): rank 0 draws the id with
+    TpGroup.unique_id(), the caller distributes those 128 bytes, every rank constructs its group."""
+
+    @staticmethod
+    def unique_id():
+        buf = (C.c_uint8 * 128)()
+        check(load().b2_tp_unique_id(buf))
+        return bytes(buf)
+
+    def __init__(self, ctx, unique_id, rank, world):
+        self.h = C.c_void_p()
+        self.rank, self.world = rank, world
+        idbuf = (C.c_uint8 * 128).from_buffer_copy(unique_id) if unique_id is not None else None
+        check(load().b2_tp_group_create(ctx.h, idbuf, int(rank), int(world), C.byref(self.h)))
+
+    def all_reduce_f32(self, buf, n):
+        check(load().b2_tp_all_reduce_f32(self.h, ptr(buf), C.c_int64(n)))
+
+    def free(self):
+        if self.h:
+            check(load().b2_tp_group_free(self.h))
             self.h = C.c_void_p()
 
 
@@ -427,7 +453,7 @@ class CProfile(C.Structure):
                 ("attn_decode_bytes", C.c_double), ("attn_prefill_flops", C.c_double)]
 
 
-PROFILE_CLASSES = ["gemm", "attn_decode", "attn_prefill", "rope_kv", "elementwise", "meta_copies"]
+PROFILE_CLASSES = ["gemm", "attn_decode", "attn_prefill", "rope_kv", "elementwise", "meta_copies", "collective"]
 
 
 def profile_enable(ctx, on=True):

@@ -147,7 +147,7 @@ def engine_config(eng, cfg=CONFIG0, quant_bits=0):
                             quant_group=64 if quant_bits else 0)
 
 
-def build_engine_model(eng, ctx, cfg=CONFIG0, weights=None, quant=None):
+def build_engine_model(eng, ctx, cfg=CONFIG0, weights=None, quant=None, tp=None):
     """The same tiny weights as build_oracle_model, handed to the engine as f32 host tensors under
     the Hugging Face key names CausalLm::from_weights reads (src/models/llama.rs:122-181, :245-281)."""
     weights = weights or tiny_weights(cfg)
@@ -164,7 +164,7 @@ def build_engine_model(eng, ctx, cfg=CONFIG0, weights=None, quant=None):
         if cfg.get("qk_norm"):
             w.add(names["q_norm"], np.ones(cfg["head_dim"], np.float32))
             w.add(names["k_norm"], np.ones(cfg["head_dim"], np.float32))
-    m = eng.CausalLm.from_weights(ctx, w, "", engine_config(eng, cfg), quant)
+    m = eng.CausalLm.from_weights(ctx, w, "", engine_config(eng, cfg), quant, tp=tp)
     w.free()
     return m
 
