@@ -94,6 +94,8 @@ def continuous_setup(args, rank, world, local_rank):
     from mlx_llm_b200 import _lib, engine as eng, workloads as wl
     from mlx_llm_b200.replica import shard_indices, weak_scaled_requests
 
+    if args.workload == "qwen3_32b_q8_tp":
+        return tp_setup(args, rank, world, local_rank)
     shape = dict(wl.LLAMA3_8B if args.layers <= 0 else dict(wl.LLAMA3_8B, num_layers=args.layers))
     ctx = _lib.Context(local_rank)
     cfg = eng.model_config(**shape, quant_bits=4, quant_group=64)
@@ -105,6 +107,37 @@ def continuous_setup(args, rank, world, local_rank):
     reqs = [eng.BatchRequest(prompts[i], int(outs[i]), arrival_s=float(arrival[i])) for i in idx]
     ccfg = eng.ContinuousConfig(max_batch=args.max_batch, block_size=16, exactness=eng.THROUGHPUT, prefill_chunk_tokens=args.chunk,
                                 max_pages=args.max_pages, max_blocks_per_seq=(8192 + 512) // 16 + 2)
+    return ctx, model, reqs, ccfg, shape
+
+
+def tp_setup(args, rank, world, local_rank):
+    """BASELINE configuration 4: ONE Qwen3-32B-architecture Q8 model split over the N ranks by KV heads; every rank
+    runs the same schedule on the same 512 requests.  The pool takes what is left of HBM after the weights."""
+    from mlx_llm_b200 import _lib, engine as eng, workloads as wl
+
+    shape = dict(wl.QWEN3_32B if args.layers <= 0 else dict(wl.QWEN3_32B, num_layers=args.layers))
+    ctx = _lib.Context(local_rank)
+    uid = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        t = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            t.copy_(torch.frombuffer(bytearray(eng.TpGroup.unique_id()), dtype=torch.uint8))
+        dist.broadcast(t, 0)
+        uid = bytes(t.cpu().numpy().tobytes())
+    tp = eng.TpGroup(ctx, uid, rank, world)
+    cfg = eng.model_config(**shape, quant_bits=8, quant_group=64)
+    model = eng.CausalLm.synthetic(ctx, cfg, seed=0, tp=tp)
+    model._tp = tp  # the model points at its group: keep it alive
+    prompts, outs, arrival = wl.long_context_requests(n=args.requests if args.requests != 2048 else 512, seed=0, vocab=shape["vocab_size"])
+    reqs = [eng.BatchRequest(p, int(o), arrival_s=0.0) for p, o in zip(prompts, outs)]
+    page_bytes = shape["num_layers"] * 2 * (shape["num_kv_heads"] // world) * 16 * shape["head_dim"] * 2
+    free, _ = ctx.mem_info()
+    max_pages = args.max_pages if args.max_pages != 49152 else int((free - (12 << 30)) // page_bytes)
+    ccfg = eng.ContinuousConfig(max_batch=512, block_size=16, exactness=eng.THROUGHPUT, prefill_chunk_tokens=args.chunk,
+                                max_pages=max_pages, max_blocks_per_seq=(32768 + 256 + args.chunk) // 16 + 2)
     return ctx, model, reqs, ccfg, shape
 
 
@@ -145,23 +178,30 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     prof = eng.profile_read(ctx)
     eng.profile_enable(ctx, False)
     prof_steps = max(p1["steps"] - p0["steps"], 1)
-    all_gen, all_dev, all_wall = reduce_sum(gen), reduce_max(dev_ms), reduce_max(wall_ms)
+    tp_mode = args.workload == "qwen3_32b_q8_tp"
+    # replicas: tokens add up over ranks; tensor parallelism: every rank produced the SAME tokens, count them once
+    all_gen, all_dev, all_wall = (gen if tp_mode else reduce_sum(gen)), reduce_max(dev_ms), reduce_max(wall_ms)
     peaks = measured_peaks()
     gemm_ms = prof["ms"]["gemm"]
     tfl = prof["gemm_flops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     total_prof_ms = sum(prof["ms"].values())
     dec_ms = prof["ms"]["attn_decode"]
     out = dict(
-        metric="continuous-batch decode tok/s, Llama-3-8B-arch Q4", value=all_gen / (all_dev * 1e-3), unit="tok/s", n_gpus=world,
-        steps=int(steps), warmup=warm, ms_per_step=all_dev / max(steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
-        dtype="bf16", data="synthetic",
-        config=dict(workload="llama3_8b_q4_continuous (BASELINE configuration 3)", layers=shape["num_layers"], requests=args.requests,
-                    arrivals=args.arrivals, max_batch=args.max_batch, page=16, prefill_chunk=args.chunk, ramp_steps=args.ramp,
-                    parallelism=f"replica x{world}, requests sharded id mod N", l2="per-step working set (weights 5 GB + KV) exceeds L2",
+        metric="continuous-batch decode tok/s, Qwen3-32B-arch Q8, tensor-parallel" if tp_mode else "continuous-batch decode tok/s, Llama-3-8B-arch Q4",
+        value=all_gen / (all_dev * 1e-3), unit="tok/s", n_gpus=world,
+        steps=int(steps), warmup=warm, ms_per_step=all_dev / max(steps, 1), higher_is_better=True, scaling="strong" if tp_mode else "weak",
+        vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload="qwen3_32b_q8_tp (BASELINE configuration 4)" if tp_mode else "llama3_8b_q4_continuous (BASELINE configuration 3)",
+                    layers=shape["num_layers"], requests=len(reqs) if tp_mode else args.requests,
+                    arrivals="all at time 0" if tp_mode else args.arrivals, max_batch=ccfg.max_batch, page=16, prefill_chunk=args.chunk,
+                    ramp_steps=args.ramp, max_pages=int(ccfg.max_pages), peak_concurrent=int(s1.get("peak_concurrent", 0)),
+                    parallelism=(f"tensor-parallel x{world} over KV heads, NCCL all-reduce (f32) after o_proj and down_proj" if tp_mode
+                                 else f"replica x{world}, requests sharded id mod N"),
+                    l2="per-step working set (weights + KV) exceeds L2",
                     prefill_tokens_per_step=pre / max(steps, 1), generated_tokens_per_step=gen / max(steps, 1)),
         roofline=dict(bound="tensor", achieved=tfl, peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
                       frac=tfl / peaks["bf16_tflops_sustained"], traffic=None, peak_source=peaks["source"] + " (sustained)",
-                      kernel="projection GEMMs (Q4 dequant fused) + bf16 lm_head", launches_per_step=prof["launches"]["gemm"] / prof_steps,
+                      kernel=("projection GEMMs (Q8 dequant fused) + bf16 lm_head" if tp_mode else "projection GEMMs (Q4 dequant fused) + bf16 lm_head"), launches_per_step=prof["launches"]["gemm"] / prof_steps,
                       ms_per_step=gemm_ms / prof_steps, share_of_step=gemm_ms / total_prof_ms if total_prof_ms else None,
                       algorithmic_flops_per_step=prof["gemm_flops"] / prof_steps),
         roofline_paged_attn_decode=dict(bound="hbm", achieved=(prof["attn_decode_bytes"] / (dec_ms * 1e-3) / 1e9) if dec_ms > 0 else None,
@@ -357,7 +397,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode"])
+    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode", "qwen3_32b_q8_tp"])
     ap.add_argument("--chunk-tokens", dest="chunk_tokens", type=int, default=0, help="paged_attn_decode: split-K chunk")
     ap.add_argument("--requests", type=int, default=2048)
     ap.add_argument("--arrivals", default="saturated", choices=["saturated", "poisson"])

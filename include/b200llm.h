@@ -54,6 +54,8 @@ int32_t b2_free(b2_ctx* ctx, void* dev);
 int32_t b2_memcpy_h2d(b2_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 int32_t b2_memcpy_d2h(b2_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
 int32_t b2_memset(b2_ctx* ctx, void* dst_dev, int value, size_t bytes);
+/* Free and total device memory of the context's GPU (for sizing the page pool). */
+int32_t b2_mem_info(b2_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
 int32_t b2_host_alloc_pinned(size_t bytes, void** out_host);
 int32_t b2_host_free_pinned(void* host);
 /* CUDA-event timing on the context's stream (every kernel of this library launches there). */

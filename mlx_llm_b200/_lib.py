@@ -118,6 +118,11 @@ class Context:
     def profiler_range(self, on):
         check(load().b2_profiler_range(self.h, C.c_int32(1 if on else 0)))
 
+    def mem_info(self):
+        f, t = C.c_size_t(0), C.c_size_t(0)
+        check(load().b2_mem_info(self.h, C.byref(f), C.byref(t)))
+        return f.value, t.value
+
     def launch_count(self):
         n = C.c_int64(0)
         check(load().b2_launch_count(self.h, C.byref(n)))

@@ -114,6 +114,13 @@ int32_t b2_memset(b2_ctx* ctx, void* dst_dev, int value, size_t bytes) {
     B2_CUDA(cudaMemsetAsync(dst_dev, value, bytes, ctx->stream));
     return B2_OK;
 }
+int32_t b2_mem_info(b2_ctx* ctx, size_t* free_bytes, size_t* total_bytes) {
+    B2_REQUIRE(ctx && free_bytes && total_bytes, B2_ERR_MSG, "b2_mem_info: null argument");
+    B2_CUDA(cudaSetDevice(ctx->device));
+    B2_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+    return B2_OK;
+}
+
 int32_t b2_host_alloc_pinned(size_t bytes, void** out_host) {
     B2_CUDA(cudaHostAlloc(out_host, bytes ? bytes : 16, cudaHostAllocDefault));
     return B2_OK;

@@ -28,6 +28,15 @@ def serving_requests(n=2048, seed=0, rate=50.0, vocab=128256, median_prompt=512,
     return prompts, out, arrival
 
 
+def long_context_requests(n=512, seed=0, vocab=151936, min_prompt=1024, max_prompt=32768, max_new=256):
+    """BASELINE configuration 4: n sequences, prompt lengths uniform in [min_prompt, max_prompt], max_new outputs each,
+    all present at time 0.  Returns (prompts, max_new [n], arrival_s [n])."""
+    rng = np.random.default_rng(seed)
+    plen = rng.integers(min_prompt, max_prompt + 1, size=n)
+    prompts = [rng.integers(0, vocab, size=int(p), dtype=np.int32) for p in plen]
+    return prompts, np.full(n, max_new, np.int64), np.zeros(n)
+
+
 def shard(items, rank, world):
     """Replica sharding: request id mod world (independent units, no collective)."""
     return [x for i, x in enumerate(items) if i % world == rank]
