@@ -252,7 +252,7 @@ int32_t b2_paged_attn_prefill(b2_ctx* ctx, const uint16_t* q_dev, const uint16_t
                "b2_paged_attn_prefill: null argument");
     B2_REQUIRE(page_size > 0 && page_size % 16 == 0, B2_ERR_UNSUPPORTED, "b2_paged_attn_prefill: page_size must be a multiple of 16");
     if (num_seqs <= 0) return B2_OK;
-    const int q_tile = 64;
+    const int q_tile = b2_prefill_q_tile(ctx, head_dim);
     std::vector<int32_t> host;  // slot[B] cu[B+1] ctx[B] pf_seq[P] pf_qstart[P] n_work
     std::vector<int32_t> pf_seq, pf_q;
     for (int i = 0; i < num_seqs; i++) {
@@ -293,6 +293,9 @@ int32_t b2_paged_attn_prefill(b2_ctx* ctx, const uint16_t* q_dev, const uint16_t
     p.page_tiles = page_size / 16;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.out = out_dev;
+    p.q_tile = q_tile;
+    p.q_rows = cu_seqlens_host[num_seqs];
+    p.pool_rows = 1ll << 30;  // the pool's size is not an argument: any bound works, boxes are addressed through the block table
     return b2_prefill_attn_launch(ctx, p, head_dim, P);
 }
 

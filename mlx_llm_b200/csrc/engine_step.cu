@@ -159,7 +159,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     // pages for the new tokens (host allocator), then the step descriptors
     for (auto& s : seqs) B2_CHECK(b2_cache_reserve(s.cache, s.n));
     const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, m->hkv_l, ctx->sm_count);
-    const int q_tile = 64;
+    const int q_tile = b2_prefill_q_tile(ctx, c.head_dim);
     int W = 0, P = 0;
     double pf_flops = 0;  // 4*hd*hq flops per (query, visible key) pair
     for (auto& s : seqs) {
@@ -301,6 +301,9 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
             pp.page_tiles = pool->block_size / 16;
             pp.scale_log2 = scale_log2;
             pp.out = w.attn;
+            pp.q_tile = q_tile;
+            pp.q_rows = w.t_cap;
+            pp.pool_rows = (int64_t)pool->max_pages * hkv * pool->block_size;
             b2_prof_mark(ctx, B2_CLS_ATTN_PREFILL);
             B2_CHECK(b2_prefill_attn_launch(ctx, pp, hd, P));
             ctx->attn_prefill_flops += pf_flops;

@@ -141,5 +141,12 @@ struct PrefillAttnParams {
     int hq, hkv, page_tiles;
     float scale_log2;
     uint16_t* out;               // [T, hq, hd]
+    int q_tile;                  // queries per work item: b2_prefill_q_tile() at the time the work list was built
+    int q_rows;                  // rows of the q allocation (>= T)
+    int64_t pool_rows;           // rows of one layer's K (or V) pool = pages * hkv * page_size (or any bound >= it)
 };
+// 128 when the tcgen05 kernel (paged_attn_prefill_tc.cu) will take the launch, else 64.
+int b2_prefill_q_tile(const b2_ctx* ctx, int head_dim);
 int32_t b2_prefill_attn_launch(b2_ctx* ctx, const PrefillAttnParams& p, int head_dim, int grid_work);
+bool b2_prefill_attn_tc_eligible(const PrefillAttnParams& p, int head_dim);
+int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int grid_work);

@@ -200,9 +200,16 @@ __global__ void __launch_bounds__(kThreads) paged_attn_prefill_kernel(const Pref
 
 }  // namespace
 
+int b2_prefill_q_tile(const b2_ctx* ctx, int head_dim) { return ctx->use_tc && head_dim == 128 ? 128 : QT; }
+
 int32_t b2_prefill_attn_launch(b2_ctx* ctx, const PrefillAttnParams& p, int head_dim, int grid_work) {
     if (grid_work <= 0) return B2_OK;
     B2_REQUIRE(p.hkv > 0 && p.hq % p.hkv == 0, B2_ERR_MSG, "paged_attn_prefill: hq must be a multiple of hkv");
+    if (p.q_tile == 128) {
+        B2_REQUIRE(b2_prefill_attn_tc_eligible(p, head_dim), B2_ERR_UNSUPPORTED, "paged_attn_prefill: 128-query work items need head_dim 128 and 16-byte aligned operands");
+        return b2_prefill_attn_tc_launch(ctx, p, grid_work);
+    }
+    B2_REQUIRE(p.q_tile == QT, B2_ERR_MSG, "paged_attn_prefill: the work list was built for another tile size");
     dim3 grid(grid_work, p.hq);
     if (head_dim == 128) {
         const int smem = QT * 256 + 4 * KT * 256;

@@ -1,0 +1,480 @@
+// Chunked-prefill paged attention on the 5th-generation tensor cores (tcgen05 + TMEM), head_dim 128.
+//
+// Same contract as the warp-level kernel in paged_attn_prefill.cu (it replaces the whole-prompt prefill
+// attention of the reference: src/decode/continuous.rs:255 -> src/models/llama.rs:837-852 ->
+// src/primitives/attention.rs:68-102, bottom-right aligned causal mask attention.rs:31-39); this one takes
+// over for head_dim 128, where a long context makes the chunk's attention the largest item of a step.
+//
+// CTA = (128-query tile of one sequence's chunk, one q head), flash-attention over 128-key tiles:
+//   warp 4      one thread drives TMA: the Q tile once, then per key tile 16 boxes of 16 keys x 64 dims
+//               for K and 16 for V, each located through the block table (a page holds 16 keys of one
+//               kv head contiguously); boxes past the context are pointed outside the tensor and arrive
+//               as zeros
+//   warp 5      one thread issues tcgen05.mma: S = Q K^T (M 128 queries, N 128 keys, 8 steps of K = 16
+//               over head_dim) into one of two S buffers in TMEM, and O += P V (N = head_dim, 8 steps
+//               over the keys, V read as an MN-major operand straight from the page layout); P enters
+//               twice, as its bf16 head and its bf16 remainder, so the product keeps ~16 mantissa bits
+//   warps 0-3   softmax, thread = query row = TMEM lane: two passes over the row's 128 scores
+//               (maximum; then exp2, row sum, P written to shared memory in the K-major UMMA layout).
+//               The running maximum is raised only when a tile exceeds it by more than 2^8 ("lazy
+//               rescale"): P stays within bf16/f32 range, the final division by the row sum makes the
+//               result independent of the reference point, and the O accumulator in TMEM is touched
+//               (tcgen05.ld / st) only on those rare tiles.
+// S(j+1) is issued before the softmax of tile j has finished, so the tensor pipe always has the next
+// scores or the previous P V to work on.  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+constexpr int QT = 128, KT = 128, HD = 128;
+constexpr int kSoftmaxWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kThreads = 192;
+constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 64 bf16: one 128B-swizzled block
+constexpr int TILE_BYTES = 2 * HALF_BYTES;       // 128 x 128 bf16
+constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + 2 * TILE_BYTES, OFF_PH = OFF_V + 2 * TILE_BYTES, OFF_PL = OFF_PH + TILE_BYTES;
+constexpr int OFF_BAR = OFF_PL + TILE_BYTES;     // 224 KB of operands, then the barriers
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr uint32_t kSpinLimit = 64;
+constexpr float kRescaleThreshold = 8.0f;        // log2 units
+
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(addr), "r"(bytes) : "memory");
+}
+// Bounded wait; false when the limit (about 2 s) ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    long long start = 0;
+    while (true) {
+        for (uint32_t i = 0; i < kSpinLimit; i++) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}\n"
+                : "=r"(ok)
+                : "r"(addr), "r"(parity)
+                : "memory");
+            if (ok) return true;
+        }
+        const long long now = clock64();
+        if (start == 0) start = now;
+        if (now - start > 4000000000ll) return false;
+    }
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+        "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+        "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(mbar)
+        : "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart (SBO), descriptor version 1.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand, 128-byte swizzle: 64 contiguous MN elements per 128-byte row, one row per K index,
+// 8-row groups 1024 B apart (SBO), the next 64 MN elements 16 KB further (LBO).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)(HALF_BYTES >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// f32 accumulate, bf16 x bf16, M = 128, N = 128; bit 16 set = B is MN-major
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
+
+struct TcPrefillExtra {
+    int* err;
+    int oob_row;  // a row coordinate outside the K/V tensor maps: such boxes arrive as zeros
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+    paged_attn_prefill_tc_kernel(const PrefillAttnParams p, const TcPrefillExtra ex, const __grid_constant__ CUtensorMap map_q,
+                                 const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ uint8_t smem_raw[];
+    const int w = blockIdx.x;
+    if (w >= *p.n_work) return;
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t bar = base + OFF_BAR;
+    const uint32_t q_full = bar;
+    auto k_full = [&](int s) { return bar + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bar + 8u * (3 + s); };
+    auto v_full = [&](int s) { return bar + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bar + 8u * (7 + s); };
+    auto s_ready = [&](int s) { return bar + 8u * (9 + s); };
+    auto s_free = [&](int s) { return bar + 8u * (11 + s); };
+    const uint32_t p_ready = bar + 8u * 13, pv_done = bar + 8u * 14;
+    const uint32_t slot_addr = bar + 8u * 15;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw));
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.y, kvh = head / (p.hq / p.hkv);
+    const int b = p.pf_seq[w], q_start = p.pf_qstart[w];
+    const int tok0 = p.cu_seqlens[b], qn = p.cu_seqlens[b + 1] - tok0;
+    const int ctx = p.context_lens[b], ctx_before = ctx - qn;
+    const int rows = min(QT, qn - q_start);
+    const int page_size = p.page_tiles * 16;
+    const int last_q_pos = ctx_before + q_start + rows - 1;
+    const int n_tiles = last_q_pos / KT + 1;
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
+            mbar_init(s_ready(s), 1);
+            mbar_init(s_free(s), kSoftmaxWarps);
+        }
+        mbar_init(p_ready, kSoftmaxWarps);
+        mbar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot_addr), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256u;
+    bool alive = true;
+
+    if (warp == kTmaWarp) {
+        if (lane == 0) {
+            const int32_t* bt = p.block_tables + (size_t)p.seq_slot[b] * p.max_blocks;
+            mbar_expect_tx(q_full, TILE_BYTES);
+            tma_load_2d(base + OFF_Q, &map_q, head * HD, tok0 + q_start, q_full);
+            tma_load_2d(base + OFF_Q + HALF_BYTES, &map_q, head * HD + 64, tok0 + q_start, q_full);
+            for (int j = 0; j < n_tiles && alive; j++) {
+                const int st = j & 1;
+                const uint32_t par = (uint32_t)(j >> 1) & 1u;
+                // rows of the 8 sub-tiles (16 keys each) of this key tile in the pool's (page, kv head, slot) order
+                int row[8];
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    const int key0 = j * KT + s * 16;
+                    row[s] = ex.oob_row;
+                    if (key0 < ctx) row[s] = (__ldg(bt + key0 / page_size) * p.hkv + kvh) * page_size + key0 % page_size;
+                }
+                if (!mbar_wait(k_empty(st), par ^ 1u)) {
+                    alive = false;
+                    break;
+                }
+                mbar_expect_tx(k_full(st), TILE_BYTES);
+                const uint32_t kdst = base + OFF_K + st * TILE_BYTES;
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    tma_load_2d(kdst + s * 2048, &map_k, 0, row[s], k_full(st));
+                    tma_load_2d(kdst + HALF_BYTES + s * 2048, &map_k, 64, row[s], k_full(st));
+                }
+                if (!mbar_wait(v_empty(st), par ^ 1u)) {
+                    alive = false;
+                    break;
+                }
+                mbar_expect_tx(v_full(st), TILE_BYTES);
+                const uint32_t vdst = base + OFF_V + st * TILE_BYTES;
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    tma_load_2d(vdst + s * 2048, &map_v, 0, row[s], v_full(st));
+                    tma_load_2d(vdst + HALF_BYTES + s * 2048, &map_v, 64, row[s], v_full(st));
+                }
+            }
+            if (!alive) atomicExch(ex.err, 2);
+        }
+        __syncwarp();
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            auto issue_qk = [&](int j) {  // S[j & 1] = Q K_j^T
+                const int st = j & 1;
+                const uint32_t sQ = base + OFF_Q, sK = base + OFF_K + st * TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++) {
+                    const uint32_t off = (uint32_t)(k >> 2) * HALF_BYTES + (uint32_t)(k & 3) * 32;
+                    tc_mma(tmem_base + (uint32_t)st * 128u, desc_kmajor(sQ + off), desc_kmajor(sK + off), kIdescQK, k > 0 ? 1u : 0u);
+                }
+                tc_commit(s_ready(st));
+                tc_commit(k_empty(st));
+            };
+            alive = mbar_wait(q_full, 0) && mbar_wait(k_full(0), 0);
+            if (alive) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_tiles && alive; j++) {
+                if (j + 1 < n_tiles) {
+                    const int st = (j + 1) & 1;
+                    alive = mbar_wait(k_full(st), (uint32_t)((j + 1) >> 1) & 1u);
+                    // the softmax of tile j-1 has read the S buffer that tile j+1 is about to overwrite
+                    if (alive && j >= 1) alive = mbar_wait(s_free(st), (uint32_t)((j - 1) >> 1) & 1u);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                const int st = j & 1;
+                alive = mbar_wait(v_full(st), (uint32_t)(j >> 1) & 1u) && mbar_wait(p_ready, (uint32_t)j & 1u);
+                if (!alive) break;
+                tc_fence_after();
+                const uint32_t sV = base + OFF_V + st * TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < KT / 16; k++) {  // O += P_hi V + P_lo V, 16 keys per step
+                    const uint32_t poff = (uint32_t)(k >> 2) * HALF_BYTES + (uint32_t)(k & 3) * 32;
+                    const uint64_t dv = desc_mnmajor(sV + (uint32_t)k * 2048u);
+                    tc_mma(tmem_o, desc_kmajor(base + OFF_PH + poff), dv, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+                    tc_mma(tmem_o, desc_kmajor(base + OFF_PL + poff), dv, kIdescPV, 1u);
+                }
+                tc_commit(pv_done);
+                tc_commit(v_empty(st));
+            }
+            if (!alive) atomicExch(ex.err, 3);
+        }
+        __syncwarp();
+    } else {
+        // ---------------- softmax: thread = query row = TMEM lane ----------------
+        const int r = tid;  // 0..127
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const bool row_ok = r < rows;
+        // last key this row may see; rows past the chunk see the whole context (their result is dropped)
+        const int kvis = row_ok ? min(ctx_before + q_start + r, ctx - 1) : ctx - 1;
+        float m_run = -INFINITY, l_run = 0.f;
+        const uint32_t sw = (uint32_t)(r & 7);
+        const uint32_t p_row = (uint32_t)r * 128u;
+        for (int j = 0; j < n_tiles && alive; j++) {
+            const int st = j & 1;
+            const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)st * 128u;
+            if (!__all_sync(0xffffffffu, mbar_wait(s_ready(st), (uint32_t)(j >> 1) & 1u))) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            const int key_base = j * KT;
+            const bool need_mask = key_base + KT - 1 > kvis;
+            // pass 1: row maximum of the visible scores (log2 domain)
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tc_ld32(s_addr + (uint32_t)c * 32u, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float t = __uint_as_float(v[i]) * p.scale_log2;
+                    if (need_mask && key_base + c * 32 + i > kvis) t = -INFINITY;
+                    mx = fmaxf(mx, t);
+                }
+            }
+            // raise the reference point only when this tile exceeds it by more than the threshold
+            float alpha = 1.f;
+            bool rescale = false;
+            if (j == 0) {
+                m_run = mx;  // key 0 is visible to every row, so this is finite
+            } else if (mx > m_run + kRescaleThreshold) {
+                alpha = exp2f(m_run - mx);
+                m_run = mx;
+                rescale = true;
+            }
+            // P and O belong to the previous tile's P V until it has completed
+            if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(j - 1) & 1u))) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t v[32];
+                    tc_ld32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tc_st32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
+                }
+                l_run *= alpha;
+            }
+            // pass 2: P = exp2(s - m), row sum, bf16 head + remainder into the K-major operand layout
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tc_ld32(s_addr + (uint32_t)c * 32u, v);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {  // 8 keys = one 16-byte chunk
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float pv[2];
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const int i = g * 8 + e * 2 + h;
+                            float t = __uint_as_float(v[i]) * p.scale_log2;
+                            if (need_mask && key_base + c * 32 + i > kvis) t = -INFINITY;
+                            pv[h] = fast_exp2(t - m_run);
+                            l_run += pv[h];
+                        }
+                        hi[e] = pack_bf2(pv[0], pv[1]);
+                        lo[e] = pack_bf2(pv[0] - bflo(hi[e]), pv[1] - bfhi(hi[e]));
+                    }
+                    const int chunk = c * 4 + g;  // 16 chunks of 8 keys per row: 0-7 first key half, 8-15 second
+                    const uint32_t off = (uint32_t)(chunk >> 3) * HALF_BYTES + p_row + ((((uint32_t)chunk & 7u) ^ sw) << 4);
+                    sts128(base + OFF_PH + off, hi[0], hi[1], hi[2], hi[3]);
+                    sts128(base + OFF_PL + off, lo[0], lo[1], lo[2], lo[3]);
+                }
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_free(st));
+                mbar_arrive(p_ready);
+            }
+        }
+        // ---------------- output: O / l ----------------
+        if (alive && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u))) alive = false;
+        if (alive) {
+            tc_fence_after();
+            const float inv = 1.0f / l_run;
+            uint16_t* dst = p.out + ((size_t)(tok0 + q_start + (row_ok ? r : 0)) * p.hq + head) * HD;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tc_ld32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        uint4 o4;
+                        o4.x = pack_bf2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+                        o4.y = pack_bf2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+                        o4.z = pack_bf2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+                        o4.w = pack_bf2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o4;
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(ex.err, 4);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ---- tensor maps -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+struct MapEntry {
+    const void* ptr;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows;
+    int device;
+    CUtensorMap map;
+};
+// bf16 matrix [rows, cols] with row stride ld elements; box = 64 columns x box_rows, 128-byte swizzle, zero fill
+int32_t get_map(b2_ctx* ctx, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, CUtensorMap* out) {
+    static thread_local std::vector<MapEntry> cache;
+    for (auto& e : cache)
+        if (e.ptr == ptr && e.rows == rows && e.cols == cols && e.ld == ld && e.box_rows == box_rows && e.device == ctx->device) {
+            *out = e.map;
+            return B2_OK;
+        }
+    EncodeTiledFn fn = encode_fn();
+    B2_REQUIRE(fn != nullptr, B2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    B2_REQUIRE(((uintptr_t)ptr & 15) == 0 && (ld * 2) % 16 == 0, B2_ERR_UNSUPPORTED, "tcgen05 attention: operand must be 16-byte aligned");
+    if (cache.size() >= 1024) cache.clear();
+    MapEntry e{ptr, rows, cols, ld, box_rows, ctx->device, {}};
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(&e.map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B2_REQUIRE(r == CUDA_SUCCESS, B2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    cache.push_back(e);
+    *out = e.map;
+    return B2_OK;
+}
+
+}  // namespace
+
+bool b2_prefill_attn_tc_eligible(const PrefillAttnParams& p, int head_dim) {
+    return head_dim == 128 && p.pool_rows > 0 && p.q_rows > 0 && ((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.k_pool & 15) == 0 &&
+           ((uintptr_t)p.v_pool & 15) == 0;
+}
+
+// The work list (pf_seq / pf_qstart) must have been built with 128-query tiles.
+int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int grid_work) {
+    if (grid_work <= 0) return B2_OK;
+    B2_SMEM_ONCE(ctx, paged_attn_prefill_tc_kernel, SMEM_BYTES);
+    if (!ctx->dev_err) {
+        B2_CUDA(cudaMalloc((void**)&ctx->dev_err, 16));
+        B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, 16, ctx->stream));
+    }
+    CUtensorMap mq, mk, mv;
+    B2_CHECK(get_map(ctx, p.q, (uint64_t)p.q_rows, (uint64_t)p.hq * HD, (uint64_t)p.hq * HD, QT, &mq));
+    B2_CHECK(get_map(ctx, p.k_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mk));
+    B2_CHECK(get_map(ctx, p.v_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mv));
+    TcPrefillExtra ex{ctx->dev_err, (int)p.pool_rows};
+    dim3 grid(grid_work, p.hq);
+    paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv);
+    B2_LAUNCHED(ctx);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}

@@ -328,3 +328,46 @@ def test_attention_reference_shapes_f64_host(env):
         got = H.bf16_to_f32_np(out.download()).transpose(1, 0, 2)
         rel = np.abs(got - host).max() / (np.abs(host).max() + 1e-20)
         assert rel < 4e-3, (nh, nkv, ql, kl, hd, rel)  # 2e-3 of the reference + one bf16 output ulp (2^-8 relative)
+
+
+@pytest.mark.parametrize("hq,hkv,page", [(8, 2, 16), (4, 1, 32)])
+def test_prefill_attention_long_contexts_hd128(env, hq, hkv, page):
+    """head_dim 128 takes the tcgen05 kernel: many 128-key tiles per work item (ring phases wrap), chunks that end
+    inside a tile, several 128-query work items per sequence, contexts that are not multiples of the page."""
+    ctx, K, orc = env
+    q_lens = [300, 128, 129, 5, 512]
+    ctx_lens = [1500, 128, 700, 1031, 2048]
+    case = H.make_paged_case(21, ctx_lens, hq, hkv, 128, page, q_lens=q_lens)
+    kp, vp, bt, q = ctx.buf(case["kpool"]), ctx.buf(case["vpool"]), ctx.buf(case["block_tables"]), ctx.buf(case["q"])
+    out = ctx.empty(case["q"].shape, np.uint16)
+    K.paged_attn_prefill(ctx, q, kp, vp, bt, case["max_blocks"], case["cu_seqlens"], case["ctx_lens"], hq, hkv, 128, page, case["scale"], out)
+    ctx.sync()
+    ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"], case["ctx_lens"],
+                              case["scale"])
+    ok, err = H.close_bf16_out(out.download(), ref)
+    assert ok, f"max-abs {err}"
+
+
+def test_prefill_attention_rising_scores_hd128(env):
+    """Scores that keep growing along the context force the running maximum up by more than the lazy-rescale
+    threshold several times (the accumulator in TMEM is rescaled in place), and a peaked softmax exercises the
+    two-part P."""
+    ctx, K, orc = env
+    hq, hkv, hd, page = 4, 2, 128, 16
+    case = H.make_paged_case(22, [900], hq, hkv, hd, page, q_lens=[200])
+    # keys in logical order get a growing component along one direction that every query shares
+    kpool = H.bf16_to_f32_np(case["kpool"]).copy()
+    qf = H.bf16_to_f32_np(case["q"]).copy()
+    qf[:, :, 0] = 6.0
+    for pos in range(900):
+        pg, slot = case["block_tables"][0, pos // page], pos % page
+        kpool[pg, :, slot, 0] = 0.04 * pos  # score contribution 6 * 0.04 * pos / sqrt(128): ~19 units over the context
+    case["kpool"], case["q"] = H.f32_to_bf16_np(kpool), H.f32_to_bf16_np(qf)
+    kp, vp, bt, q = ctx.buf(case["kpool"]), ctx.buf(case["vpool"]), ctx.buf(case["block_tables"]), ctx.buf(case["q"])
+    out = ctx.empty(case["q"].shape, np.uint16)
+    K.paged_attn_prefill(ctx, q, kp, vp, bt, case["max_blocks"], case["cu_seqlens"], case["ctx_lens"], hq, hkv, hd, page, case["scale"], out)
+    ctx.sync()
+    ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"], case["ctx_lens"],
+                              case["scale"])
+    ok, err = H.close_bf16_out(out.download(), ref)
+    assert ok, f"max-abs {err}"
