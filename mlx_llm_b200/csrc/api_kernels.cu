@@ -295,7 +295,22 @@ int32_t b2_paged_attn_prefill(b2_ctx* ctx, const uint16_t* q_dev, const uint16_t
     p.out = out_dev;
     p.q_tile = q_tile;
     p.q_rows = cu_seqlens_host[num_seqs];
-    p.pool_rows = 1ll << 30;  // the pool's size is not an argument: any bound works, boxes are addressed through the block table
+    // the pool's size is not an argument: the largest page the block tables name bounds the rows that are read
+    {
+        std::vector<int32_t> bt((size_t)num_seqs * max_blocks);
+        B2_CUDA(cudaMemcpyAsync(bt.data(), block_tables_dev, bt.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        int32_t max_page = 0;
+        for (int i = 0; i < num_seqs; i++) {
+            const int used = (ctx_lens_host[i] + page_size - 1) / page_size;
+            B2_REQUIRE(used <= max_blocks, B2_ERR_MSG, "b2_paged_attn_prefill: a context needs more blocks than a block-table row holds");
+            for (int j = 0; j < used; j++) {
+                B2_REQUIRE(bt[(size_t)i * max_blocks + j] >= 0, B2_ERR_MSG, "b2_paged_attn_prefill: negative page in a block table");
+                max_page = std::max(max_page, bt[(size_t)i * max_blocks + j]);
+            }
+        }
+        p.pool_rows = ((int64_t)max_page + 1) * hkv * page_size;
+    }
     return b2_prefill_attn_launch(ctx, p, head_dim, P);
 }
 

@@ -153,10 +153,12 @@ int32_t set_local_dims(b2_model* m, b2_tp_group* tp) {
     const int world = tp ? tp->world : 1;
     B2_REQUIRE(!tp || tp->ctx == m->ctx, B2_ERR_MSG, "tensor-parallel group belongs to another context");
     B2_REQUIRE(c.num_kv_heads % world == 0, B2_ERR_UNSUPPORTED, "tensor parallelism: the group size must divide num_kv_heads");
-    B2_REQUIRE(c.intermediate_size % (64 * world) == 0, B2_ERR_UNSUPPORTED,
-               "tensor parallelism: every rank's slice of the MLP width must be a multiple of the quantization group (64)");
-    B2_REQUIRE((c.num_heads / world * c.head_dim) % 64 == 0, B2_ERR_UNSUPPORTED,
-               "tensor parallelism: every rank's slice of the attention width must be a multiple of 64");
+    if (world > 1) {
+        B2_REQUIRE(c.intermediate_size % (64 * world) == 0, B2_ERR_UNSUPPORTED,
+                   "tensor parallelism: every rank's slice of the MLP width must be a multiple of the quantization group (64)");
+        B2_REQUIRE((c.num_heads / world * c.head_dim) % 64 == 0, B2_ERR_UNSUPPORTED,
+                   "tensor parallelism: every rank's slice of the attention width must be a multiple of 64");
+    }
     m->tp = world > 1 ? tp : nullptr;
     m->hq_l = c.num_heads / world;
     m->hkv_l = c.num_kv_heads / world;

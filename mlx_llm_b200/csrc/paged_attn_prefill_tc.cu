@@ -6,10 +6,9 @@
 // over for head_dim 128, where a long context makes the chunk's attention the largest item of a step.
 //
 // CTA = (128-query tile of one sequence's chunk, one q head), flash-attention over 128-key tiles:
-//   warp 4      one thread drives TMA: the Q tile once, then per key tile 16 boxes of 16 keys x 64 dims
+//   warp 4      one thread drives TMA: the Q tile once (16-row boxes), then per key tile 16 boxes of 16 keys x 64 dims
 //               for K and 16 for V, each located through the block table (a page holds 16 keys of one
-//               kv head contiguously); boxes past the context are pointed outside the tensor and arrive
-//               as zeros
+//               kv head contiguously); boxes past the context are filled from a page of zeros
 //   warp 5      one thread issues tcgen05.mma: S = Q K^T (M 128 queries, N 128 keys, 8 steps of K = 16
 //               over head_dim) into one of two S buffers in TMEM, and O += P V (N = head_dim, 8 steps
 //               over the keys, V read as an MN-major operand straight from the page layout); P enters
@@ -128,12 +127,14 @@ constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 
 struct TcPrefillExtra {
     int* err;
-    int oob_row;  // a row coordinate outside the K/V tensor maps: such boxes arrive as zeros
+    int oob_row;  // marks a 16-key box past the context: it is filled from a page of zeros
+    int q_box;    // rows per Q box: 16, or the largest power of two that the q tensor's row count allows
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
     paged_attn_prefill_tc_kernel(const PrefillAttnParams p, const TcPrefillExtra ex, const __grid_constant__ CUtensorMap map_q,
-                                 const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+                                 const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                 const __grid_constant__ CUtensorMap map_zero) {
     extern __shared__ uint8_t smem_raw[];
     const int w = blockIdx.x;
     if (w >= *p.n_work) return;
@@ -189,9 +190,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == kTmaWarp) {
         if (lane == 0) {
             const int32_t* bt = p.block_tables + (size_t)p.seq_slot[b] * p.max_blocks;
-            mbar_expect_tx(q_full, TILE_BYTES);
-            tma_load_2d(base + OFF_Q, &map_q, head * HD, tok0 + q_start, q_full);
-            tma_load_2d(base + OFF_Q + HALF_BYTES, &map_q, head * HD + 64, tok0 + q_start, q_full);
+            // the Q tile in boxes of 16 rows, only as many as the chunk has rows (a box never starts outside the
+            // tensor; the rows of the tile that stay unwritten belong to queries whose results are dropped)
+            const int q_boxes = (rows + ex.q_box - 1) / ex.q_box;
+            const uint32_t q_box_bytes = (uint32_t)ex.q_box * 128u;
+            mbar_expect_tx(q_full, (uint32_t)q_boxes * 2u * q_box_bytes);
+            for (int qb = 0; qb < q_boxes; qb++) {
+                tma_load_2d(base + OFF_Q + qb * q_box_bytes, &map_q, head * HD, tok0 + q_start + qb * ex.q_box, q_full);
+                tma_load_2d(base + OFF_Q + HALF_BYTES + qb * q_box_bytes, &map_q, head * HD + 64, tok0 + q_start + qb * ex.q_box, q_full);
+            }
             for (int j = 0; j < n_tiles && alive; j++) {
                 const int st = j & 1;
                 const uint32_t par = (uint32_t)(j >> 1) & 1u;
@@ -201,7 +208,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int s = 0; s < 8; s++) {
                     const int key0 = j * KT + s * 16;
                     row[s] = ex.oob_row;
-                    if (key0 < ctx) row[s] = (__ldg(bt + key0 / page_size) * p.hkv + kvh) * page_size + key0 % page_size;
+                    if (key0 < ctx) {
+                        const int blk = key0 / page_size;
+                        if (blk >= p.max_blocks) {  // self-check: never index past the block-table row
+                            atomicExch(ex.err, 5);
+                        } else {
+                            const long rr = ((long)__ldg(bt + blk) * p.hkv + kvh) * page_size + key0 % page_size;
+                            if (rr < 0 || rr + 16 > p.pool_rows)
+                                atomicExch(ex.err, 6);  // a page outside the pool: skip the access
+                            else
+                                row[s] = (int)rr;
+                        }
+                    }
                 }
                 if (!mbar_wait(k_empty(st), par ^ 1u)) {
                     alive = false;
@@ -211,8 +229,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t kdst = base + OFF_K + st * TILE_BYTES;
 #pragma unroll
                 for (int s = 0; s < 8; s++) {
-                    tma_load_2d(kdst + s * 2048, &map_k, 0, row[s], k_full(st));
-                    tma_load_2d(kdst + HALF_BYTES + s * 2048, &map_k, 64, row[s], k_full(st));
+                    const bool past = row[s] == ex.oob_row;
+                    tma_load_2d(kdst + s * 2048, past ? &map_zero : &map_k, 0, past ? 0 : row[s], k_full(st));
+                    tma_load_2d(kdst + HALF_BYTES + s * 2048, past ? &map_zero : &map_k, 64, past ? 0 : row[s], k_full(st));
                 }
                 if (!mbar_wait(v_empty(st), par ^ 1u)) {
                     alive = false;
@@ -222,8 +241,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t vdst = base + OFF_V + st * TILE_BYTES;
 #pragma unroll
                 for (int s = 0; s < 8; s++) {
-                    tma_load_2d(vdst + s * 2048, &map_v, 0, row[s], v_full(st));
-                    tma_load_2d(vdst + HALF_BYTES + s * 2048, &map_v, 64, row[s], v_full(st));
+                    const bool past = row[s] == ex.oob_row;
+                    tma_load_2d(vdst + s * 2048, past ? &map_zero : &map_v, 0, past ? 0 : row[s], v_full(st));
+                    tma_load_2d(vdst + HALF_BYTES + s * 2048, past ? &map_zero : &map_v, 64, past ? 0 : row[s], v_full(st));
                 }
             }
             if (!alive) atomicExch(ex.err, 2);
@@ -381,7 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int c = 0; c < 4; c++) {
                 uint32_t v[32];
                 tc_ld32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
-                if (row_ok) {
+                if (row_ok && tok0 + q_start + r < p.q_rows) {
 #pragma unroll
                     for (int g = 0; g < 4; g++) {
                         uint4 o4;
@@ -467,13 +487,24 @@ int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int g
         B2_CUDA(cudaMalloc((void**)&ctx->dev_err, 16));
         B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, 16, ctx->stream));
     }
-    CUtensorMap mq, mk, mv;
-    B2_CHECK(get_map(ctx, p.q, (uint64_t)p.q_rows, (uint64_t)p.hq * HD, (uint64_t)p.hq * HD, QT, &mq));
+    // a page of zeros for the 16-key boxes that lie past a sequence's context
+    static thread_local void* zero_page[16] = {};
+    void*& zp = zero_page[ctx->device & 15];
+    if (!zp) {
+        B2_CUDA(cudaMalloc(&zp, 16 * HD * 2));
+        B2_CUDA(cudaMemsetAsync(zp, 0, 16 * HD * 2, ctx->stream));
+    }
+    CUtensorMap mq, mk, mv, mz;
+    B2_CHECK(get_map(ctx, zp, 16, HD, HD, 16, &mz));
+    // a box is never taller than the tensor it reads
+    int q_box = 16;
+    while (q_box > p.q_rows) q_box >>= 1;
+    B2_CHECK(get_map(ctx, p.q, (uint64_t)p.q_rows, (uint64_t)p.hq * HD, (uint64_t)p.hq * HD, (uint32_t)q_box, &mq));
     B2_CHECK(get_map(ctx, p.k_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mk));
     B2_CHECK(get_map(ctx, p.v_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mv));
-    TcPrefillExtra ex{ctx->dev_err, (int)p.pool_rows};
+    TcPrefillExtra ex{ctx->dev_err, -1, q_box};
     dim3 grid(grid_work, p.hq);
-    paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv);
+    paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv, mz);
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
