@@ -6,15 +6,16 @@
 // over for head_dim 128, where a long context makes the chunk's attention the largest item of a step.
 //
 // CTA = (128-query tile of one sequence's chunk, one q head), flash-attention over 128-key tiles:
-//   warp 4      one thread drives TMA: the Q tile once (16-row boxes), then per key tile 16 boxes of 16 keys x 64 dims
+//   warp 8      one thread drives TMA: the Q tile once, then per key tile 16 boxes of 16 keys x 64 dims
 //               for K and 16 for V, each located through the block table (a page holds 16 keys of one
 //               kv head contiguously); boxes past the context are filled from a page of zeros
-//   warp 5      one thread issues tcgen05.mma: S = Q K^T (M 128 queries, N 128 keys, 8 steps of K = 16
+//   warp 9      one thread issues tcgen05.mma: S = Q K^T (M 128 queries, N 128 keys, 8 steps of K = 16
 //               over head_dim) into one of two S buffers in TMEM, and O += P V (N = head_dim, 8 steps
 //               over the keys, V read as an MN-major operand straight from the page layout); P enters
 //               twice, as its bf16 head and its bf16 remainder, so the product keeps ~16 mantissa bits
-//   warps 0-3   softmax, thread = query row = TMEM lane: two passes over the row's 128 scores
-//               (maximum; then exp2, row sum, P written to shared memory in the K-major UMMA layout).
+//   warps 0-7   softmax, thread = (query row = TMEM lane, half of the key tile): two passes over its 64
+//               scores (maximum, exchanged with the row's other thread through shared memory; then exp2, row
+//               sum, P written to shared memory in the K-major UMMA layout).
 //               The running maximum is raised only when a tile exceeds it by more than 2^8 ("lazy
 //               rescale"): P stays within bf16/f32 range, the final division by the row sum makes the
 //               result independent of the reference point, and the O accumulator in TMEM is touched
@@ -29,12 +30,13 @@
 namespace {
 
 constexpr int QT = 128, KT = 128, HD = 128;
-constexpr int kSoftmaxWarps = 4, kTmaWarp = 4, kMmaWarp = 5, kThreads = 192;
+constexpr int kSoftmaxWarps = 8, kTmaWarp = 8, kMmaWarp = 9, kThreads = 320;
 constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 64 bf16: one 128B-swizzled block
 constexpr int TILE_BYTES = 2 * HALF_BYTES;       // 128 x 128 bf16
 constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + 2 * TILE_BYTES, OFF_PH = OFF_V + 2 * TILE_BYTES, OFF_PL = OFF_PH + TILE_BYTES;
-constexpr int OFF_BAR = OFF_PL + TILE_BYTES;     // 224 KB of operands, then the barriers
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr int OFF_BAR = OFF_PL + TILE_BYTES;     // 224 KB of operands, then 256 B of barriers
+constexpr int OFF_X = OFF_BAR + 256;             // row-maximum / row-sum exchange between the two softmax groups
+constexpr int SMEM_BYTES = OFF_X + 2048;         // dynamic shared memory must start 1024-byte aligned (checked)
 constexpr uint32_t kSpinLimit = 64;
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
@@ -128,18 +130,22 @@ constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 struct TcPrefillExtra {
     int* err;
     int oob_row;  // marks a 16-key box past the context: it is filled from a page of zeros
-    int q_box;    // rows per Q box: 16, or the largest power of two that the q tensor's row count allows
+    int q_box;    // rows per Q box: 128, or the largest power of two that the q tensor's row count allows
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
     paged_attn_prefill_tc_kernel(const PrefillAttnParams p, const TcPrefillExtra ex, const __grid_constant__ CUtensorMap map_q,
                                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                  const __grid_constant__ CUtensorMap map_zero) {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int w = blockIdx.x;
     if (w >= *p.n_work) return;
     const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
+    if (raw & 1023u) {  // the swizzled operand layouts need this alignment; every thread sees the same value
+        if (threadIdx.x == 0) atomicExch(ex.err, 7);
+        return;
+    }
+    const uint32_t base = raw;
     const uint32_t bar = base + OFF_BAR;
     const uint32_t q_full = bar;
     auto k_full = [&](int s) { return bar + 8u * (1 + s); };
@@ -149,7 +155,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     auto s_ready = [&](int s) { return bar + 8u * (9 + s); };
     auto s_free = [&](int s) { return bar + 8u * (11 + s); };
     const uint32_t p_ready = bar + 8u * 13, pv_done = bar + 8u * 14;
-    const uint32_t slot_addr = bar + 8u * 15;
+    auto x_ready = [&](int s) { return bar + 8u * (15 + s); };  // both softmax groups have published their maxima
+    const uint32_t l_ready = bar + 8u * 17;
+    const uint32_t slot_addr = bar + 8u * 18;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -171,7 +179,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(v_empty(s), 1);
             mbar_init(s_ready(s), 1);
             mbar_init(s_free(s), kSoftmaxWarps);
+            mbar_init(x_ready(s), kSoftmaxWarps);
         }
+        mbar_init(l_ready, kSoftmaxWarps);
         mbar_init(p_ready, kSoftmaxWarps);
         mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -190,8 +200,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == kTmaWarp) {
         if (lane == 0) {
             const int32_t* bt = p.block_tables + (size_t)p.seq_slot[b] * p.max_blocks;
-            // the Q tile in boxes of 16 rows, only as many as the chunk has rows (a box never starts outside the
-            // tensor; the rows of the tile that stay unwritten belong to queries whose results are dropped)
+            // the Q tile in as few boxes as the q tensor's height allows (a box is never taller than the tensor and
+            // never starts outside it; rows of the tile that stay unwritten belong to queries whose results are dropped)
             const int q_boxes = (rows + ex.q_box - 1) / ex.q_box;
             const uint32_t q_box_bytes = (uint32_t)ex.q_box * 128u;
             mbar_expect_tx(q_full, (uint32_t)q_boxes * 2u * q_box_bytes);
@@ -199,28 +209,40 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tma_load_2d(base + OFF_Q + qb * q_box_bytes, &map_q, head * HD, tok0 + q_start + qb * ex.q_box, q_full);
                 tma_load_2d(base + OFF_Q + HALF_BYTES + qb * q_box_bytes, &map_q, head * HD + 64, tok0 + q_start + qb * ex.q_box, q_full);
             }
+            // page of each of the 8 sub-tiles (16 keys) of a key tile; the index is clamped to the block-table row so
+            // the eight loads are unconditional and in flight together, one tile ahead of their use
+            auto load_pages = [&](int j, int (&pg)[8]) {
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    const int blk = (j * KT + s * 16) / page_size;
+                    pg[s] = __ldg(bt + (blk < p.max_blocks ? blk : p.max_blocks - 1));
+                }
+            };
+            int pg[8], pg_next[8];
+            load_pages(0, pg);
             for (int j = 0; j < n_tiles && alive; j++) {
                 const int st = j & 1;
                 const uint32_t par = (uint32_t)(j >> 1) & 1u;
-                // rows of the 8 sub-tiles (16 keys each) of this key tile in the pool's (page, kv head, slot) order
+                if (j + 1 < n_tiles) load_pages(j + 1, pg_next);
+                // rows of the sub-tiles in the pool's (page, kv head, slot) order; self-checks: never past the
+                // block-table row, never outside the pool
                 int row[8];
 #pragma unroll
                 for (int s = 0; s < 8; s++) {
                     const int key0 = j * KT + s * 16;
                     row[s] = ex.oob_row;
                     if (key0 < ctx) {
-                        const int blk = key0 / page_size;
-                        if (blk >= p.max_blocks) {  // self-check: never index past the block-table row
+                        const long rr = ((long)pg[s] * p.hkv + kvh) * page_size + key0 % page_size;
+                        if (key0 / page_size >= p.max_blocks)
                             atomicExch(ex.err, 5);
-                        } else {
-                            const long rr = ((long)__ldg(bt + blk) * p.hkv + kvh) * page_size + key0 % page_size;
-                            if (rr < 0 || rr + 16 > p.pool_rows)
-                                atomicExch(ex.err, 6);  // a page outside the pool: skip the access
-                            else
-                                row[s] = (int)rr;
-                        }
+                        else if (rr < 0 || rr + 16 > p.pool_rows)
+                            atomicExch(ex.err, 6);
+                        else
+                            row[s] = (int)rr;
                     }
                 }
+#pragma unroll
+                for (int s = 0; s < 8; s++) pg[s] = pg_next[s];
                 if (!mbar_wait(k_empty(st), par ^ 1u)) {
                     alive = false;
                     break;
@@ -296,29 +318,32 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
     } else {
-        // ---------------- softmax: thread = query row = TMEM lane ----------------
-        const int r = tid;  // 0..127
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        // ---------------- softmax: thread = (query row = TMEM lane, half of the key tile) ----------------
+        // warps 0-3 take keys 0-63 of every tile, warps 4-7 keys 64-127 (a warp reaches the TMEM lanes
+        // 32 * (warp % 4) ..); the two threads of a row agree on the row maximum through shared memory
+        const int wg = warp >> 2, r = tid & 127;
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const bool row_ok = r < rows;
         // last key this row may see; rows past the chunk see the whole context (their result is dropped)
         const int kvis = row_ok ? min(ctx_before + q_start + r, ctx - 1) : ctx - 1;
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's half of the row sum
         const uint32_t sw = (uint32_t)(r & 7);
         const uint32_t p_row = (uint32_t)r * 128u;
+        volatile float* xb = reinterpret_cast<volatile float*>(smem_raw + OFF_X);  // [2 tiles in flight][2 groups][128 rows]
         for (int j = 0; j < n_tiles && alive; j++) {
             const int st = j & 1;
-            const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)st * 128u;
+            const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)st * 128u + (uint32_t)wg * 64u;
             if (!__all_sync(0xffffffffu, mbar_wait(s_ready(st), (uint32_t)(j >> 1) & 1u))) {
                 alive = false;
                 break;
             }
             tc_fence_after();
-            const int key_base = j * KT;
-            const bool need_mask = key_base + KT - 1 > kvis;
-            // pass 1: row maximum of the visible scores (log2 domain)
+            const int key_base = j * KT + wg * 64;
+            const bool need_mask = key_base + 63 > kvis;
+            // pass 1: maximum of this half's visible scores (log2 domain), then of the whole row
             float mx = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t v[32];
                 tc_ld32(s_addr + (uint32_t)c * 32u, v);
 #pragma unroll
@@ -328,6 +353,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                     mx = fmaxf(mx, t);
                 }
             }
+            xb[(st * 2 + wg) * 128 + r] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_ready(st));  // (release: the maxima above are visible to whoever sees the phase complete)
+            if (!__all_sync(0xffffffffu, mbar_wait(x_ready(st), (uint32_t)(j >> 1) & 1u))) {
+                alive = false;
+                break;
+            }
+            mx = fmaxf(mx, xb[(st * 2 + (wg ^ 1)) * 128 + r]);
             // raise the reference point only when this tile exceeds it by more than the threshold
             float alpha = 1.f;
             bool rescale = false;
@@ -344,20 +377,21 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after();
-            if (__any_sync(0xffffffffu, rescale)) {
+            if (__any_sync(0xffffffffu, rescale)) {  // this group rescales its half of the head dimension
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < 2; c++) {
+                    const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)wg * 64u + (uint32_t)c * 32u;
                     uint32_t v[32];
-                    tc_ld32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
+                    tc_ld32(o_addr, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tc_st32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
+                    tc_st32(o_addr, v);
                 }
-                l_run *= alpha;
             }
+            l_run *= alpha;
             // pass 2: P = exp2(s - m), row sum, bf16 head + remainder into the K-major operand layout
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t v[32];
                 tc_ld32(s_addr + (uint32_t)c * 32u, v);
 #pragma unroll
@@ -377,8 +411,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                         hi[e] = pack_bf2(pv[0], pv[1]);
                         lo[e] = pack_bf2(pv[0] - bflo(hi[e]), pv[1] - bfhi(hi[e]));
                     }
-                    const int chunk = c * 4 + g;  // 16 chunks of 8 keys per row: 0-7 first key half, 8-15 second
-                    const uint32_t off = (uint32_t)(chunk >> 3) * HALF_BYTES + p_row + ((((uint32_t)chunk & 7u) ^ sw) << 4);
+                    // 16 chunks of 8 keys per row: this group's 8 chunks form one 128-byte row of its key half
+                    const uint32_t off = (uint32_t)wg * HALF_BYTES + p_row + ((((uint32_t)(c * 4 + g)) ^ sw) << 4);
                     sts128(base + OFF_PH + off, hi[0], hi[1], hi[2], hi[3]);
                     sts128(base + OFF_PL + off, lo[0], lo[1], lo[2], lo[3]);
                 }
@@ -391,16 +425,25 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mbar_arrive(p_ready);
             }
         }
-        // ---------------- output: O / l ----------------
+        // ---------------- output: O / l, each group its half of the head dimension ----------------
         if (alive && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u))) alive = false;
+        // the row sum is the two halves' sums (slot of the tile parity that is not in use any more)
+        if (alive) {
+            const int slot = n_tiles & 1;
+            xb[(slot * 2 + wg) * 128 + r] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(l_ready);
+            if (!__all_sync(0xffffffffu, mbar_wait(l_ready, 0))) alive = false;
+            l_run += xb[(slot * 2 + (wg ^ 1)) * 128 + r];
+        }
         if (alive) {
             tc_fence_after();
             const float inv = 1.0f / l_run;
-            uint16_t* dst = p.out + ((size_t)(tok0 + q_start + (row_ok ? r : 0)) * p.hq + head) * HD;
+            uint16_t* dst = p.out + ((size_t)(tok0 + q_start + (row_ok ? r : 0)) * p.hq + head) * HD + wg * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t v[32];
-                tc_ld32(tmem_o + lane_addr + (uint32_t)c * 32u, v);
+                tc_ld32(tmem_o + lane_addr + (uint32_t)wg * 64u + (uint32_t)c * 32u, v);
                 if (row_ok && tok0 + q_start + r < p.q_rows) {
 #pragma unroll
                     for (int g = 0; g < 4; g++) {
@@ -497,7 +540,7 @@ int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int g
     CUtensorMap mq, mk, mv, mz;
     B2_CHECK(get_map(ctx, zp, 16, HD, HD, 16, &mz));
     // a box is never taller than the tensor it reads
-    int q_box = 16;
+    int q_box = QT;
     while (q_box > p.q_rows) q_box >>= 1;
     B2_CHECK(get_map(ctx, p.q, (uint64_t)p.q_rows, (uint64_t)p.hq * HD, (uint64_t)p.hq * HD, (uint32_t)q_box, &mq));
     B2_CHECK(get_map(ctx, p.k_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mk));
