@@ -88,6 +88,17 @@ class ClockSampler:
                     samples=len(sm))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures whose
+# summaries (with the commands) are under profiles/
+NCU_TRAFFIC = dict(
+    gemm_gate_up_launch=95.4e6,
+    gemm_note="gate+up projection launch of gemm_tc_pair_kernel<4,0> (N 28672, K 4096) at ~570 tokens in the 2-layer capture; "
+              "algorithmic 66.1 MB of packed weights + activations/outputs that mostly stay in L2",
+    attn_decode_config1_launch=578.4e6,
+    attn_note="paged_attn_decode_kernel<128> on the configuration-1 batch (algorithmic 565.0 MB)",
+)
+
+
 # ------------------------------------------------------------------------------------------------
 # BASELINE configuration 3: Llama-3-8B-architecture Q4 continuous batching
 def continuous_setup(args, rank, world, local_rank):
@@ -200,7 +211,8 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
                     l2="per-step working set (weights + KV) exceeds L2",
                     prefill_tokens_per_step=pre / max(steps, 1), generated_tokens_per_step=gen / max(steps, 1)),
         roofline=dict(bound="tensor", achieved=tfl, peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
-                      frac=tfl / peaks["bf16_tflops_sustained"], traffic=None, peak_source=peaks["source"] + " (sustained)",
+                      frac=tfl / peaks["bf16_tflops_sustained"], traffic=None if tp_mode else NCU_TRAFFIC["gemm_gate_up_launch"],
+                      traffic_note=None if tp_mode else NCU_TRAFFIC["gemm_note"], peak_source=peaks["source"] + " (sustained)",
                       kernel=("projection GEMMs (Q8 dequant fused) + bf16 lm_head" if tp_mode else "projection GEMMs (Q4 dequant fused) + bf16 lm_head"), launches_per_step=prof["launches"]["gemm"] / prof_steps,
                       ms_per_step=gemm_ms / prof_steps, share_of_step=gemm_ms / total_prof_ms if total_prof_ms else None,
                       algorithmic_flops_per_step=prof["gemm_flops"] / prof_steps),
@@ -324,7 +336,8 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_su
         vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload="paged_attn_decode (BASELINE configuration 1): 64 seqs, 32q/8kv heads, hd 128, page 16, ctx U[128,4096]",
                     l2="flushed between timed iterations", parallelism=f"replica x{world}", chunk_tokens=args.chunk_tokens or 512),
-        roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"], traffic=None,
+        roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"],
+                      traffic=NCU_TRAFFIC["attn_decode_config1_launch"], traffic_note=NCU_TRAFFIC["attn_note"],
                       peak_source=peaks["source"], algorithmic_bytes=alg, kernel="paged_attn_decode_kernel<128> (+ work list, merge)"),
         e2e=dict(value=n * world / (t_e2e / args.steps * 1e-3), unit="tok/s", h2d_bytes_per_step=case["q"].nbytes,
                  d2h_bytes_per_step=case["q"].nbytes),
