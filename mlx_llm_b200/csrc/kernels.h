@@ -47,6 +47,9 @@ struct GemmParams {
     float* out_f32;          // EPI_F32
 };
 int32_t b2_gemm_launch(b2_ctx* ctx, const GemmParams& p);
+// weight-streaming kernel for up to 64 tokens (gemm_stream.cu): taken by b2_gemm_launch when eligible.
+bool b2_gemm_stream_eligible(const GemmParams& p);
+int32_t b2_gemm_stream_launch(b2_ctx* ctx, const GemmParams& p);
 // tcgen05 / TMEM path, CTA-pair form (gemm_tc.cu): taken by b2_gemm_launch when eligible.
 bool b2_gemm_tc_eligible(const GemmParams& p);
 int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p);

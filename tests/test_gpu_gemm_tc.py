@@ -75,3 +75,48 @@ def test_tc_matches_warp_level_kernel(env):
         outs.append(y.download())
     _lib.check(_lib.load().b2_ctx_set_tensor_path(ctx.h, 1))
     assert np.abs(outs[0] - outs[1]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("bits", [4, 8, 0])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (5, 256, 512), (8, 1024, 4096), (9, 128, 1024), (16, 384, 2048), (33, 256, 4096),
+                                   (64, 512, 1024), (3, 128, 14336)])
+def test_stream_gemm_vs_oracle(env, bits, m, n, k):
+    """Up to 64 tokens with N a multiple of 128 and K of 256 take the weight-streaming kernel: every token-tile
+    count (8, 16, 32, 64 wide), one and several K ranges, ragged token counts."""
+    ctx, K, orc, _lib = env
+    rng = np.random.default_rng(7 * m + n + k)
+    x = H.f32_to_bf16_np(rng.standard_normal((m, k)).astype(np.float32))
+    dx = ctx.buf(x)
+    yb, yf = ctx.empty((m, n), np.uint16), ctx.empty((m, n), np.float32)
+    if bits:
+        packed, scales, biases = quant_case(3, n, k, bits)
+        K.qmm(ctx, dx, ctx.buf(packed), ctx.buf(scales), ctx.buf(biases), m, n, k, bits, yb, yf)
+        rf, _ = orc.qmm(x, packed, scales, biases, 64, bits)
+    else:
+        w = H.f32_to_bf16_np(rng.standard_normal((n, k)).astype(np.float32) * 0.03)
+        K.linear(ctx, dx, ctx.buf(w), m, n, k, yb, yf)
+        rf, _ = orc.linear(x, w)
+    ctx.sync()
+    got = yf.download()
+    assert np.isfinite(got).all()
+    assert np.abs(got - rf).max() <= 2e-3, f"max-abs {np.abs(got - rf).max()}"
+    assert H.close_bf16_out(yb.download(), rf)[0]
+
+
+def test_stream_matches_tile_kernel(env):
+    """Same bf16 weights, f32 accumulation: the streaming kernel and the tile kernel agree to summation-order noise."""
+    ctx, K, orc, _lib = env
+    m, n, k = 7, 512, 4096
+    rng = np.random.default_rng(1)
+    x = H.f32_to_bf16_np(rng.standard_normal((m, k)).astype(np.float32))
+    packed, scales, biases = quant_case(4, n, k, 4)
+    dx, dp, ds, db = ctx.buf(x), ctx.buf(packed), ctx.buf(scales), ctx.buf(biases)
+    outs = []
+    for fast in (1, 0):
+        _lib.check(_lib.load().b2_ctx_set_tensor_path(ctx.h, fast))
+        y = ctx.empty((m, n), np.float32)
+        K.qmm(ctx, dx, dp, ds, db, m, n, k, 4, None, y)
+        ctx.sync()
+        outs.append(y.download())
+    _lib.check(_lib.load().b2_ctx_set_tensor_path(ctx.h, 1))
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-4
