@@ -222,6 +222,14 @@ int32_t b2_weights_add(b2_weights* w, const char* name, int32_t dtype, const int
 int32_t b2_weights_contains(const b2_weights* w, const char* name);        /* Weights::contains */
 int32_t b2_weights_free(b2_weights* w);
 
+/* write_snapshot (src/snapshot.rs:86-148): writes `out_dir/model.safetensors` + `out_dir/config.json` from a dense,
+ * Hugging-Face-keyed tensor set.  With a QuantSpec every attention / MLP projection (PROJECTION_SUFFIXES,
+ * snapshot.rs:41-49) is cast to bf16, quantized on the GPU to MLX group-64 Q4 / Q8 and stored as the packed triplet
+ * `<base>.weight` (u32) / `.scales` / `.biases` (bf16); everything else is written through unchanged and config.json
+ * gains the `quantization` block that makes loaders read the triplets as stored (src/models/llama.rs:77-95).
+ * quant == NULL writes a dense snapshot.  *num_tensors_out (nullable) = tensors written (a triplet counts three). */
+int32_t b2_write_snapshot(b2_ctx* ctx, const b2_weights* w, const char* config_json, const b2_quant_spec* quant /* nullable */,
+                          const char* out_dir, int32_t* num_tensors_out);
 /* ModelConfig::from_json (src/config.rs:315-502) for the Llama/Qwen3 subset. */
 int32_t b2_model_config_from_json(const char* json, b2_model_config* out);
 /* CausalLm::from_weights_with (src/models/llama.rs:57-303): every tensor is cast to bf16 (:71);

@@ -192,6 +192,16 @@ class CausalLm:
             self.h = C.c_void_p()
 
 
+def write_snapshot(ctx, weights, config_json, out_dir, quant: Optional[QuantSpec] = None):
+    """write_snapshot (src/snapshot.rs:86-148): dense tensors -> out_dir/{model.safetensors, config.json}, the
+    projections re-quantized to MLX Q4/Q8 triplets when `quant` is given.  Returns the number of tensors written."""
+    n = C.c_int32(0)
+    q = C.byref(CQuantSpec(quant.group_size, quant.bits)) if quant else None
+    cfg = config_json if isinstance(config_json, str) else json.dumps(config_json)
+    check(load().b2_write_snapshot(ctx.h, weights.h, cfg.encode(), q, str(out_dir).encode(), C.byref(n)))
+    return n.value
+
+
 class TpGroup:
     """Tensor-parallel group of one rank per GPU (b2_tp_group_*): rank 0 draws the id with
     TpGroup.unique_id(), the caller distributes those 128 bytes, every rank constructs its group."""
