@@ -348,6 +348,70 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     return out
 
 
+# ------------------------------------------------------------------------------------------------
+# Decode-only iterations (no prefill in the batch): the weight-streaming regime of low-concurrency serving
+def run_decode_only(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
+    from mlx_llm_b200 import _lib, engine as eng, workloads as wl
+
+    shape = dict(wl.LLAMA3_8B if args.layers <= 0 else dict(wl.LLAMA3_8B, num_layers=args.layers))
+    ctx = _lib.Context(local_rank)
+    model = eng.CausalLm.synthetic(ctx, eng.model_config(**shape, quant_bits=4, quant_group=64), seed=0)
+    B = args.max_batch if args.max_batch != 256 else 8
+    rng = np.random.default_rng(rank)
+    warm = max(args.warmup, 3)
+    reqs = [eng.BatchRequest(rng.integers(0, 1000, size=32, dtype=np.int32), args.steps + warm + args.profile_steps + 64) for _ in range(B)]
+    ccfg = eng.ContinuousConfig(max_batch=B, block_size=16, exactness=eng.THROUGHPUT, prefill_chunk_tokens=args.chunk, max_pages=4096,
+                                max_blocks_per_seq=256)
+    engine = eng.ContinuousEngine(model, reqs, ccfg)
+    done, st = engine.step(8)          # the prompts (one chunk) and a few decode iterations, untimed
+    done, st = engine.step(warm)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    if args.profiler_range:
+        ctx.profiler_range(True)
+    t0 = time.perf_counter()
+    done, s1 = engine.step(args.steps)
+    ctx.sync()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    if args.profiler_range:
+        ctx.profiler_range(False)
+    barrier()
+    clocks = sampler.stop()
+    steps = s1["steps"] - st["steps"]
+    gen = s1["decode_tokens"] - st["decode_tokens"]
+    dev_ms = s1["device_ms"] - st["device_ms"]
+    eng.profile_enable(ctx, True)
+    p0 = engine.step(0)[1]
+    done, p1 = engine.step(args.profile_steps)
+    prof = eng.profile_read(ctx)
+    eng.profile_enable(ctx, False)
+    prof_steps = max(p1["steps"] - p0["steps"], 1)
+    all_gen, all_dev, all_wall = reduce_sum(gen), reduce_max(dev_ms), reduce_max(wall_ms)
+    peaks = measured_peaks()
+    weight_bytes = wl.step_weight_bytes(shape, 4)
+    gemm_ms = prof["ms"]["gemm"] / prof_steps
+    gbs = weight_bytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
+    out = dict(
+        metric="decode-only tok/s, Llama-3-8B-arch Q4", value=all_gen / (all_dev * 1e-3), unit="tok/s", n_gpus=world, steps=int(steps),
+        warmup=warm, ms_per_step=all_dev / max(steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+        data="synthetic",
+        config=dict(workload=f"llama3_8b_q4 decode-only iterations, {B} sequences per replica", layers=shape["num_layers"], page=16,
+                    parallelism=f"replica x{world}", l2="every iteration streams 5 GB of weights, far beyond L2",
+                    generated_tokens_per_step=gen / max(steps, 1)),
+        roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"], traffic=None,
+                      peak_source=peaks["source"], kernel="gemm_stream_kernel (projection weights once per iteration) + bf16 lm_head",
+                      algorithmic_bytes_per_step=weight_bytes, ms_per_step=gemm_ms, launches_per_step=prof["launches"]["gemm"] / prof_steps),
+        class_ms_per_step={k: v / prof_steps for k, v in prof["ms"].items()},
+        e2e=dict(value=all_gen / (all_wall * 1e-3), unit="tok/s", h2d_bytes_per_step=int((s1["h2d_bytes"] - st["h2d_bytes"]) / max(steps, 1)),
+                 d2h_bytes_per_step=int((s1["d2h_bytes"] - st["d2h_bytes"]) / max(steps, 1))),
+        gpu_launches=int(s1["kernel_launches"] - st["kernel_launches"]), clocks=clocks,
+    )
+    engine.free()
+    model.free()
+    return out
+
+
 def cpu_baseline_paged_attn(case, sample=16, seconds=5.0):
     """Oracle paged attention (f32 accumulate, OpenMP over (sequence, kv head)) on the first `sample`
     sequences of the same batch."""
@@ -395,6 +459,11 @@ def run_reference(args, rank, world):
         dt = float(np.mean([r["measured_seconds"] for r in runs]))
         metric, sample = "continuous-batch decode tok/s, Llama-3-8B-arch Q4", runs[0]["sample"] + f"; {steps} such samples"
         wl_name = "llama3_8b_q4_continuous (BASELINE configuration 3)"
+        if args.workload == "decode_only":
+            metric, wl_name = "decode-only tok/s, Llama-3-8B-arch Q4", "llama3_8b_q4 decode-only iterations (CPU: the same bounded loop)"
+        elif args.workload == "qwen3_32b_q8_tp":
+            metric, wl_name = ("continuous-batch decode tok/s, Qwen3-32B-arch Q8, tensor-parallel",
+                               "qwen3_32b_q8_tp (BASELINE configuration 4; CPU: the bounded Llama-3-8B-shape sample, the 32B model is not run on CPU)")
         args.steps = steps
     return dict(impl="reference", metric=metric, value=v, unit="tok/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                 ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
@@ -410,7 +479,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode", "qwen3_32b_q8_tp"])
+    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode", "qwen3_32b_q8_tp", "decode_only"])
     ap.add_argument("--chunk-tokens", dest="chunk_tokens", type=int, default=0, help="paged_attn_decode: split-K chunk")
     ap.add_argument("--requests", type=int, default=2048)
     ap.add_argument("--arrivals", default="saturated", choices=["saturated", "poisson"])
@@ -444,6 +513,8 @@ def main():
 
     if args.workload == "paged_attn_decode":
         out = run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
+    elif args.workload == "decode_only":
+        out = run_decode_only(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
     else:
         out = run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
         if rank == 0 and args.cpu_baseline:

@@ -48,6 +48,7 @@ struct b2_ctx {
     float* tc_partial = nullptr;
     size_t tc_partial_bytes = 0;
     int* dev_err = nullptr;
+    int* tile_counters = nullptr;  // per row-tile arrival counters of the split-K streaming kernel (self-resetting)
     bool use_tc = true;
     // optional per-kernel-class timing with CUDA events on the launching stream
     bool profile = false;

@@ -60,6 +60,7 @@ int32_t b2_ctx_free(b2_ctx* ctx) {
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->tc_partial) cudaFree(ctx->tc_partial);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->tile_counters) cudaFree(ctx->tile_counters);
     for (auto e : ctx->prof_ev) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);

@@ -18,7 +18,9 @@
 // CTA = 4 warps x 32 feature rows (two 16-row MMA tiles per warp, sharing every B fragment) = 128 rows, over
 // one K range; the activations of the range pass through a double-buffered shared-memory chunk of 256 K.
 // K is split over CTAs (grid.y) until the grid covers the machine about twice; with more than one range the
-// f32 partial sums go to scratch and a second kernel adds them and applies the epilogue.
+// f32 partial sums go to scratch; up to 16 tokens the CTA of a row tile that finishes last adds them (in range
+// order) and applies the epilogue, so a projection is one launch; beyond that a second kernel does it with the
+// whole machine.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -83,6 +85,7 @@ struct StreamExtra {
     int splits;          // K ranges (grid.y)
     int k_per_split;     // a multiple of KC
     float* partial;      // [splits, M, N] f32 when splits > 1
+    int* counters;       // [row tiles], zero between launches: the CTA that arrives last adds the ranges up
 };
 
 template <int WK, int NT, int EPI>
@@ -253,9 +256,63 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
                     p.out[(size_t)tok * p.ldo + row] = f2bf(bf2f(p.res[(size_t)tok * p.ldres + row]) + rbf(v));
                 }
             }
+    if (ex.splits == 1 || ex.counters == nullptr) return;  // one range, or a separate pass adds the ranges up
+
+    // Several K ranges: the CTA of this row tile that finishes last adds the ranges up in index order (so the
+    // sum does not depend on who is last) and applies the epilogue.  No CTA waits for another.
+    __shared__ int s_last;
+    __threadfence();  // this CTA's partial sums are visible before its arrival is counted
+    __syncthreads();
+    if (tid == 0) {
+        const int arrived = atomicAdd(ex.counters + blockIdx.x, 1);
+        s_last = arrived == ex.splits - 1;
+        if (s_last) ex.counters[blockIdx.x] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int row0 = blockIdx.x * ROWS_PER_CTA;
+    const size_t plane = (size_t)M * N;
+    // four consecutive rows per thread and iteration; the ranges are added in index order, four loads in flight
+    for (int e = tid; e < M * (ROWS_PER_CTA / 4); e += kThreads) {
+        const int tok = e / (ROWS_PER_CTA / 4), row = row0 + (e % (ROWS_PER_CTA / 4)) * 4;
+        const float* src = ex.partial + (size_t)tok * N + row;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        int z = 0;
+        for (; z + 4 <= ex.splits; z += 4) {
+            const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)z * plane));
+            const float4 v1 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z + 1) * plane));
+            const float4 v2 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z + 2) * plane));
+            const float4 v3 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z + 3) * plane));
+            a.x = (((a.x + v0.x) + v1.x) + v2.x) + v3.x;
+            a.y = (((a.y + v0.y) + v1.y) + v2.y) + v3.y;
+            a.z = (((a.z + v0.z) + v1.z) + v2.z) + v3.z;
+            a.w = (((a.w + v0.w) + v1.w) + v2.w) + v3.w;
+        }
+        for (; z < ex.splits; z++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)z * plane));
+            a.x += v.x, a.y += v.y, a.z += v.z, a.w += v.w;
+        }
+        const float av[4] = {a.x, a.y, a.z, a.w};
+        if (EPI == EPI_F32) {
+            *reinterpret_cast<float4*>(p.out_f32 + (size_t)tok * p.ldo + row) = a;
+        } else if (EPI == EPI_BF16) {
+            uint2 o;
+            o.x = pack_bf2(av[0], av[1]);
+            o.y = pack_bf2(av[2], av[3]);
+            *reinterpret_cast<uint2*>(p.out + (size_t)tok * p.ldo + row) = o;
+        } else {
+            const uint2 r = *reinterpret_cast<const uint2*>(p.res + (size_t)tok * p.ldres + row);
+            uint2 o;
+            o.x = pack_bf2(bflo(r.x) + rbf(av[0]), bfhi(r.x) + rbf(av[1]));
+            o.y = pack_bf2(bflo(r.y) + rbf(av[2]), bfhi(r.y) + rbf(av[3]));
+            *reinterpret_cast<uint2*>(p.out + (size_t)tok * p.ldo + row) = o;
+        }
+    }
 }
 
-// out = epilogue(sum over K ranges of partial)
+// out = epilogue(sum over K ranges of partial): the separate pass used from 17 tokens on, where one CTA per row
+// tile would be too little parallelism for the sums
 template <int EPI>
 __global__ void stream_reduce_kernel(const GemmParams p, const float* __restrict__ partial, int splits) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -284,7 +341,7 @@ int32_t launch_stream(b2_ctx* ctx, const GemmParams& p) {
     if (splits < 1) splits = 1;
     const int chunks_per = (chunks + splits - 1) / splits;
     splits = (chunks + chunks_per - 1) / chunks_per;
-    StreamExtra ex{splits, chunks_per * KC, nullptr};
+    StreamExtra ex{splits, chunks_per * KC, nullptr, nullptr};
     if (splits > 1) {
         const size_t bytes = (size_t)splits * p.M * p.N * sizeof(float);
         if (bytes > ctx->tc_partial_bytes) {
@@ -295,10 +352,17 @@ int32_t launch_stream(b2_ctx* ctx, const GemmParams& p) {
             ctx->tc_partial_bytes = bytes + (bytes >> 2);
         }
         ex.partial = ctx->tc_partial;
+        constexpr int kMaxTiles = 8192;  // row tiles of 128: up to N = 1 M features
+        B2_REQUIRE(row_tiles <= kMaxTiles, B2_ERR_UNSUPPORTED, "gemm: output too wide for the split-K streaming kernel");
+        if (!ctx->tile_counters) {
+            B2_CUDA(cudaMalloc((void**)&ctx->tile_counters, kMaxTiles * sizeof(int)));
+            B2_CUDA(cudaMemsetAsync(ctx->tile_counters, 0, kMaxTiles * sizeof(int), ctx->stream));
+        }
+        if (p.M <= 16) ex.counters = ctx->tile_counters;  // the last CTA of a row tile adds the ranges up
     }
     gemm_stream_kernel<WK, NT, EPI><<<dim3(row_tiles, splits), kThreads, smem, ctx->stream>>>(p, ex);
     B2_LAUNCHED(ctx);
-    if (splits > 1) {
+    if (splits > 1 && !ex.counters) {
         const size_t total = (size_t)p.M * p.N;
         stream_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, ex.partial, splits);
         B2_LAUNCHED(ctx);
@@ -329,7 +393,10 @@ int32_t dispatch_nt(b2_ctx* ctx, const GemmParams& p) {
 
 bool b2_gemm_stream_eligible(const GemmParams& p) {
     return p.M >= 1 && p.M <= 64 && p.N % ROWS_PER_CTA == 0 && p.K % KC == 0 && p.ldx % 4 == 0 && ((uintptr_t)p.x & 7) == 0 &&
-           ((uintptr_t)p.w & 15) == 0 && (p.bits == 0 || p.bits == 4 || p.bits == 8);
+           ((uintptr_t)p.w & 15) == 0 && (p.bits == 0 || p.bits == 4 || p.bits == 8) &&
+           // the reduction of several K ranges stores four rows at a time
+           p.ldo % 4 == 0 && ((uintptr_t)p.out & 7) == 0 && ((uintptr_t)p.out_f32 & 15) == 0 &&
+           (p.epilogue != EPI_BF16_RESADD || (p.ldres % 4 == 0 && ((uintptr_t)p.res & 7) == 0));
 }
 
 int32_t b2_gemm_stream_launch(b2_ctx* ctx, const GemmParams& p) {
