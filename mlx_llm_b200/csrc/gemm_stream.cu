@@ -17,7 +17,7 @@
 //
 // CTA = 4 warps x 32 feature rows (two 16-row MMA tiles per warp, sharing every B fragment) = 128 rows, over
 // one K range; the activations of the range pass through a double-buffered shared-memory chunk of 256 K.
-// K is split over CTAs (grid.y) until the grid covers the machine about twice; with more than one range the
+// K is split over CTAs (grid.y) until the grid fills every CTA slot of the machine; with more than one range the
 // f32 partial sums go to scratch; up to 16 tokens the CTA of a row tile that finishes last adds them (in range
 // order) and applies the epilogue, so a projection is one launch; beyond that a second kernel does it with the
 // whole machine.
@@ -335,8 +335,8 @@ int32_t launch_stream(b2_ctx* ctx, const GemmParams& p) {
     B2_SMEM_ONCE(ctx, (gemm_stream_kernel<WK, NT, EPI>), smem);
     const int row_tiles = p.N / ROWS_PER_CTA;
     const int chunks = p.K / KC;
-    // K ranges: enough CTAs to cover the machine about twice, at least two chunks per range
-    int splits = (2 * ctx->sm_count + row_tiles - 1) / row_tiles;
+    // K ranges: enough CTAs for every slot of the machine, at least two chunks per range
+    int splits = (4 * ctx->sm_count + row_tiles - 1) / row_tiles;  // four CTAs fit an SM (registers): fill them all
     if (splits > chunks / 2) splits = chunks / 2;
     if (splits < 1) splits = 1;
     const int chunks_per = (chunks + splits - 1) / splits;
