@@ -58,6 +58,18 @@ __device__ __forceinline__ void dequant8_q4(uint32_t w, uint32_t s2, uint32_t b2
     out[2] = prmt(r0, r1, 0x7632u);
     out[3] = prmt(r2, r3, 0x7632u);
 }
+// The same eight values in the order the nibble masks produce them: (c0,c4) (c1,c5) (c2,c6) (c3,c7).  Used when
+// there are few token tiles: the four interleaving permutes per word and ROW are saved, and the activation
+// fragments (per word and TOKEN TILE) are permuted to match instead.
+__device__ __forceinline__ void dequant8_q4_paired(uint32_t w, uint32_t s2, uint32_t b2, uint32_t (&out)[4]) {
+    const uint32_t magic = 0x43004300u;
+    const uint32_t r0 = (w & 0x000f000fu) | magic, r1 = ((w >> 4) & 0x000f000fu) | magic;
+    const uint32_t r2 = ((w >> 8) & 0x000f000fu) | magic, r3 = ((w >> 12) & 0x000f000fu) | magic;
+    out[0] = fma_bf2(sub_bf2(r0, magic), s2, b2);
+    out[1] = fma_bf2(sub_bf2(r1, magic), s2, b2);
+    out[2] = fma_bf2(sub_bf2(r2, magic), s2, b2);
+    out[3] = fma_bf2(sub_bf2(r3, magic), s2, b2);
+}
 __device__ __forceinline__ void dequant4_q8(uint32_t w, float s, float b, uint32_t (&out)[2]) {
     const float c0 = (float)(w & 0xffu), c1 = (float)((w >> 8) & 0xffu), c2 = (float)((w >> 16) & 0xffu), c3 = (float)(w >> 24);
     out[0] = pack_bf2(__fmaf_rn(c0, s, b), __fmaf_rn(c1, s, b));
@@ -91,6 +103,7 @@ struct StreamExtra {
 template <int WK, int NT, int EPI>
 __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams p, const StreamExtra ex) {
     using SP = Span<WK>;
+    constexpr bool kPaired = WK == 4 && NT <= 2;  // see dequant8_q4_paired
     extern __shared__ __align__(16) uint8_t smem[];  // two chunks of [NT*8 tokens][XS_STRIDE]
     const uint32_t xs = smem_u32(smem);
     constexpr int CHUNK_BYTES = NT * 8 * XS_STRIDE;
@@ -203,7 +216,9 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
                 uint32_t o[4][4];  // [row][pair]: positions 8 e8 + (0,1) (2,3) (4,5) (6,7)
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    if (WK == 4) {
+                    if (WK == 4 && kPaired) {
+                        dequant8_q4_paired((&cw[i].x)[e8], s2[i], b2[i], o[i]);
+                    } else if (WK == 4) {
                         dequant8_q4((&cw[i].x)[e8], s2[i], b2[i], o[i]);
                     } else if (WK == 8) {
                         uint32_t lo2[2], hi2[2];
@@ -213,6 +228,26 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
                     } else {
                         o[i][0] = cw[i].x, o[i][1] = cw[i].y, o[i][2] = cw[i].z, o[i][3] = cw[i].w;
                     }
+                }
+                if (kPaired) {
+                    // MMA step h of this word takes positions (2h, 2h+4) and (2h+1, 2h+5): the activation pairs are
+                    // built from the two 8-byte pieces that hold positions 0-3 and 4-7
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        uint32_t x0[2], x1[2];
+                        const uint32_t xa = xspan + (uint32_t)(nt * 8 + g) * XS_STRIDE + (uint32_t)(32 * e8 + 4 * t) * 2;
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(x0[0]), "=r"(x0[1]) : "r"(xa));
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(x1[0]), "=r"(x1[1]) : "r"(xa + 32u));
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const uint32_t b[2] = {prmt(x0[h], x1[h], 0x5410u), prmt(x0[h], x1[h], 0x7632u)};
+                            const uint32_t a0[4] = {o[0][2 * h], o[1][2 * h], o[0][2 * h + 1], o[1][2 * h + 1]};
+                            const uint32_t a1[4] = {o[2][2 * h], o[3][2 * h], o[2][2 * h + 1], o[3][2 * h + 1]};
+                            mma_bf16_16816(acc[0][nt], a0, b);
+                            mma_bf16_16816(acc[1][nt], a1, b);
+                        }
+                    }
+                    continue;
                 }
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
