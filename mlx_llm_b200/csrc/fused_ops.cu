@@ -23,6 +23,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 // One CTA per row, 8 bf16 (16 bytes) per thread per iteration.
 __global__ void rms_norm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, float eps, int dim, int ldx,
                                 const int32_t* __restrict__ row_idx, uint16_t* __restrict__ out) {
+    // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic
+    // stream serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int row = blockIdx.x;
     const int src = row_idx ? row_idx[row] : row;
     const uint16_t* xr = x + (size_t)src * ldx;
@@ -94,6 +97,9 @@ __device__ __forceinline__ float swiglu_one(float g, float u) {
 }
 // LlamaMlp::forward (src/models/llama.rs:1040-1045) on a fused [rows, 2*inter] gate|up buffer.
 __global__ void swiglu_kernel(const uint16_t* __restrict__ gu, int inter, uint16_t* __restrict__ out) {
+    // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic
+    // stream serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int row = blockIdx.y;
     const uint16_t* g = gu + (size_t)row * 2 * inter;
     const uint16_t* u = g + inter;

@@ -166,12 +166,16 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
         }
     };
 
+    // The weights do not depend on the kernel before this one: their first loads go out at once.  Everything else
+    // (activations, residual, the shared partial-sum scratch) waits for the previous grid to complete — this kernel
+    // is launched with programmatic stream serialisation, so its CTAs may start while that grid's last CTAs finish.
     if (n_chunks > 0) {
-        load_x(0, 0);
 #pragma unroll
         for (int j = 0; j < PF; j++)
             if (k_begin + j * SP::LEN < k_end) load_w(j, k_begin + j * SP::LEN);
     }
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (n_chunks > 0) load_x(0, 0);
     for (int c = 0; c < n_chunks; c++) {
         const int buf = c & 1;
         if (c + 1 < n_chunks) load_x(c + 1, buf ^ 1);
@@ -395,7 +399,19 @@ int32_t launch_stream(b2_ctx* ctx, const GemmParams& p) {
         }
         if (p.M <= 16) ex.counters = ctx->tile_counters;  // the last CTA of a row tile adds the ranges up
     }
-    gemm_stream_kernel<WK, NT, EPI><<<dim3(row_tiles, splits), kThreads, smem, ctx->stream>>>(p, ex);
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(row_tiles, splits);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        B2_CUDA(cudaLaunchKernelEx(&cfg, gemm_stream_kernel<WK, NT, EPI>, p, ex));
+    }
     B2_LAUNCHED(ctx);
     if (splits > 1 && !ex.counters) {
         const size_t total = (size_t)p.M * p.N;

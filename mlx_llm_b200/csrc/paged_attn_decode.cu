@@ -224,6 +224,9 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
 // Merge the chunks of one (sequence, kv head): out = sum_c O_c 2^(m_c-M) / sum_c l_c 2^(m_c-M).
 template <int HD>
 __global__ void paged_attn_merge_kernel(const DecodeAttnParams p) {
+    // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic
+    // stream serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int seq = blockIdx.x, kvh = blockIdx.y;
     const int w0 = p.seq_work_off[seq], n = p.seq_work_off[seq + 1] - w0;
     if (n <= 1) return;
