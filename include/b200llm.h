@@ -259,6 +259,31 @@ int32_t b2_tp_group_free(b2_tp_group* g);
 int32_t b2_tp_group_info(const b2_tp_group* g, int32_t* rank, int32_t* world);
 /* In-place sum of an f32 device buffer over the group, enqueued on the context's stream. */
 int32_t b2_tp_all_reduce_f32(b2_tp_group* g, float* buf_dev, int64_t n);
+/* Reductions over peer memory instead of NCCL (ranks on one node whose GPUs reach one another over NVLink): one
+ * kernel per reduction waits for every rank's projection, sums the ranks' f32 partial sums for the columns it
+ * owns with loads from the peers' memory, adds the residual, and stores the new bf16 hidden state into every
+ * rank's copy.  Set-up, once per group and before the group's models run: every rank calls b2_tp_peer_alloc
+ * (max_tokens = the most tokens one step will carry; hidden = the model's hidden size, a multiple of 4 x world)
+ * and gets the 64-byte handle of its region; the host program gathers the handles (the channel that carried the
+ * id); every rank calls b2_tp_peer_attach with all of them in rank order.  From then on a model of that hidden
+ * size on this group keeps its hidden state inside the region and reduces there; a step of more than
+ * max_tokens tokens fails with B2_ERR_UNSUPPORTED.  If a region cannot be mapped (GPUs without peer access,
+ * devices hidden from the process) attach fails with B2_ERR_UNSUPPORTED and the group stays on NCCL.  A group
+ * created with id128 == NULL and world > 1 has no NCCL communicator and can only reduce this way.  Every wait
+ * in the kernel is bounded (about four seconds); when one runs out the context's error word is raised,
+ * b2_ctx_sync returns B2_ERR_TIMEOUT and later reductions return at once.  Ranks must enter their steps
+ * within that time of one another: start them from a common point (a host barrier after loading). */
+int32_t b2_tp_peer_alloc(b2_tp_group* g, int32_t max_tokens, int32_t hidden, uint8_t* handle64_out);
+int32_t b2_tp_peer_attach(b2_tp_group* g, const uint8_t* handles /* world x 64 bytes */, int32_t n_handles);
+/* This rank's region: the f32 partial sums [max_tokens, hidden] a projection writes and the bf16 hidden state. */
+int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** part_dev, uint16_t** x_dev, int32_t* max_tokens, int32_t* hidden);
+/* x[0:rows] = bf16(x + bf16(sum over ranks of part[0:rows])) on every rank; enqueued on the context's stream. */
+int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows);
+/* All ranks of a group inside ONE process on one device (protocol tests without N GPUs): the groups' regions
+ * are used directly, and the whole group's reduction runs as a single cooperative launch, because kernels
+ * that wait on one another must not be separate launches on one device. */
+int32_t b2_tp_peer_attach_local(b2_tp_group* const* groups, int32_t n);
+int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, int32_t rows);
 /* The two constructors with a group (NULL: the whole model, as without the suffix).  b2_model_get_config
  * still reports the WHOLE model's dimensions. */
 int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,

@@ -78,7 +78,7 @@ int32_t b2_ctx_sync(b2_ctx* ctx) {
         B2_CUDA(cudaStreamSynchronize(ctx->stream));
         if (e != 0) {
             B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
-            return b2_fail(B2_ERR_TIMEOUT, "a device-side wait (tcgen05 GEMM pipeline) timed out");
+            return b2_fail(B2_ERR_TIMEOUT, "a bounded device-side wait ran out (tcgen05 pipeline barrier or a peer-memory reduction flag)");
         }
     }
     return B2_OK;

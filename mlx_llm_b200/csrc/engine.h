@@ -36,10 +36,22 @@ struct b2_weights {
 struct b2_tp_group {
     b2_ctx* ctx = nullptr;
     int rank = 0, world = 1;
-    void* comm = nullptr;  // ncclComm_t
+    void* comm = nullptr;  // ncclComm_t (null for a group that reduces over peer memory only)
+    // peer-memory reductions (tp_peer.cu): this rank's exported region and every rank's region as mapped here
+    void* peer_local = nullptr;
+    void* peer_base[8] = {};
+    int peer_cap_rows = 0, peer_hidden = 0;
+    size_t peer_x_off = 0;
+    bool peer_ready = false, peer_ipc = false;
+    uint32_t peer_seq = 0;  // number of the last reduction; every rank advances it in step
 };
 // In-place sum over the group of an f32 device buffer, enqueued on the context's stream.
 int32_t b2_tp_all_reduce_sum_f32(b2_tp_group* g, float* buf, size_t n);
+// Peer-memory path: the region's partial sums / hidden state of this rank, and the fused sum + residual add.
+float* b2_tp_peer_part(const b2_tp_group* g);
+uint16_t* b2_tp_peer_x(const b2_tp_group* g);
+int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M);
+void b2_tp_peer_release(b2_tp_group* g);
 
 // ---- Model (src/models/llama.rs: CausalLm, LlamaLayer, LlamaAttention, LlamaMlp) ------------------
 struct Proj {  // Projection::{Dense,Quantized} (src/primitives/projection.rs:34-47)
@@ -60,6 +72,7 @@ struct Workspace {
     uint16_t *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *act = nullptr;
     uint16_t *last = nullptr, *logits = nullptr;
     float* tp_part = nullptr;  // [t_cap, hidden] f32 partial sums of o_proj / down_proj (tensor-parallel only)
+    bool x_in_peer_region = false;  // x points into the group's exported region (not owned by the workspace)
     int32_t* argmax = nullptr;
     int32_t* ids = nullptr;
     int32_t* meta = nullptr;      // packer outputs (b2_batch_meta_carve layout)

@@ -682,7 +682,7 @@ int32_t b2_model_free(b2_model* m) {
     if (m->cos_tab) cudaFree(m->cos_tab);
     if (m->sin_tab) cudaFree(m->sin_tab);
     Workspace& w = m->ws;
-    void* dev[] = {w.x, w.xn, w.qkv, w.q, w.attn, w.gu, w.act, w.last, w.logits, w.argmax, w.ids, w.meta, w.stage_dev, w.attn_scratch};
+    void* dev[] = {w.x_in_peer_region ? nullptr : (void*)w.x, w.tp_part, w.xn, w.qkv, w.q, w.attn, w.gu, w.act, w.last, w.logits, w.argmax, w.ids, w.meta, w.stage_dev, w.attn_scratch};
     for (void* p : dev)
         if (p) cudaFree(p);
     if (w.stage_host) cudaFreeHost(w.stage_host);

@@ -29,10 +29,22 @@ int32_t ensure_workspace(b2_model* m, int T, int B, int W, int P, size_t stage_i
     const b2_model_config& c = m->cfg;
     const bool grow_t = T > w.t_cap, grow_b = B > w.b_cap, grow_w = W > w.w_cap, grow_p = P > w.p_cap;
     if (grow_t || grow_b || grow_w || grow_p) B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    // reductions over peer memory write x on every rank: x then lives in the group's exported region
+    const bool peer = m->tp && m->tp->world > 1 && m->tp->peer_ready && m->tp->peer_hidden == c.hidden_size;
+    if (peer) {
+        B2_REQUIRE(T <= m->tp->peer_cap_rows, B2_ERR_UNSUPPORTED,
+                   "a step of " + std::to_string(T) + " tokens exceeds the peer regions' " + std::to_string(m->tp->peer_cap_rows));
+        if (!w.x_in_peer_region) {
+            B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
+            if (w.x) cudaFree(w.x);
+            w.x = b2_tp_peer_x(m->tp);
+            w.x_in_peer_region = true;
+        }
+    }
     if (grow_t) {
         const size_t t = (size_t)std::max(T, 64) * 5 / 4;
         const size_t qkv_w = (size_t)(m->hq_l + 2 * m->hkv_l) * c.head_dim;
-        B2_CHECK(regrow(w.x, t * c.hidden_size));
+        if (!w.x_in_peer_region) B2_CHECK(regrow(w.x, t * c.hidden_size));
         B2_CHECK(regrow(w.xn, t * c.hidden_size));
         B2_CHECK(regrow(w.qkv, t * qkv_w));
         B2_CHECK(regrow(w.q, t * m->hq_l * c.head_dim));
@@ -112,8 +124,14 @@ int32_t gemm_reduce_residual(b2_model* m, const Proj& p, const uint16_t* a, int 
     g.ldo = H;
     g.ldres = H;
     g.epilogue = EPI_F32;
-    g.out_f32 = m->ws.tp_part;
     b2_prof_mark(ctx, B2_CLS_GEMM);
+    if (m->ws.x_in_peer_region) {  // one kernel: sum of every rank's partial sums over peer memory + residual add
+        g.out_f32 = b2_tp_peer_part(m->tp);
+        B2_CHECK(b2_gemm_launch(ctx, g));
+        b2_prof_mark(ctx, B2_CLS_COLLECTIVE);
+        return b2_tp_peer_reduce_residual_launch(m->tp, M);
+    }
+    g.out_f32 = m->ws.tp_part;
     B2_CHECK(b2_gemm_launch(ctx, g));
     b2_prof_mark(ctx, B2_CLS_COLLECTIVE);
     B2_CHECK(b2_tp_all_reduce_sum_f32(m->tp, m->ws.tp_part, (size_t)M * H));

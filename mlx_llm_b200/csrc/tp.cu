@@ -61,6 +61,7 @@ int32_t nccl_fail(const char* what, ncclResult_t r) {
 
 int32_t b2_tp_all_reduce_sum_f32(b2_tp_group* g, float* buf, size_t n) {
     if (!g || g->world == 1) return B2_OK;
+    B2_REQUIRE(g->comm, B2_ERR_UNSUPPORTED, "this group was created without an NCCL id: it reduces over peer memory only");
     const ncclResult_t r = api().AllReduce(buf, buf, n, ncclFloat32, ncclSum, reinterpret_cast<ncclComm_t>(g->comm), g->ctx->stream);
     if (r != ncclSuccess) return nccl_fail("ncclAllReduce", r);
     return B2_OK;
@@ -80,13 +81,13 @@ int32_t b2_tp_unique_id(uint8_t* out128) {
 }
 
 int32_t b2_tp_group_create(b2_ctx* ctx, const uint8_t* id128, int32_t rank, int32_t world, b2_tp_group** out) {
-    B2_REQUIRE(ctx && out && (world == 1 || id128), B2_ERR_MSG, "b2_tp_group_create: null argument");
+    B2_REQUIRE(ctx && out, B2_ERR_MSG, "b2_tp_group_create: null argument");
     B2_REQUIRE(world >= 1 && rank >= 0 && rank < world, B2_ERR_MSG, "b2_tp_group_create: rank outside the group");
     b2_tp_group* g = new b2_tp_group();
     g->ctx = ctx;
     g->rank = rank;
     g->world = world;
-    if (world > 1) {
+    if (world > 1 && id128) {
         if (!api().handle) {
             delete g;
             return b2_fail(B2_ERR_UNSUPPORTED, api().why);
@@ -108,6 +109,7 @@ int32_t b2_tp_group_create(b2_ctx* ctx, const uint8_t* id128, int32_t rank, int3
 
 int32_t b2_tp_group_free(b2_tp_group* g) {
     if (!g) return B2_OK;
+    b2_tp_peer_release(g);
     if (g->comm) {
         cudaStreamSynchronize(g->ctx->stream);
         api().CommDestroy(reinterpret_cast<ncclComm_t>(g->comm));

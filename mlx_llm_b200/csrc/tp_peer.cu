@@ -1,0 +1,290 @@
+// Tensor-parallel reduction over peer memory (NVLink / NVSwitch), one kernel per reduction:
+//
+//     x = bf16(x + bf16(sum over ranks of the projection's f32 partial sums))
+//
+// on every rank, without a library collective.  Every rank exports one region (cudaIpc) holding its partial
+// sums, its copy of the hidden state x and two sets of flags; every rank maps every other rank's region.
+// Rank r owns the columns [r*H/world, (r+1)*H/world): its kernel waits until every rank's projection has
+// finished (flag1), reads that column range of every rank's partial sums (peer loads, summed in rank order so
+// the result does not depend on timing), adds the residual, rounds, and stores the new bf16 values into
+// EVERY rank's x (peer stores).  Block g then tells block g of every other rank that its rows are in place
+// (flag2) and waits for theirs, so that when the kernel ends this rank's x is complete.  Flags carry the
+// number of the reduction (a counter every rank advances in step), so nothing is ever reset.
+//
+// Why one buffer of each kind suffices: a rank overwrites its partial sums only after its own kernel ended,
+// which it does only after every other rank signalled flag2, which a rank does only after it finished reading
+// the partial sums; and a rank's columns of x are written by their owner only.
+//
+// There is no counterpart in the reference (a single-device program).  The waits are bounded: on expiry the
+// kernel raises the context's error word and returns; later reductions see the word and return at once.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "engine.h"
+
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxCtas = 1024;                          // flag2 slots per source rank
+constexpr size_t kFlag1Off = 0;                         // u32 [kMaxWorld]
+constexpr size_t kFlag2Off = 128;                       // u32 [kMaxWorld][kMaxCtas]
+constexpr size_t kDataOff = 128 + (size_t)kMaxWorld * kMaxCtas * 4 + 128;  // partial sums start here (256-byte aligned)
+static_assert(kDataOff % 256 == 0, "data offset alignment");
+constexpr long long kWaitCycles = 8000000000LL;         // ~4 s at 1.9 GHz
+
+struct PeerReduceParams {
+    unsigned char* base[kMaxWorld];  // every rank's region as mapped in this process
+    int rank;                        // -1: blockIdx.y is the rank (the whole group emulated by one launch)
+    int world, M, H, chunk;          // chunk = H / world columns owned by each rank
+    uint32_t seq;
+    size_t x_off;                    // offset of x in a region (the partial sums sit at kDataOff)
+    int* err;                        // the error word of the context (of rank 0's context when emulating)
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Spins until *flag has reached `seq` (wrap-safe); false when the limit ran out.
+__device__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(flag) - seq) < 0) {
+        if (clock64() - t0 > kWaitCycles) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+
+__global__ void __launch_bounds__(256) tp_peer_reduce_residual_kernel(const PeerReduceParams p) {
+    __shared__ int gave_up;
+    const int r = p.rank >= 0 ? p.rank : (int)blockIdx.y;
+    const int g = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
+    if (tid == 0) gave_up = (*reinterpret_cast<volatile int*>(p.err) != 0);
+    __syncthreads();
+    if (gave_up) return;  // an earlier wait ran out: the group is broken, do not wait again
+    // this rank's projection ended before this launch began: tell the others
+    if (g == 0 && tid < p.world && tid != r) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(p.base[tid] + kFlag1Off) + r, p.seq);
+    }
+    if (tid < p.world && tid != r) {
+        if (!wait_flag(reinterpret_cast<const uint32_t*>(p.base[r] + kFlag1Off) + tid, p.seq)) {
+            atomicExch(p.err, 7);
+            gave_up = 1;
+        }
+    }
+    __syncthreads();
+    if (gave_up) return;
+
+    const int qpr = p.chunk >> 2;  // groups of four columns per row of this rank's range
+    const int64_t items = (int64_t)p.M * qpr;
+    for (int64_t i = (int64_t)g * blockDim.x + tid; i < items; i += (int64_t)G * blockDim.x) {
+        const int row = (int)(i / qpr), col = r * p.chunk + (int)(i % qpr) * 4;
+        const size_t off = (size_t)row * p.H + col;
+        float4 part[kMaxWorld];
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; s++)
+            if (s < p.world) part[s] = ld_peer_f4(reinterpret_cast<const float*>(p.base[s] + kDataOff) + off);
+        float4 acc = part[0];
+#pragma unroll
+        for (int s = 1; s < kMaxWorld; s++)
+            if (s < p.world) acc.x += part[s].x, acc.y += part[s].y, acc.z += part[s].z, acc.w += part[s].w;
+        uint2 xv = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.base[r] + p.x_off) + off);
+        const float a0 = bf2f((uint16_t)(xv.x & 0xffff)) + rbf(acc.x), a1 = bf2f((uint16_t)(xv.x >> 16)) + rbf(acc.y);
+        const float a2 = bf2f((uint16_t)(xv.y & 0xffff)) + rbf(acc.z), a3 = bf2f((uint16_t)(xv.y >> 16)) + rbf(acc.w);
+        xv.x = pack_bf2(a0, a1);
+        xv.y = pack_bf2(a2, a3);
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; s++)
+            if (s < p.world) *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.base[s] + p.x_off) + off) = xv;
+    }
+    // the rows of this block are in every rank's x: say so, then wait for the same block of every other rank
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.world && tid != r) {
+        st_release_sys(reinterpret_cast<uint32_t*>(p.base[tid] + kFlag2Off) + (size_t)r * kMaxCtas + g, p.seq);
+        if (!wait_flag(reinterpret_cast<const uint32_t*>(p.base[r] + kFlag2Off) + (size_t)tid * kMaxCtas + g, p.seq)) atomicExch(p.err, 8);
+    }
+}
+
+int grid_for(int M, int chunk, int cap) {
+    const int64_t items = (int64_t)M * (chunk / 4);
+    return (int)std::max<int64_t>(1, std::min<int64_t>(cap, (items + 1023) / 1024));  // about four items per thread
+}
+
+int32_t ensure_err_word(b2_ctx* ctx) {
+    if (!ctx->dev_err) {
+        B2_CUDA(cudaMalloc((void**)&ctx->dev_err, 16));
+        B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, 16, ctx->stream));
+    }
+    return B2_OK;
+}
+
+size_t region_bytes(int cap_rows, int hidden, size_t* x_off) {
+    const size_t part = ((size_t)cap_rows * hidden * 4 + 255) / 256 * 256;
+    *x_off = kDataOff + part;
+    return *x_off + ((size_t)cap_rows * hidden * 2 + 255) / 256 * 256;
+}
+
+}  // namespace
+
+float* b2_tp_peer_part(const b2_tp_group* g) { return reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + kDataOff); }
+uint16_t* b2_tp_peer_x(const b2_tp_group* g) { return reinterpret_cast<uint16_t*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + g->peer_x_off); }
+
+// x (the region's) += sum over ranks of the regions' partial sums, for the first M rows; on the context's stream.
+int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M) {
+    B2_REQUIRE(g && g->peer_ready, B2_ERR_MSG, "peer reduction: the group has no attached peer regions");
+    B2_REQUIRE(M >= 0 && M <= g->peer_cap_rows, B2_ERR_MSG, "peer reduction: more rows than the regions hold");
+    if (M == 0) return B2_OK;
+    PeerReduceParams p{};
+    for (int s = 0; s < g->world; s++) p.base[s] = static_cast<unsigned char*>(g->peer_base[s]);
+    p.rank = g->rank;
+    p.world = g->world;
+    p.M = M;
+    p.H = g->peer_hidden;
+    p.chunk = g->peer_hidden / g->world;
+    p.seq = ++g->peer_seq;
+    p.x_off = g->peer_x_off;
+    p.err = g->ctx->dev_err;
+    tp_peer_reduce_residual_kernel<<<grid_for(M, p.chunk, kMaxCtas), 256, 0, g->ctx->stream>>>(p);
+    B2_LAUNCHED(g->ctx);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" {
+
+int32_t b2_tp_peer_alloc(b2_tp_group* g, int32_t max_tokens, int32_t hidden, uint8_t* handle64_out) {
+    B2_REQUIRE(g && handle64_out, B2_ERR_MSG, "b2_tp_peer_alloc: null argument");
+    B2_REQUIRE(!g->peer_local, B2_ERR_MSG, "b2_tp_peer_alloc: the group already has a region");
+    B2_REQUIRE(g->world <= kMaxWorld, B2_ERR_UNSUPPORTED, "peer reduction: at most 8 ranks");
+    B2_REQUIRE(max_tokens > 0 && hidden > 0 && hidden % (4 * g->world) == 0, B2_ERR_MSG,
+               "b2_tp_peer_alloc: hidden size must be a multiple of 4 x world");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    B2_CUDA(cudaSetDevice(g->ctx->device));
+    B2_CHECK(ensure_err_word(g->ctx));
+    size_t x_off = 0;
+    const size_t bytes = region_bytes(max_tokens, hidden, &x_off);
+    void* base = nullptr;
+    B2_CUDA(cudaMalloc(&base, bytes));
+    B2_CUDA(cudaMemsetAsync(base, 0, bytes, g->ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(g->ctx->stream));  // zeroed before any other rank can see the handle
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, base) != cudaSuccess) {
+        cudaGetLastError();
+        memset(&h, 0, sizeof(h));  // still usable inside one process (b2_tp_peer_attach_local)
+    }
+    memcpy(handle64_out, &h, 64);
+    g->peer_local = base;
+    g->peer_cap_rows = max_tokens;
+    g->peer_hidden = hidden;
+    g->peer_x_off = x_off;
+    return B2_OK;
+}
+
+int32_t b2_tp_peer_attach(b2_tp_group* g, const uint8_t* handles, int32_t n_handles) {
+    B2_REQUIRE(g && handles, B2_ERR_MSG, "b2_tp_peer_attach: null argument");
+    B2_REQUIRE(g->peer_local && !g->peer_ready, B2_ERR_MSG, "b2_tp_peer_attach: call b2_tp_peer_alloc first, attach once");
+    B2_REQUIRE(n_handles == g->world, B2_ERR_MSG, "b2_tp_peer_attach: one handle per rank, in rank order");
+    B2_CUDA(cudaSetDevice(g->ctx->device));
+    for (int s = 0; s < g->world; s++) {
+        if (s == g->rank) {
+            g->peer_base[s] = g->peer_local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)s * 64, 64);
+        void* p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            for (int t = 0; t < s; t++)
+                if (t != g->rank && g->peer_base[t]) cudaIpcCloseMemHandle(g->peer_base[t]), g->peer_base[t] = nullptr;
+            return b2_fail(B2_ERR_UNSUPPORTED, std::string("rank ") + std::to_string(s) + "'s region cannot be mapped (" + cudaGetErrorString(e) +
+                                                   "): the reductions stay on NCCL");
+        }
+        g->peer_base[s] = p;
+    }
+    g->peer_ipc = true;
+    g->peer_ready = true;
+    return B2_OK;
+}
+
+// All ranks of a group living in ONE process on one device (no IPC): the regions are used as they are.
+int32_t b2_tp_peer_attach_local(b2_tp_group* const* groups, int32_t n) {
+    B2_REQUIRE(groups && n >= 1 && n <= kMaxWorld, B2_ERR_MSG, "b2_tp_peer_attach_local: bad argument");
+    for (int s = 0; s < n; s++)
+        B2_REQUIRE(groups[s] && groups[s]->world == n && groups[s]->rank == s && groups[s]->peer_local && !groups[s]->peer_ready &&
+                       groups[s]->peer_hidden == groups[0]->peer_hidden && groups[s]->peer_cap_rows == groups[0]->peer_cap_rows &&
+                       groups[s]->ctx->device == groups[0]->ctx->device,
+                   B2_ERR_MSG, "b2_tp_peer_attach_local: the groups must be ranks 0..n-1 of one group with equal regions on one device");
+    for (int s = 0; s < n; s++) {
+        for (int t = 0; t < n; t++) groups[s]->peer_base[t] = groups[t]->peer_local;
+        groups[s]->peer_ready = true;
+    }
+    return B2_OK;
+}
+
+int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** part_dev, uint16_t** x_dev, int32_t* max_tokens, int32_t* hidden) {
+    B2_REQUIRE(g && g->peer_ready, B2_ERR_MSG, "b2_tp_peer_buffers: no attached peer regions");
+    if (part_dev) *part_dev = b2_tp_peer_part(g);
+    if (x_dev) *x_dev = b2_tp_peer_x(g);
+    if (max_tokens) *max_tokens = g->peer_cap_rows;
+    if (hidden) *hidden = g->peer_hidden;
+    return B2_OK;
+}
+
+int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows) { return b2_tp_peer_reduce_residual_launch(g, rows); }
+
+// The whole group's reduction as ONE launch (grid.y = rank) for groups attached with b2_tp_peer_attach_local:
+// kernels that wait on one another must not be separate launches on one device.
+int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, int32_t rows) {
+    B2_REQUIRE(groups && n >= 1 && n <= kMaxWorld && groups[0] && groups[0]->peer_ready && !groups[0]->peer_ipc, B2_ERR_MSG,
+               "b2_tp_peer_reduce_residual_local: needs groups attached with b2_tp_peer_attach_local");
+    b2_tp_group* g0 = groups[0];
+    B2_REQUIRE(rows >= 0 && rows <= g0->peer_cap_rows, B2_ERR_MSG, "peer reduction: more rows than the regions hold");
+    if (rows == 0) return B2_OK;
+    PeerReduceParams p{};
+    for (int s = 0; s < n; s++) p.base[s] = static_cast<unsigned char*>(g0->peer_base[s]);
+    p.rank = -1;
+    p.world = n;
+    p.M = rows;
+    p.H = g0->peer_hidden;
+    p.chunk = g0->peer_hidden / n;
+    uint32_t seq = 0;
+    for (int s = 0; s < n; s++) seq = ++groups[s]->peer_seq;
+    p.seq = seq;
+    p.x_off = g0->peer_x_off;
+    p.err = g0->ctx->dev_err;
+    // every block of every rank resident at once: a cooperative launch, sized to fit
+    int per_sm = 0;
+    B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_peer_reduce_residual_kernel, 256, 0));
+    const int cap = std::max(1, per_sm * g0->ctx->sm_count / n);
+    dim3 grid(grid_for(rows, p.chunk, std::min(cap, kMaxCtas)), n);
+    void* args[] = {&p};
+    B2_CUDA(cudaLaunchCooperativeKernel((const void*)tp_peer_reduce_residual_kernel, grid, dim3(256), args, 0, g0->ctx->stream));
+    B2_LAUNCHED(g0->ctx);
+    return B2_OK;
+}
+
+}  // extern "C"
+
+void b2_tp_peer_release(b2_tp_group* g) {
+    if (!g->peer_local) return;
+    cudaStreamSynchronize(g->ctx->stream);
+    if (g->peer_ipc)
+        for (int s = 0; s < g->world; s++)
+            if (s != g->rank && g->peer_base[s]) cudaIpcCloseMemHandle(g->peer_base[s]);
+    cudaFree(g->peer_local);
+    g->peer_local = nullptr;
+    g->peer_ready = false;
+}

@@ -221,6 +221,50 @@ class TpGroup:
     def all_reduce_f32(self, buf, n):
         check(load().b2_tp_all_reduce_f32(self.h, ptr(buf), C.c_int64(n)))
 
+    # ---- reductions over peer memory (b2_tp_peer_*) ----
+    def peer_alloc(self, max_tokens, hidden):
+        """Allocates this rank's region and returns its 64-byte handle; gather every rank's handle (rank
+        order) and pass them to peer_attach."""
+        buf = (C.c_uint8 * 64)()
+        check(load().b2_tp_peer_alloc(self.h, int(max_tokens), int(hidden), buf))
+        return bytes(buf)
+
+    def peer_attach(self, handles):
+        blob = b"".join(handles)
+        arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(load().b2_tp_peer_attach(self.h, arr, len(handles)))
+
+    def enable_peer(self, max_tokens, hidden, all_gather):
+        """alloc + attach; `all_gather(bytes) -> list of every rank's bytes in rank order` is the caller's
+        channel.  Returns False (and leaves the group on NCCL) when a region cannot be mapped."""
+        from ._lib import B2Error
+
+        handles = all_gather(self.peer_alloc(max_tokens, hidden))
+        try:
+            self.peer_attach(handles)
+        except B2Error:
+            return False
+        return True
+
+    def peer_buffers(self):
+        part, x = C.c_void_p(), C.c_void_p()
+        cap, hidden = C.c_int32(), C.c_int32()
+        check(load().b2_tp_peer_buffers(self.h, C.byref(part), C.byref(x), C.byref(cap), C.byref(hidden)))
+        return part.value, x.value, cap.value, hidden.value
+
+    def peer_reduce_residual(self, rows):
+        check(load().b2_tp_peer_reduce_residual(self.h, int(rows)))
+
+    @staticmethod
+    def peer_attach_local(groups):
+        arr = (C.c_void_p * len(groups))(*[g.h for g in groups])
+        check(load().b2_tp_peer_attach_local(arr, len(groups)))
+
+    @staticmethod
+    def peer_reduce_residual_local(groups, rows):
+        arr = (C.c_void_p * len(groups))(*[g.h for g in groups])
+        check(load().b2_tp_peer_reduce_residual_local(arr, len(groups), int(rows)))
+
     def free(self):
         if self.h:
             check(load().b2_tp_group_free(self.h))

@@ -41,7 +41,7 @@ def _run_steps(eng, model, ctx, prompts):
     return np.asarray(logits), toks, np.asarray(l2)
 
 
-def _worker(rank, world, uid_q, q):
+def _worker(rank, world, uid_q, q, inboxes):
     sys.path.insert(0, ROOT)
     from mlx_llm_b200 import _lib, engine as eng
     from tests import helpers as H
@@ -73,6 +73,26 @@ def _worker(rank, world, uid_q, q):
     m_tp = eng.CausalLm.synthetic(ctx, cfg, seed=3, tp=tp)
     out["synthetic"] = _run_steps(eng, m_tp, ctx, prompts)
     m_tp.free()
+    # the same models with the two reductions per layer done by one kernel over peer memory instead of NCCL
+    def gather(blob):
+        for r in range(world):
+            if r != rank:
+                inboxes[r].put((rank, blob))
+        every = {rank: blob}
+        while len(every) < world:
+            r, b = inboxes[rank].get(timeout=300)
+            every[r] = b
+        return [every[r] for r in range(world)]
+
+    out["peer_ok"] = tp.enable_peer(256, TP_CFG["hidden"], gather)
+    if out["peer_ok"]:
+        for name, bits in (("dense", 0), ("q4", 4)):
+            quant = eng.QuantSpec(64, bits) if bits else None
+            m_tp = H.build_engine_model(eng, ctx, TP_CFG, quant=quant, tp=tp)
+            tp.all_reduce_f32(buf, 1000)  # the ranks leave together: the kernel's waits are bounded
+            ctx.sync()
+            out[name + "_peer"] = _run_steps(eng, m_tp, ctx, prompts)
+            m_tp.free()
     if rank == 0:  # the single-GPU answers (no collective involved)
         for name, bits in (("dense", 0), ("q8", 8), ("q4", 4)):
             quant = eng.QuantSpec(64, bits) if bits else None
@@ -96,7 +116,8 @@ def test_tp2_matches_single_gpu():
 
     ctx = mp.get_context("spawn")
     q, uid_q = ctx.Queue(), ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, uid_q, q)) for r in range(2)]
+    inboxes = [ctx.Queue() for _ in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, uid_q, q, inboxes)) for r in range(2)]
     for p in procs:
         p.start()
     res = {}
@@ -107,10 +128,11 @@ def test_tp2_matches_single_gpu():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert res[0]["sum_ok"] and res[1]["sum_ok"] and res[0]["sum"] == 3.0
-    for name in ("dense", "q8", "q4", "synthetic"):
+    assert res[0]["peer_ok"] and res[1]["peer_ok"], "the peer regions could not be mapped on a two-GPU box"
+    for name in ("dense", "q8", "q4", "synthetic", "dense_peer", "q4_peer"):
         lg0, tok0, d0 = res[0][name]
         lg1, tok1, d1 = res[1][name]
-        ref_lg, ref_tok, ref_d = res[0][name + "_ref"]
+        ref_lg, ref_tok, ref_d = res[0][name.replace("_peer", "") + "_ref"]
         # both ranks hold the same bits (the all-reduce gives every rank the same sum, the rest is replicated)
         assert np.array_equal(lg0, lg1) and np.array_equal(d0, d1) and tok0 == tok1, name
         # against the single-GPU model: same bf16 weights, f32 partial sums added in another order
