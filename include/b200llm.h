@@ -259,25 +259,34 @@ int32_t b2_tp_group_free(b2_tp_group* g);
 int32_t b2_tp_group_info(const b2_tp_group* g, int32_t* rank, int32_t* world);
 /* In-place sum of an f32 device buffer over the group, enqueued on the context's stream. */
 int32_t b2_tp_all_reduce_f32(b2_tp_group* g, float* buf_dev, int64_t n);
-/* Reductions over peer memory instead of NCCL (ranks on one node whose GPUs reach one another over NVLink): one
- * kernel per reduction waits for every rank's projection, sums the ranks' f32 partial sums for the columns it
- * owns with loads from the peers' memory, adds the residual, and stores the new bf16 hidden state into every
- * rank's copy.  Set-up, once per group and before the group's models run: every rank calls b2_tp_peer_alloc
- * (max_tokens = the most tokens one step will carry; hidden = the model's hidden size, a multiple of 4 x world)
- * and gets the 64-byte handle of its region; the host program gathers the handles (the channel that carried the
- * id); every rank calls b2_tp_peer_attach with all of them in rank order.  From then on a model of that hidden
- * size on this group keeps its hidden state inside the region and reduces there; a step of more than
- * max_tokens tokens fails with B2_ERR_UNSUPPORTED.  If a region cannot be mapped (GPUs without peer access,
- * devices hidden from the process) attach fails with B2_ERR_UNSUPPORTED and the group stays on NCCL.  A group
- * created with id128 == NULL and world > 1 has no NCCL communicator and can only reduce this way.  Every wait
- * in the kernel is bounded (about four seconds); when one runs out the context's error word is raised,
- * b2_ctx_sync returns B2_ERR_TIMEOUT and later reductions return at once.  Ranks must enter their steps
- * within that time of one another: start them from a common point (a host barrier after loading). */
+/* Reductions over peer memory instead of NCCL (ranks on one node whose GPUs reach one another over NVLink).  Rank r
+ * owns the hidden-state columns [r*H/world, (r+1)*H/world).  The o_proj / down_proj kernels store each column range
+ * of their f32 partial sums from the epilogue straight into the owner's memory (slot [source rank] of the owner's
+ * region), so the transfer overlaps the multiplication tile by tile; one kernel then waits for every rank's
+ * projection, adds up the slots of its own columns (in rank order), adds the residual, and stores the new bf16
+ * hidden state into every rank's copy.  Set-up, once per group and before the group's models run: every rank
+ * calls b2_tp_peer_alloc (max_tokens = the most tokens one step will carry; hidden = the model's hidden size, a
+ * multiple of 4 x world) and gets the 64-byte handle of its region; the host program gathers the handles (the
+ * channel that carried the id); every rank calls b2_tp_peer_attach with all of them in rank order.  From then on
+ * a model of that hidden size on this group keeps its hidden state inside the region and reduces there; a step
+ * of more than max_tokens tokens fails with B2_ERR_UNSUPPORTED.  If a region cannot be mapped (GPUs without peer
+ * access, devices hidden from the process) attach fails with B2_ERR_UNSUPPORTED and the group stays on NCCL.  A
+ * group created with id128 == NULL and world > 1 has no NCCL communicator and can only reduce this way.  Every
+ * wait in the kernel is bounded (about four seconds); when one runs out the context's error word is raised,
+ * b2_ctx_sync returns B2_ERR_TIMEOUT and later reductions return at once.  Ranks must enter their steps within
+ * that time of one another: start them from a common point (a host barrier after loading). */
 int32_t b2_tp_peer_alloc(b2_tp_group* g, int32_t max_tokens, int32_t hidden, uint8_t* handle64_out);
 int32_t b2_tp_peer_attach(b2_tp_group* g, const uint8_t* handles /* world x 64 bytes */, int32_t n_handles);
-/* This rank's region: the f32 partial sums [max_tokens, hidden] a projection writes and the bf16 hidden state. */
-int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** part_dev, uint16_t** x_dev, int32_t* max_tokens, int32_t* hidden);
-/* x[0:rows] = bf16(x + bf16(sum over ranks of part[0:rows])) on every rank; enqueued on the context's stream. */
+/* This rank's region: `world` slots of f32 partial sums, slot s = [max_tokens, hidden] at slots_dev +
+ * s * slot_stride_floats (only this rank's columns of a slot are ever read), and the bf16 hidden state. */
+int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** slots_dev, int64_t* slot_stride_floats, uint16_t** x_dev,
+                           int32_t* max_tokens, int32_t* hidden);
+/* The first half on its own: this rank's partial projection x[m, in_dim] . W^T with `hidden` output features (W dense
+ * bf16 when bits == 0, else MLX group-64 Q4 / Q8), each column range stored from the kernel's epilogue into slot
+ * [this rank] of the range's owner. */
+int32_t b2_tp_peer_projection(b2_tp_group* g, const uint16_t* x_dev, int32_t m, int32_t in_dim, const void* w_dev,
+                              const uint16_t* scales_dev /* nullable when bits == 0 */, const uint16_t* biases_dev, int32_t bits);
+/* x[0:rows, own columns] = bf16(x + bf16(sum over s of slot s)) stored into every rank's x; on the context's stream. */
 int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows);
 /* All ranks of a group inside ONE process on one device (protocol tests without N GPUs): the groups' regions
  * are used directly, and the whole group's reduction runs as a single cooperative launch, because kernels

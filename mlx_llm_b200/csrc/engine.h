@@ -41,14 +41,15 @@ struct b2_tp_group {
     void* peer_local = nullptr;
     void* peer_base[8] = {};
     int peer_cap_rows = 0, peer_hidden = 0;
-    size_t peer_x_off = 0;
+    size_t peer_x_off = 0, peer_slot_bytes = 0;
     bool peer_ready = false, peer_ipc = false;
     uint32_t peer_seq = 0;  // number of the last reduction; every rank advances it in step
 };
 // In-place sum over the group of an f32 device buffer, enqueued on the context's stream.
 int32_t b2_tp_all_reduce_sum_f32(b2_tp_group* g, float* buf, size_t n);
-// Peer-memory path: the region's partial sums / hidden state of this rank, and the fused sum + residual add.
-float* b2_tp_peer_part(const b2_tp_group* g);
+// Peer-memory path: the projection's scattered f32 output, this rank's hidden state, the fused sum + residual add.
+struct GemmParams;
+void b2_tp_peer_scatter(const b2_tp_group* g, GemmParams& p);
 uint16_t* b2_tp_peer_x(const b2_tp_group* g);
 int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M);
 void b2_tp_peer_release(b2_tp_group* g);

@@ -125,8 +125,8 @@ int32_t gemm_reduce_residual(b2_model* m, const Proj& p, const uint16_t* a, int 
     g.ldres = H;
     g.epilogue = EPI_F32;
     b2_prof_mark(ctx, B2_CLS_GEMM);
-    if (m->ws.x_in_peer_region) {  // one kernel: sum of every rank's partial sums over peer memory + residual add
-        g.out_f32 = b2_tp_peer_part(m->tp);
+    if (m->ws.x_in_peer_region) {  // the epilogue stores each column range into its owner's memory; one kernel sums + adds the residual
+        b2_tp_peer_scatter(m->tp, g);
         B2_CHECK(b2_gemm_launch(ctx, g));
         b2_prof_mark(ctx, B2_CLS_COLLECTIVE);
         return b2_tp_peer_reduce_residual_launch(m->tp, M);

@@ -211,8 +211,9 @@ __global__ void __launch_bounds__(kThreads) gemm_tile_kernel(const GemmParams p)
                 const float v0 = acc[mt][nt][2 * hh], v1 = acc[mt][nt][2 * hh + 1];
                 const size_t o = (size_t)gm * p.ldo + gn;
                 if (EPI == EPI_F32) {
-                    p.out_f32[o] = v0;
-                    if (gn + 1 < N) p.out_f32[o + 1] = v1;
+                    float* dst = gemm_f32_dst(p, gm, gn);  // gn is even and the chunk a multiple of 4: both columns in one chunk
+                    dst[0] = v0;
+                    if (gn + 1 < N) dst[1] = v1;
                 } else if (EPI == EPI_BF16) {
                     if (gn + 1 < N)
                         *reinterpret_cast<uint32_t*>(p.out + o) = pack_bf2(v0, v1);

@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
                 if (ex.splits > 1) {
                     ex.partial[((size_t)blockIdx.y * M + tok) * N + row] = v;
                 } else if (EPI == EPI_F32) {
-                    p.out_f32[(size_t)tok * p.ldo + row] = v;
+                    *gemm_f32_dst(p, tok, row) = v;
                 } else if (EPI == EPI_BF16) {
                     p.out[(size_t)tok * p.ldo + row] = f2bf(v);
                 } else {
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
         }
         const float av[4] = {a.x, a.y, a.z, a.w};
         if (EPI == EPI_F32) {
-            *reinterpret_cast<float4*>(p.out_f32 + (size_t)tok * p.ldo + row) = a;
+            *reinterpret_cast<float4*>(gemm_f32_dst(p, tok, row)) = a;
         } else if (EPI == EPI_BF16) {
             uint2 o;
             o.x = pack_bf2(av[0], av[1]);
@@ -361,7 +361,7 @@ __global__ void stream_reduce_kernel(const GemmParams p, const float* __restrict
     for (int z = 0; z < splits; z++) a += partial[(size_t)z * total + i];
     const int t = (int)(i / p.N), f = (int)(i % p.N);
     if (EPI == EPI_F32)
-        p.out_f32[(size_t)t * p.ldo + f] = a;
+        *gemm_f32_dst(p, t, f) = a;
     else if (EPI == EPI_BF16)
         p.out[(size_t)t * p.ldo + f] = f2bf(a);
     else

@@ -408,7 +408,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         if (splits > 1) {
                             plan.partial[((size_t)pc.split * M + t) * N + f] = a;
                         } else if (EPI == EPI_F32) {
-                            p.out_f32[(size_t)t * p.ldo + f] = a;
+                            *gemm_f32_dst(p, t, f) = a;
                         } else if (EPI == EPI_BF16) {
                             p.out[(size_t)t * p.ldo + f] = f2bf(a);
                         } else {
@@ -551,7 +551,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict
     for (int z = 0; z < splits; z++) a += partial[(size_t)z * total + i];
     const int t = (int)(i / p.N), f = (int)(i % p.N);
     if (EPI == EPI_F32)
-        p.out_f32[(size_t)t * p.ldo + f] = a;
+        *gemm_f32_dst(p, t, f) = a;
     else if (EPI == EPI_BF16)
         p.out[(size_t)t * p.ldo + f] = f2bf(a);
     else

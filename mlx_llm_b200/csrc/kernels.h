@@ -45,7 +45,26 @@ struct GemmParams {
     uint16_t* out;           // bf16 output (EPI_BF16 / EPI_BF16_RESADD)
     const uint16_t* res;     // residual input (may alias out)
     float* out_f32;          // EPI_F32
+    // EPI_F32 split by column range (tensor-parallel reductions over peer memory): when f32_chunk > 0, column f of
+    // the result is stored at out_f32_by_chunk[f / f32_chunk] + t*ldo + f instead, each entry being the same
+    // [M, ldo] view inside another rank's memory, so that the projection's epilogue itself carries every partial
+    // sum to the rank that will add it up.  f32_chunk is a multiple of 4.
+    float* out_f32_by_chunk[8];
+    int f32_chunk;
 };
+#ifdef __CUDACC__
+__device__ __forceinline__ float* gemm_f32_dst(const GemmParams& p, int t, int f) {
+    float* base = p.out_f32;
+    if (p.f32_chunk > 0) {
+        const int q = f / p.f32_chunk;
+        base = p.out_f32_by_chunk[0];
+#pragma unroll
+        for (int i = 1; i < 8; i++)
+            if (q == i) base = p.out_f32_by_chunk[i];
+    }
+    return base + (size_t)t * p.ldo + f;
+}
+#endif
 int32_t b2_gemm_launch(b2_ctx* ctx, const GemmParams& p);
 // weight-streaming kernel for up to 64 tokens (gemm_stream.cu): taken by b2_gemm_launch when eligible.
 bool b2_gemm_stream_eligible(const GemmParams& p);

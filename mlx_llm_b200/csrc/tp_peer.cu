@@ -1,19 +1,24 @@
-// Tensor-parallel reduction over peer memory (NVLink / NVSwitch), one kernel per reduction:
+// Tensor-parallel reduction over peer memory (NVLink / NVSwitch), fused with the projection before it and the
+// residual add after it:
 //
 //     x = bf16(x + bf16(sum over ranks of the projection's f32 partial sums))
 //
-// on every rank, without a library collective.  Every rank exports one region (cudaIpc) holding its partial
-// sums, its copy of the hidden state x and two sets of flags; every rank maps every other rank's region.
-// Rank r owns the columns [r*H/world, (r+1)*H/world): its kernel waits until every rank's projection has
-// finished (flag1), reads that column range of every rank's partial sums (peer loads, summed in rank order so
-// the result does not depend on timing), adds the residual, rounds, and stores the new bf16 values into
-// EVERY rank's x (peer stores).  Block g then tells block g of every other rank that its rows are in place
-// (flag2) and waits for theirs, so that when the kernel ends this rank's x is complete.  Flags carry the
-// number of the reduction (a counter every rank advances in step), so nothing is ever reset.
+// on every rank, without a library collective.  Every rank exports one region (cudaIpc) holding `world` slots of
+// f32 partial sums, its copy of the hidden state x and two sets of flags; every rank maps every other rank's
+// region.  Rank r owns the columns [r*H/world, (r+1)*H/world).
+//   1. The projection kernels (o_proj, down_proj) store their f32 results by column range: the columns rank q
+//      owns go straight from the epilogue into slot [this rank] of q's region (GemmParams::out_f32_by_chunk), so
+//      the partial sums cross NVLink tile by tile while other tiles are still being multiplied.
+//   2. One kernel (below) tells the other ranks that this rank's projection has ended (flag1), waits for theirs,
+//      adds up the `world` slots of its own columns -- local reads, in rank order, so the result does not depend
+//      on timing -- adds the residual, rounds, and stores the new bf16 values into EVERY rank's x (peer stores).
+//      Block g then tells block g of every other rank that its rows are in place (flag2) and waits for theirs,
+//      so that when the kernel ends this rank's x is complete.
+// Flags carry the number of the reduction (a counter every rank advances in step), so nothing is ever reset.
 //
-// Why one buffer of each kind suffices: a rank overwrites its partial sums only after its own kernel ended,
-// which it does only after every other rank signalled flag2, which a rank does only after it finished reading
-// the partial sums; and a rank's columns of x are written by their owner only.
+// Why one set of slots suffices: a rank starts its next projection only after its own kernel 2 ended, which it
+// does only after every other rank signalled flag2, which a rank does only after it finished reading its slots;
+// and a rank's columns of x are written by their owner only.
 //
 // There is no counterpart in the reference (a single-device program).  The waits are bounded: on expiry the
 // kernel raises the context's error word and returns; later reductions see the word and return at once.
@@ -37,7 +42,8 @@ struct PeerReduceParams {
     int rank;                        // -1: blockIdx.y is the rank (the whole group emulated by one launch)
     int world, M, H, chunk;          // chunk = H / world columns owned by each rank
     uint32_t seq;
-    size_t x_off;                    // offset of x in a region (the partial sums sit at kDataOff)
+    size_t slot_bytes;               // slot s of a region sits at kDataOff + s * slot_bytes
+    size_t x_off;                    // offset of x in a region
     int* err;                        // the error word of the context (of rank 0's context when emulating)
 };
 
@@ -71,7 +77,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_residual_kernel(const Peer
     if (tid == 0) gave_up = (*reinterpret_cast<volatile int*>(p.err) != 0);
     __syncthreads();
     if (gave_up) return;  // an earlier wait ran out: the group is broken, do not wait again
-    // this rank's projection ended before this launch began: tell the others
+    // this rank's projection, and with it its stores into the other ranks' slots, ended before this launch began
     if (g == 0 && tid < p.world && tid != r) {
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t*>(p.base[tid] + kFlag1Off) + r, p.seq);
@@ -93,7 +99,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_residual_kernel(const Peer
         float4 part[kMaxWorld];
 #pragma unroll
         for (int s = 0; s < kMaxWorld; s++)
-            if (s < p.world) part[s] = ld_peer_f4(reinterpret_cast<const float*>(p.base[s] + kDataOff) + off);
+            if (s < p.world) part[s] = ld_peer_f4(reinterpret_cast<const float*>(p.base[r] + kDataOff + (size_t)s * p.slot_bytes) + off);
         float4 acc = part[0];
 #pragma unroll
         for (int s = 1; s < kMaxWorld; s++)
@@ -129,15 +135,21 @@ int32_t ensure_err_word(b2_ctx* ctx) {
     return B2_OK;
 }
 
-size_t region_bytes(int cap_rows, int hidden, size_t* x_off) {
-    const size_t part = ((size_t)cap_rows * hidden * 4 + 255) / 256 * 256;
-    *x_off = kDataOff + part;
+size_t region_bytes(int cap_rows, int hidden, int world, size_t* slot_bytes, size_t* x_off) {
+    *slot_bytes = ((size_t)cap_rows * hidden * 4 + 255) / 256 * 256;
+    *x_off = kDataOff + (size_t)world * *slot_bytes;
     return *x_off + ((size_t)cap_rows * hidden * 2 + 255) / 256 * 256;
 }
 
 }  // namespace
 
-float* b2_tp_peer_part(const b2_tp_group* g) { return reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + kDataOff); }
+// Where this rank's projection stores its f32 result: the columns rank q owns go to slot [this rank] of q's region.
+void b2_tp_peer_scatter(const b2_tp_group* g, GemmParams& p) {
+    p.f32_chunk = g->peer_hidden / g->world;
+    for (int q = 0; q < g->world; q++)
+        p.out_f32_by_chunk[q] = reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[q]) + kDataOff + (size_t)g->rank * g->peer_slot_bytes);
+    p.out_f32 = p.out_f32_by_chunk[g->rank];
+}
 uint16_t* b2_tp_peer_x(const b2_tp_group* g) { return reinterpret_cast<uint16_t*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + g->peer_x_off); }
 
 // x (the region's) += sum over ranks of the regions' partial sums, for the first M rows; on the context's stream.
@@ -153,6 +165,7 @@ int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M) {
     p.H = g->peer_hidden;
     p.chunk = g->peer_hidden / g->world;
     p.seq = ++g->peer_seq;
+    p.slot_bytes = g->peer_slot_bytes;
     p.x_off = g->peer_x_off;
     p.err = g->ctx->dev_err;
     tp_peer_reduce_residual_kernel<<<grid_for(M, p.chunk, kMaxCtas), 256, 0, g->ctx->stream>>>(p);
@@ -172,8 +185,8 @@ int32_t b2_tp_peer_alloc(b2_tp_group* g, int32_t max_tokens, int32_t hidden, uin
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
     B2_CUDA(cudaSetDevice(g->ctx->device));
     B2_CHECK(ensure_err_word(g->ctx));
-    size_t x_off = 0;
-    const size_t bytes = region_bytes(max_tokens, hidden, &x_off);
+    size_t x_off = 0, slot_bytes = 0;
+    const size_t bytes = region_bytes(max_tokens, hidden, g->world, &slot_bytes, &x_off);
     void* base = nullptr;
     B2_CUDA(cudaMalloc(&base, bytes));
     B2_CUDA(cudaMemsetAsync(base, 0, bytes, g->ctx->stream));
@@ -188,6 +201,7 @@ int32_t b2_tp_peer_alloc(b2_tp_group* g, int32_t max_tokens, int32_t hidden, uin
     g->peer_cap_rows = max_tokens;
     g->peer_hidden = hidden;
     g->peer_x_off = x_off;
+    g->peer_slot_bytes = slot_bytes;
     return B2_OK;
 }
 
@@ -234,9 +248,11 @@ int32_t b2_tp_peer_attach_local(b2_tp_group* const* groups, int32_t n) {
     return B2_OK;
 }
 
-int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** part_dev, uint16_t** x_dev, int32_t* max_tokens, int32_t* hidden) {
+int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** slots_dev, int64_t* slot_stride_floats, uint16_t** x_dev, int32_t* max_tokens,
+                           int32_t* hidden) {
     B2_REQUIRE(g && g->peer_ready, B2_ERR_MSG, "b2_tp_peer_buffers: no attached peer regions");
-    if (part_dev) *part_dev = b2_tp_peer_part(g);
+    if (slots_dev) *slots_dev = reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + kDataOff);
+    if (slot_stride_floats) *slot_stride_floats = (int64_t)(g->peer_slot_bytes / 4);
     if (x_dev) *x_dev = b2_tp_peer_x(g);
     if (max_tokens) *max_tokens = g->peer_cap_rows;
     if (hidden) *hidden = g->peer_hidden;
@@ -244,6 +260,32 @@ int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** part_dev, uint16_t** x_
 }
 
 int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows) { return b2_tp_peer_reduce_residual_launch(g, rows); }
+
+// The first half of the fused reduction on its own: this rank's partial projection x[m, in_dim] . W^T (W dense bf16
+// when bits == 0, else MLX group-64 Q4 / Q8 with its scales and biases; `hidden` output features), every column
+// range stored from the kernel's epilogue into slot [this rank] of the range's owner.
+int32_t b2_tp_peer_projection(b2_tp_group* g, const uint16_t* x_dev, int32_t m, int32_t in_dim, const void* w_dev, const uint16_t* scales_dev,
+                              const uint16_t* biases_dev, int32_t bits) {
+    B2_REQUIRE(g && g->peer_ready && x_dev && w_dev, B2_ERR_MSG, "b2_tp_peer_projection: null argument or no attached peer regions");
+    B2_REQUIRE(bits == 0 || ((bits == 4 || bits == 8) && scales_dev && biases_dev), B2_ERR_UNSUPPORTED, "b2_tp_peer_projection: bits must be 0, 4 or 8");
+    B2_REQUIRE(m >= 0 && m <= g->peer_cap_rows, B2_ERR_MSG, "b2_tp_peer_projection: more rows than the regions hold");
+    GemmParams p{};
+    p.x = x_dev;
+    p.w = w_dev;
+    p.scales = scales_dev;
+    p.biases = biases_dev;
+    p.bits = bits;
+    p.group = 64;
+    p.M = m;
+    p.N = g->peer_hidden;
+    p.K = in_dim;
+    p.ldx = in_dim;
+    p.ldo = g->peer_hidden;
+    p.ldres = g->peer_hidden;
+    p.epilogue = EPI_F32;
+    b2_tp_peer_scatter(g, p);
+    return b2_gemm_launch(g->ctx, p);
+}
 
 // The whole group's reduction as ONE launch (grid.y = rank) for groups attached with b2_tp_peer_attach_local:
 // kernels that wait on one another must not be separate launches on one device.
@@ -263,6 +305,7 @@ int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, 
     uint32_t seq = 0;
     for (int s = 0; s < n; s++) seq = ++groups[s]->peer_seq;
     p.seq = seq;
+    p.slot_bytes = g0->peer_slot_bytes;
     p.x_off = g0->peer_x_off;
     p.err = g0->ctx->dev_err;
     // every block of every rank resident at once: a cooperative launch, sized to fit

@@ -247,10 +247,16 @@ class TpGroup:
         return True
 
     def peer_buffers(self):
-        part, x = C.c_void_p(), C.c_void_p()
+        """(slots pointer, slot stride in floats, x pointer, max_tokens, hidden) of this rank's region."""
+        slots, x = C.c_void_p(), C.c_void_p()
+        stride = C.c_int64()
         cap, hidden = C.c_int32(), C.c_int32()
-        check(load().b2_tp_peer_buffers(self.h, C.byref(part), C.byref(x), C.byref(cap), C.byref(hidden)))
-        return part.value, x.value, cap.value, hidden.value
+        check(load().b2_tp_peer_buffers(self.h, C.byref(slots), C.byref(stride), C.byref(x), C.byref(cap), C.byref(hidden)))
+        return slots.value, stride.value, x.value, cap.value, hidden.value
+
+    def peer_projection(self, x, m, in_dim, w, scales=None, biases=None, bits=0):
+        check(load().b2_tp_peer_projection(self.h, ptr(x), int(m), int(in_dim), ptr(w), ptr(scales) if scales is not None else None,
+                                           ptr(biases) if biases is not None else None, int(bits)))
 
     def peer_reduce_residual(self, rows):
         check(load().b2_tp_peer_reduce_residual(self.h, int(rows)))

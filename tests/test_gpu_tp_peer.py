@@ -40,14 +40,15 @@ def test_peer_reduce_residual_matches_numpy(world, hidden, cap):
         g.peer_alloc(cap, hidden)
     eng.TpGroup.peer_attach_local(groups)
     bufs = [g.peer_buffers() for g in groups]
-    assert all(b[2] == cap and b[3] == hidden for b in bufs)
+    assert all(b[3] == cap and b[4] == hidden for b in bufs)
     rng = np.random.default_rng(world * 1000 + hidden)
     x = H.f32_to_bf16_np(rng.standard_normal((cap, hidden)).astype(np.float32))
     for rows in (cap, 1, max(1, cap // 3), cap):  # consecutive reductions reuse the regions and the flags
         parts = [(rng.standard_normal((rows, hidden)) * 3).astype(np.float32) for _ in range(world)]
-        for r in range(world):
-            _upload(lib, ctx, bufs[r][0], parts[r])
-            _upload(lib, ctx, bufs[r][1], x)
+        for r in range(world):  # slot s of rank r's region holds rank s's partial sums (r's columns of it are read)
+            for src in range(world):
+                _upload(lib, ctx, bufs[r][0] + src * bufs[r][1] * 4, parts[src])
+            _upload(lib, ctx, bufs[r][2], x)
         eng.TpGroup.peer_reduce_residual_local(groups, rows)
         ctx.sync()
         acc = parts[0].copy()
@@ -57,7 +58,7 @@ def test_peer_reduce_residual_matches_numpy(world, hidden, cap):
         y = H.bf16_to_f32_np(H.f32_to_bf16_np(acc))
         want[:rows] = H.f32_to_bf16_np(H.bf16_to_f32_np(x[:rows]) + y)
         for r in range(world):
-            got = _download(lib, ctx, bufs[r][1], (cap, hidden), np.uint16)
+            got = _download(lib, ctx, bufs[r][2], (cap, hidden), np.uint16)
             assert np.array_equal(got, want), (world, rows, r)
         x = want
     for g in groups:
@@ -83,4 +84,58 @@ def test_peer_reduce_argument_errors():
         buf = ctx.buf(np.zeros(8, np.float32))
         g.all_reduce_f32(buf, 8)              # created without an NCCL id
     g.free()
+    ctx.close()
+
+
+@pytest.mark.parametrize("world,m,hidden,k_local,bits", [(2, 700, 1024, 512, 4), (4, 300, 1024, 256, 0), (2, 8, 1024, 512, 4),
+                                                         (4, 40, 2048, 1024, 8), (2, 33, 192, 128, 4), (8, 520, 5120, 256, 4)])
+def test_projection_scatters_into_owners_and_reduces(world, m, hidden, k_local, bits):
+    """The fused path end to end on one GPU: every (emulated) rank's projection stores each column range from its
+    epilogue into the owner's slot, the single-launch reduction adds the slots and the residual.  The expected
+    partial sums come from the same projection kernels with a plain f32 output, so the comparison is bit-exact.
+    Shapes reach the tcgen05 pair kernel (> 64 tokens), the streaming kernel with its in-kernel and separate
+    split-K sums (<= 16 / <= 64 tokens) and the warp-level tile kernel (width not a multiple of 128)."""
+    from mlx_llm_b200 import _lib, engine as eng, kernels as K
+
+    lib = _lib.load()
+    ctx = _lib.Context(0)
+    cap = m + 5
+    groups = [eng.TpGroup(ctx, None, r, world) for r in range(world)]
+    for g in groups:
+        g.peer_alloc(cap, hidden)
+    eng.TpGroup.peer_attach_local(groups)
+    bufs = [g.peer_buffers() for g in groups]
+    rng = np.random.default_rng(world + m + hidden + bits)
+    x = H.f32_to_bf16_np(rng.standard_normal((cap, hidden)).astype(np.float32))
+    parts = []
+    for r, g in enumerate(groups):
+        a = ctx.buf(H.f32_to_bf16_np(rng.standard_normal((m, k_local)).astype(np.float32)))
+        yf = ctx.empty((m, hidden), np.float32)
+        if bits:
+            packed = rng.integers(0, 2**32, size=(hidden, k_local * bits // 32), dtype=np.uint32)
+            s = np.abs(rng.standard_normal((hidden, k_local // 64)).astype(np.float32) * 0.02) / 7.5
+            scales = H.f32_to_bf16_np(s)
+            biases = H.f32_to_bf16_np(-8.0 * H.bf16_to_f32_np(scales))
+            dw, ds, db = ctx.buf(packed), ctx.buf(scales), ctx.buf(biases)
+            K.qmm(ctx, a, dw, ds, db, m, hidden, k_local, bits, None, yf)
+            g.peer_projection(a, m, k_local, dw, ds, db, bits)
+        else:
+            dw = ctx.buf(H.f32_to_bf16_np(rng.standard_normal((hidden, k_local)).astype(np.float32) * 0.03))
+            K.linear(ctx, a, dw, m, hidden, k_local, None, yf)
+            g.peer_projection(a, m, k_local, dw)
+        ctx.sync()
+        parts.append(yf.download())
+        _upload(lib, ctx, bufs[r][2], x)
+    eng.TpGroup.peer_reduce_residual_local(groups, m)
+    ctx.sync()
+    acc = parts[0].copy()
+    for r in range(1, world):
+        acc = acc + parts[r]
+    want = x.copy()
+    want[:m] = H.f32_to_bf16_np(H.bf16_to_f32_np(x[:m]) + H.bf16_to_f32_np(H.f32_to_bf16_np(acc)))
+    for r in range(world):
+        got = _download(lib, ctx, bufs[r][2], (cap, hidden), np.uint16)
+        assert np.array_equal(got, want), (r, int((got != want).sum()))
+    for g in groups:
+        g.free()
     ctx.close()
