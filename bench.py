@@ -140,7 +140,7 @@ def tp_setup(args, rank, world, local_rank):
         uid = bytes(t.cpu().numpy().tobytes())
     tp = eng.TpGroup(ctx, uid, rank, world)
     tp.reduce_path = "none" if world == 1 else "nccl"
-    if world > 1 and args.tp_reduce == "peer":
+    if world > 1 and args.tp_reduce in ("peer", "peer-push"):
         def gather(blob):
             mine = torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda()
             every = [torch.zeros_like(mine) for _ in range(world)]
@@ -149,6 +149,9 @@ def tp_setup(args, rank, world, local_rank):
 
         if tp.enable_peer(args.chunk + 512, shape["hidden_size"], gather):
             tp.reduce_path = "peer memory"
+            if args.tp_reduce == "peer-push":
+                tp.peer_set_push(True)
+                tp.reduce_path = "peer memory, pushed"
     cfg = eng.model_config(**shape, quant_bits=8, quant_group=64)
     model = eng.CausalLm.synthetic(ctx, cfg, seed=0, tp=tp)
     model._tp = tp  # the model points at its group: keep it alive
@@ -218,6 +221,7 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
                     ramp_steps=args.ramp, max_pages=int(ccfg.max_pages), peak_concurrent=int(s1.get("peak_concurrent", 0)),
                     parallelism=(f"tensor-parallel x{world} over KV heads; o_proj / down_proj partial sums (f32) reduced by: "
                                  + {"peer memory": "one kernel over peer memory (loads from every rank, sum + residual add, stores to every rank)",
+                                    "peer memory, pushed": "projection epilogues storing each column range into its owner's memory + one kernel (sum + residual add, stores to every rank)",
                                     "nccl": "NCCL all-reduce + residual-add kernel", "none": "nothing (one rank)"}[getattr(model._tp, "reduce_path", "none")]
                                  if tp_mode
                                  else f"replica x{world}, requests sharded id mod N"),
@@ -504,7 +508,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0 = the full 32); not a valid bench line")
     ap.add_argument("--cpu-layers", dest="cpu_layers", type=int, default=2)
     ap.add_argument("--cpu-requests", dest="cpu_requests", type=int, default=4)
-    ap.add_argument("--tp-reduce", dest="tp_reduce", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--tp-reduce", dest="tp_reduce", default="peer", choices=["peer", "peer-push", "nccl"],
                     help="qwen3_32b_q8_tp: the reduction after o_proj / down_proj (peer falls back to nccl when a region cannot be mapped)")
     ap.add_argument("--profiler-range", dest="profiler_range", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")

@@ -260,11 +260,14 @@ int32_t b2_tp_group_info(const b2_tp_group* g, int32_t* rank, int32_t* world);
 /* In-place sum of an f32 device buffer over the group, enqueued on the context's stream. */
 int32_t b2_tp_all_reduce_f32(b2_tp_group* g, float* buf_dev, int64_t n);
 /* Reductions over peer memory instead of NCCL (ranks on one node whose GPUs reach one another over NVLink).  Rank r
- * owns the hidden-state columns [r*H/world, (r+1)*H/world).  The o_proj / down_proj kernels store each column range
- * of their f32 partial sums from the epilogue straight into the owner's memory (slot [source rank] of the owner's
- * region), so the transfer overlaps the multiplication tile by tile; one kernel then waits for every rank's
- * projection, adds up the slots of its own columns (in rank order), adds the residual, and stores the new bf16
- * hidden state into every rank's copy.  Set-up, once per group and before the group's models run: every rank
+ * owns the hidden-state columns [r*H/world, (r+1)*H/world).  The o_proj / down_proj kernels write their f32 partial
+ * sums into slot [this rank] of a region every rank exports; one kernel then waits for every rank's projection,
+ * adds up the ranks' partial sums of its own columns (loads from the peers' memory, in rank order), adds the
+ * residual, and stores the new bf16 hidden state into every rank's copy.  In push mode (b2_tp_peer_set_push) the
+ * projection's epilogue instead stores each column range straight into the owner's memory, so the transfer overlaps
+ * the multiplication tile by tile, and the sums read local memory only: worth it when a projection runs several
+ * waves of tiles (a single wave ends in one burst of remote stores that delays the kernel's end).
+ * Set-up, once per group and before the group's models run: every rank
  * calls b2_tp_peer_alloc (max_tokens = the most tokens one step will carry; hidden = the model's hidden size, a
  * multiple of 4 x world) and gets the 64-byte handle of its region; the host program gathers the handles (the
  * channel that carried the id); every rank calls b2_tp_peer_attach with all of them in rank order.  From then on
@@ -278,7 +281,8 @@ int32_t b2_tp_all_reduce_f32(b2_tp_group* g, float* buf_dev, int64_t n);
 int32_t b2_tp_peer_alloc(b2_tp_group* g, int32_t max_tokens, int32_t hidden, uint8_t* handle64_out);
 int32_t b2_tp_peer_attach(b2_tp_group* g, const uint8_t* handles /* world x 64 bytes */, int32_t n_handles);
 /* This rank's region: `world` slots of f32 partial sums, slot s = [max_tokens, hidden] at slots_dev +
- * s * slot_stride_floats (only this rank's columns of a slot are ever read), and the bf16 hidden state. */
+ * s * slot_stride_floats, and the bf16 hidden state.  Rank s's partial sums are read from slot s of s's own region,
+ * or in push mode from slot s of the reading rank's region (its own columns only). */
 int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** slots_dev, int64_t* slot_stride_floats, uint16_t** x_dev,
                            int32_t* max_tokens, int32_t* hidden);
 /* The first half on its own: this rank's partial projection x[m, in_dim] . W^T with `hidden` output features (W dense
@@ -286,7 +290,11 @@ int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** slots_dev, int64_t* slo
  * [this rank] of the range's owner. */
 int32_t b2_tp_peer_projection(b2_tp_group* g, const uint16_t* x_dev, int32_t m, int32_t in_dim, const void* w_dev,
                               const uint16_t* scales_dev /* nullable when bits == 0 */, const uint16_t* biases_dev, int32_t bits);
-/* x[0:rows, own columns] = bf16(x + bf16(sum over s of slot s)) stored into every rank's x; on the context's stream. */
+/* 1: projections store by column range into the owners' regions; 0 (default): into their own region.  Every rank of
+ * the group must choose the same mode, between steps. */
+int32_t b2_tp_peer_set_push(b2_tp_group* g, int32_t push);
+/* x[0:rows, own columns] = bf16(x + bf16(sum over s of rank s's partial sums)) stored into every rank's x; on the
+ * context's stream. */
 int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows);
 /* All ranks of a group inside ONE process on one device (protocol tests without N GPUs): the groups' regions
  * are used directly, and the whole group's reduction runs as a single cooperative launch, because kernels

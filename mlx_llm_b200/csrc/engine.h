@@ -42,7 +42,7 @@ struct b2_tp_group {
     void* peer_base[8] = {};
     int peer_cap_rows = 0, peer_hidden = 0;
     size_t peer_x_off = 0, peer_slot_bytes = 0;
-    bool peer_ready = false, peer_ipc = false;
+    bool peer_ready = false, peer_ipc = false, peer_push = false;
     uint32_t peer_seq = 0;  // number of the last reduction; every rank advances it in step
 };
 // In-place sum over the group of an f32 device buffer, enqueued on the context's stream.

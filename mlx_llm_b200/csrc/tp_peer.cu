@@ -6,18 +6,21 @@
 // on every rank, without a library collective.  Every rank exports one region (cudaIpc) holding `world` slots of
 // f32 partial sums, its copy of the hidden state x and two sets of flags; every rank maps every other rank's
 // region.  Rank r owns the columns [r*H/world, (r+1)*H/world).
-//   1. The projection kernels (o_proj, down_proj) store their f32 results by column range: the columns rank q
-//      owns go straight from the epilogue into slot [this rank] of q's region (GemmParams::out_f32_by_chunk), so
-//      the partial sums cross NVLink tile by tile while other tiles are still being multiplied.
+//   1. The projection kernels (o_proj, down_proj) store their f32 results into slot [this rank]: of their own
+//      region (default), or -- push mode, b2_tp_peer_set_push -- by column range straight from the epilogue into the
+//      region of the rank that owns the columns (GemmParams::out_f32_by_chunk), so the partial sums cross NVLink
+//      tile by tile while other tiles are still being multiplied.  Push pays off when a projection runs several
+//      waves of tiles; a single wave ends all its epilogues at once and the burst of remote stores then delays the
+//      kernel's end by more than the loads of the default mode cost (measured at two ranks, 5120 wide, ~700 tokens).
 //   2. One kernel (below) tells the other ranks that this rank's projection has ended (flag1), waits for theirs,
-//      adds up the `world` slots of its own columns -- local reads, in rank order, so the result does not depend
-//      on timing -- adds the residual, rounds, and stores the new bf16 values into EVERY rank's x (peer stores).
-//      Block g then tells block g of every other rank that its rows are in place (flag2) and waits for theirs,
-//      so that when the kernel ends this rank's x is complete.
+//      adds up the `world` partial sums of its own columns -- peer loads (default) or local reads (push), in rank
+//      order, so the result does not depend on timing -- adds the residual, rounds, and stores the new bf16 values
+//      into EVERY rank's x (peer stores).  Block g then tells block g of every other rank that its rows are in place
+//      (flag2) and waits for theirs, so that when the kernel ends this rank's x is complete.
 // Flags carry the number of the reduction (a counter every rank advances in step), so nothing is ever reset.
 //
 // Why one set of slots suffices: a rank starts its next projection only after its own kernel 2 ended, which it
-// does only after every other rank signalled flag2, which a rank does only after it finished reading its slots;
+// does only after every other rank signalled flag2, which a rank does only after it finished reading the slots;
 // and a rank's columns of x are written by their owner only.
 //
 // There is no counterpart in the reference (a single-device program).  The waits are bounded: on expiry the
@@ -40,6 +43,8 @@ constexpr long long kWaitCycles = 8000000000LL;         // ~4 s at 1.9 GHz
 struct PeerReduceParams {
     unsigned char* base[kMaxWorld];  // every rank's region as mapped in this process
     int rank;                        // -1: blockIdx.y is the rank (the whole group emulated by one launch)
+    int push;                        // 1: rank s's partial sums of this rank's columns already sit in slot s of THIS rank's
+                                     // region (stored there by s's projection); 0: they sit in slot s of s's own region
     int world, M, H, chunk;          // chunk = H / world columns owned by each rank
     uint32_t seq;
     size_t slot_bytes;               // slot s of a region sits at kDataOff + s * slot_bytes
@@ -99,7 +104,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_residual_kernel(const Peer
         float4 part[kMaxWorld];
 #pragma unroll
         for (int s = 0; s < kMaxWorld; s++)
-            if (s < p.world) part[s] = ld_peer_f4(reinterpret_cast<const float*>(p.base[r] + kDataOff + (size_t)s * p.slot_bytes) + off);
+            if (s < p.world) part[s] = ld_peer_f4(reinterpret_cast<const float*>(p.base[p.push ? r : s] + kDataOff + (size_t)s * p.slot_bytes) + off);
         float4 acc = part[0];
 #pragma unroll
         for (int s = 1; s < kMaxWorld; s++)
@@ -143,12 +148,15 @@ size_t region_bytes(int cap_rows, int hidden, int world, size_t* slot_bytes, siz
 
 }  // namespace
 
-// Where this rank's projection stores its f32 result: the columns rank q owns go to slot [this rank] of q's region.
+// Where this rank's projection stores its f32 result: slot [this rank] of its own region, or (push mode) the columns
+// rank q owns straight into slot [this rank] of q's region.
 void b2_tp_peer_scatter(const b2_tp_group* g, GemmParams& p) {
+    const size_t slot = kDataOff + (size_t)g->rank * g->peer_slot_bytes;
+    p.out_f32 = reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + slot);
+    p.f32_chunk = 0;
+    if (!g->peer_push) return;
     p.f32_chunk = g->peer_hidden / g->world;
-    for (int q = 0; q < g->world; q++)
-        p.out_f32_by_chunk[q] = reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[q]) + kDataOff + (size_t)g->rank * g->peer_slot_bytes);
-    p.out_f32 = p.out_f32_by_chunk[g->rank];
+    for (int q = 0; q < g->world; q++) p.out_f32_by_chunk[q] = reinterpret_cast<float*>(static_cast<unsigned char*>(g->peer_base[q]) + slot);
 }
 uint16_t* b2_tp_peer_x(const b2_tp_group* g) { return reinterpret_cast<uint16_t*>(static_cast<unsigned char*>(g->peer_base[g->rank]) + g->peer_x_off); }
 
@@ -160,6 +168,7 @@ int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M) {
     PeerReduceParams p{};
     for (int s = 0; s < g->world; s++) p.base[s] = static_cast<unsigned char*>(g->peer_base[s]);
     p.rank = g->rank;
+    p.push = g->peer_push ? 1 : 0;
     p.world = g->world;
     p.M = M;
     p.H = g->peer_hidden;
@@ -259,6 +268,13 @@ int32_t b2_tp_peer_buffers(const b2_tp_group* g, float** slots_dev, int64_t* slo
     return B2_OK;
 }
 
+int32_t b2_tp_peer_set_push(b2_tp_group* g, int32_t push) {
+    B2_REQUIRE(g, B2_ERR_MSG, "b2_tp_peer_set_push: null group");
+    B2_CUDA(cudaStreamSynchronize(g->ctx->stream));
+    g->peer_push = push != 0;
+    return B2_OK;
+}
+
 int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows) { return b2_tp_peer_reduce_residual_launch(g, rows); }
 
 // The first half of the fused reduction on its own: this rank's partial projection x[m, in_dim] . W^T (W dense bf16
@@ -298,6 +314,7 @@ int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, 
     PeerReduceParams p{};
     for (int s = 0; s < n; s++) p.base[s] = static_cast<unsigned char*>(g0->peer_base[s]);
     p.rank = -1;
+    p.push = g0->peer_push ? 1 : 0;
     p.world = n;
     p.M = rows;
     p.H = g0->peer_hidden;

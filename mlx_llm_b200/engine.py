@@ -258,6 +258,9 @@ class TpGroup:
         check(load().b2_tp_peer_projection(self.h, ptr(x), int(m), int(in_dim), ptr(w), ptr(scales) if scales is not None else None,
                                            ptr(biases) if biases is not None else None, int(bits)))
 
+    def peer_set_push(self, push):
+        check(load().b2_tp_peer_set_push(self.h, 1 if push else 0))
+
     def peer_reduce_residual(self, rows):
         check(load().b2_tp_peer_reduce_residual(self.h, int(rows)))
 

@@ -86,12 +86,13 @@ def _worker(rank, world, uid_q, q, inboxes):
 
     out["peer_ok"] = tp.enable_peer(256, TP_CFG["hidden"], gather)
     if out["peer_ok"]:
-        for name, bits in (("dense", 0), ("q4", 4)):
+        for name, bits, push in (("dense", 0, False), ("q4", 4, False), ("q4", 4, True)):
             quant = eng.QuantSpec(64, bits) if bits else None
             m_tp = H.build_engine_model(eng, ctx, TP_CFG, quant=quant, tp=tp)
+            tp.peer_set_push(push)
             tp.all_reduce_f32(buf, 1000)  # the ranks leave together: the kernel's waits are bounded
             ctx.sync()
-            out[name + "_peer"] = _run_steps(eng, m_tp, ctx, prompts)
+            out[name + ("_push" if push else "_peer")] = _run_steps(eng, m_tp, ctx, prompts)
             m_tp.free()
     if rank == 0:  # the single-GPU answers (no collective involved)
         for name, bits in (("dense", 0), ("q8", 8), ("q4", 4)):
@@ -129,10 +130,10 @@ def test_tp2_matches_single_gpu():
         assert p.exitcode == 0
     assert res[0]["sum_ok"] and res[1]["sum_ok"] and res[0]["sum"] == 3.0
     assert res[0]["peer_ok"] and res[1]["peer_ok"], "the peer regions could not be mapped on a two-GPU box"
-    for name in ("dense", "q8", "q4", "synthetic", "dense_peer", "q4_peer"):
+    for name in ("dense", "q8", "q4", "synthetic", "dense_peer", "q4_peer", "q4_push"):
         lg0, tok0, d0 = res[0][name]
         lg1, tok1, d1 = res[1][name]
-        ref_lg, ref_tok, ref_d = res[0][name.replace("_peer", "") + "_ref"]
+        ref_lg, ref_tok, ref_d = res[0][name.replace("_peer", "").replace("_push", "") + "_ref"]
         # both ranks hold the same bits (the all-reduce gives every rank the same sum, the rest is replicated)
         assert np.array_equal(lg0, lg1) and np.array_equal(d0, d1) and tok0 == tok1, name
         # against the single-GPU model: same bf16 weights, f32 partial sums added in another order

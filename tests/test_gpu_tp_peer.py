@@ -87,11 +87,12 @@ def test_peer_reduce_argument_errors():
     ctx.close()
 
 
+@pytest.mark.parametrize("push", [False, True])
 @pytest.mark.parametrize("world,m,hidden,k_local,bits", [(2, 700, 1024, 512, 4), (4, 300, 1024, 256, 0), (2, 8, 1024, 512, 4),
                                                          (4, 40, 2048, 1024, 8), (2, 33, 192, 128, 4), (8, 520, 5120, 256, 4)])
-def test_projection_scatters_into_owners_and_reduces(world, m, hidden, k_local, bits):
-    """The fused path end to end on one GPU: every (emulated) rank's projection stores each column range from its
-    epilogue into the owner's slot, the single-launch reduction adds the slots and the residual.  The expected
+def test_projection_and_reduction_fused(world, m, hidden, k_local, bits, push):
+    """The fused path end to end on one GPU: every (emulated) rank's projection writes its slot (push: each column
+    range from the epilogue into the owner's region), the single-launch reduction adds the slots and the residual.  The expected
     partial sums come from the same projection kernels with a plain f32 output, so the comparison is bit-exact.
     Shapes reach the tcgen05 pair kernel (> 64 tokens), the streaming kernel with its in-kernel and separate
     split-K sums (<= 16 / <= 64 tokens) and the warp-level tile kernel (width not a multiple of 128)."""
@@ -104,6 +105,8 @@ def test_projection_scatters_into_owners_and_reduces(world, m, hidden, k_local, 
     for g in groups:
         g.peer_alloc(cap, hidden)
     eng.TpGroup.peer_attach_local(groups)
+    for g in groups:
+        g.peer_set_push(push)
     bufs = [g.peer_buffers() for g in groups]
     rng = np.random.default_rng(world + m + hidden + bits)
     x = H.f32_to_bf16_np(rng.standard_normal((cap, hidden)).astype(np.float32))
