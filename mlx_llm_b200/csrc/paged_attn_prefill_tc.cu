@@ -6,22 +6,27 @@
 // over for head_dim 128, where a long context makes the chunk's attention the largest item of a step.
 //
 // CTA = (128-query tile of one sequence's chunk, one q head), flash-attention over 128-key tiles:
-//   warp 8      one thread drives TMA: the Q tile once, then per key tile 16 boxes of 16 keys x 64 dims
-//               for K and 16 for V, each located through the block table (a page holds 16 keys of one
-//               kv head contiguously); boxes past the context are filled from a page of zeros
+//   warp 8      TMA: lane 0 the Q tile once; then per key tile 16 boxes of 16 keys x 64 dims for K and 16
+//               for V, a pair of boxes per lane (16 lanes), each located through the block table (a page
+//               holds 16 keys of one kv head contiguously); boxes past the context are filled from a page
+//               of zeros; three K / V stages
 //   warp 9      one thread issues tcgen05.mma: S = Q K^T (M 128 queries, N 128 keys, 8 steps of K = 16
 //               over head_dim) into one of two S buffers in TMEM, and O += P V (N = head_dim, 8 steps
-//               over the keys, V read as an MN-major operand straight from the page layout); P enters
-//               twice, as its bf16 head and its bf16 remainder, so the product keeps ~16 mantissa bits
-//   warps 0-7   softmax, thread = (query row = TMEM lane, half of the key tile): two passes over its 64
-//               scores (maximum, exchanged with the row's other thread through shared memory; then exp2, row
-//               sum, P written to shared memory in the K-major UMMA layout).
+//               over the keys, V read as an MN-major operand straight from the page layout) with P taken
+//               from TMEM as the A operand; P enters twice, as its bf16 head and its bf16 remainder, so the
+//               product keeps ~16 mantissa bits
+//   warps 0-7   softmax, thread = (query row = TMEM lane, half of the key tile): reads its 64 scores once,
+//               agrees on the row maximum with the row's other thread through shared memory, then exp2, row
+//               sum, and P written back with tcgen05.st OVER the scores it came from: the thread's 64 f32
+//               columns become 32 columns of bf16 pairs (head) + 32 columns (remainder).
 //               The running maximum is raised only when a tile exceeds it by more than 2^8 ("lazy
 //               rescale"): P stays within bf16/f32 range, the final division by the row sum makes the
 //               result independent of the reference point, and the O accumulator in TMEM is touched
-//               (tcgen05.ld / st) only on those rare tiles.
-// S(j+1) is issued before the softmax of tile j has finished, so the tensor pipe always has the next
-// scores or the previous P V to work on.  Every mbarrier wait is bounded.
+//               (tcgen05.ld / st, after the previous P V has completed) only on those rare tiles.
+// The tensor pipe executes one thread's MMAs in issue order, which is all the ordering the S/P buffers need:
+// S(j+2) is issued after P(j) V(j) and so overwrites buffer j & 1 only once P(j) has been consumed, while the
+// softmax of tile j+1 runs on the other buffer.  No P tile in shared memory: the room goes to a third K/V
+// stage.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -33,8 +38,9 @@ constexpr int QT = 128, KT = 128, HD = 128;
 constexpr int kSoftmaxWarps = 8, kTmaWarp = 8, kMmaWarp = 9, kThreads = 320;
 constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 64 bf16: one 128B-swizzled block
 constexpr int TILE_BYTES = 2 * HALF_BYTES;       // 128 x 128 bf16
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + 2 * TILE_BYTES, OFF_PH = OFF_V + 2 * TILE_BYTES, OFF_PL = OFF_PH + TILE_BYTES;
-constexpr int OFF_BAR = OFF_PL + TILE_BYTES;     // 224 KB of operands, then 256 B of barriers
+constexpr int NS = 3;                            // K / V stages
+constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + NS * TILE_BYTES;
+constexpr int OFF_BAR = OFF_V + NS * TILE_BYTES; // 224 KB of operands, then 256 B of barriers
 constexpr int OFF_X = OFF_BAR + 256;             // row-maximum / row-sum exchange between the two softmax groups
 constexpr int SMEM_BYTES = OFF_X + 2048;         // dynamic shared memory must start 1024-byte aligned (checked)
 constexpr uint32_t kSpinLimit = 64;
@@ -69,7 +75,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
         if (now - start > 4000000000ll) return false;
     }
 }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t mbar) {
@@ -81,6 +86,15 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
         "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D += A B with A (128 rows x 16 bf16 = 8 columns of bf16 pairs per lane) read from tensor memory
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -111,9 +125,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(map), "r"(x), "r"(y), "r"(mbar)
         : "memory");
 }
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 // K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart (SBO), descriptor version 1.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
@@ -131,6 +142,7 @@ struct TcPrefillExtra {
     int* err;
     int oob_row;  // marks a 16-key box past the context: it is filled from a page of zeros
     int q_box;    // rows per Q box: 128, or the largest power of two that the q tensor's row count allows
+    int page_shift;  // log2 of the page size in keys
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -149,15 +161,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t bar = base + OFF_BAR;
     const uint32_t q_full = bar;
     auto k_full = [&](int s) { return bar + 8u * (1 + s); };
-    auto k_empty = [&](int s) { return bar + 8u * (3 + s); };
-    auto v_full = [&](int s) { return bar + 8u * (5 + s); };
-    auto v_empty = [&](int s) { return bar + 8u * (7 + s); };
-    auto s_ready = [&](int s) { return bar + 8u * (9 + s); };
-    auto s_free = [&](int s) { return bar + 8u * (11 + s); };
-    const uint32_t p_ready = bar + 8u * 13, pv_done = bar + 8u * 14;
-    auto x_ready = [&](int s) { return bar + 8u * (15 + s); };  // both softmax groups have published their maxima
-    const uint32_t l_ready = bar + 8u * 17;
-    const uint32_t slot_addr = bar + 8u * 18;
+    auto k_empty = [&](int s) { return bar + 8u * (4 + s); };
+    auto v_full = [&](int s) { return bar + 8u * (7 + s); };
+    auto v_empty = [&](int s) { return bar + 8u * (10 + s); };
+    auto s_ready = [&](int s) { return bar + 8u * (13 + s); };
+    auto p_ready = [&](int s) { return bar + 8u * (15 + s); };  // all softmax warps have written P over S buffer s
+    auto x_ready = [&](int s) { return bar + 8u * (17 + s); };  // both softmax groups have published their maxima
+    // P V of tile j completes a phase of pv_done(j & 1).  Two barriers, because a softmax warp looks at them only
+    // now and then: when it waits for tile t, P V of t - 2 is known to be complete (S(t) could not exist otherwise)
+    // and P V of t + 2 cannot have been issued, so on barrier t & 1 the awaited phase is the current or the last one.
+    auto pv_done = [&](int s) { return bar + 8u * (19 + s); };
+    const uint32_t l_ready = bar + 8u * 21;
+    const uint32_t slot_addr = bar + 8u * 22;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -172,18 +187,20 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < NS; s++) {
             mbar_init(k_full(s), 1);
             mbar_init(k_empty(s), 1);
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
+        }
+        for (int s = 0; s < 2; s++) {
             mbar_init(s_ready(s), 1);
-            mbar_init(s_free(s), kSoftmaxWarps);
+            mbar_init(p_ready(s), kSoftmaxWarps);
             mbar_init(x_ready(s), kSoftmaxWarps);
         }
         mbar_init(l_ready, kSoftmaxWarps);
-        mbar_init(p_ready, kSoftmaxWarps);
-        mbar_init(pv_done, 1);
+        mbar_init(pv_done(0), 1);
+        mbar_init(pv_done(1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == kMmaWarp) {
@@ -198,8 +215,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool alive = true;
 
     if (warp == kTmaWarp) {
+        // Lane 0 loads the Q tile.  Then sixteen lanes share each key tile: lane s < 8 fetches the s-th 16-key box pair
+        // of K, lane 8 + s the same of V, each looking up its own page one tile ahead -- a single thread doing all 32
+        // boxes and their address arithmetic was the slowest actor of the whole CTA.
+        const int32_t* bt = p.block_tables + (size_t)p.seq_slot[b] * p.max_blocks;
         if (lane == 0) {
-            const int32_t* bt = p.block_tables + (size_t)p.seq_slot[b] * p.max_blocks;
             // the Q tile in as few boxes as the q tensor's height allows (a box is never taller than the tensor and
             // never starts outside it; rows of the tile that stay unwritten belong to queries whose results are dropped)
             const int q_boxes = (rows + ex.q_box - 1) / ex.q_box;
@@ -209,110 +229,114 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tma_load_2d(base + OFF_Q + qb * q_box_bytes, &map_q, head * HD, tok0 + q_start + qb * ex.q_box, q_full);
                 tma_load_2d(base + OFF_Q + HALF_BYTES + qb * q_box_bytes, &map_q, head * HD + 64, tok0 + q_start + qb * ex.q_box, q_full);
             }
-            // page of each of the 8 sub-tiles (16 keys) of a key tile; the index is clamped to the block-table row so
-            // the eight loads are unconditional and in flight together, one tile ahead of their use
-            auto load_pages = [&](int j, int (&pg)[8]) {
-#pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const int blk = (j * KT + s * 16) / page_size;
-                    pg[s] = __ldg(bt + (blk < p.max_blocks ? blk : p.max_blocks - 1));
-                }
+        }
+        if (lane < 16) {
+            const int sub = lane & 7;
+            const bool is_v = lane >= 8;
+            const unsigned grp = is_v ? 0xff00u : 0x00ffu;
+            const CUtensorMap* map_kv = is_v ? &map_v : &map_k;
+            const uint32_t dst0 = base + (uint32_t)(is_v ? OFF_V : OFF_K) + (uint32_t)sub * 2048u;
+            // page of this lane's box; the index is clamped to the block-table row so the load is unconditional
+            auto page_of = [&](int j) {
+                const int blk = (j * KT + sub * 16) >> ex.page_shift;
+                return __ldg(bt + (blk < p.max_blocks ? blk : p.max_blocks - 1));
             };
-            int pg[8], pg_next[8];
-            load_pages(0, pg);
-            for (int j = 0; j < n_tiles && alive; j++) {
-                const int st = j & 1;
-                const uint32_t par = (uint32_t)(j >> 1) & 1u;
-                if (j + 1 < n_tiles) load_pages(j + 1, pg_next);
-                // rows of the sub-tiles in the pool's (page, kv head, slot) order; self-checks: never past the
-                // block-table row, never outside the pool
-                int row[8];
-#pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const int key0 = j * KT + s * 16;
-                    row[s] = ex.oob_row;
-                    if (key0 < ctx) {
-                        const long rr = ((long)pg[s] * p.hkv + kvh) * page_size + key0 % page_size;
-                        if (key0 / page_size >= p.max_blocks)
-                            atomicExch(ex.err, 5);
-                        else if (rr < 0 || rr + 16 > p.pool_rows)
-                            atomicExch(ex.err, 6);
-                        else
-                            row[s] = (int)rr;
-                    }
+            int pg = page_of(0);
+            int st = 0;
+            uint32_t par = 0;  // stage of tile j and the parity of its use of that stage
+            for (int j = 0; j < n_tiles; j++) {
+                const int pg_next = j + 1 < n_tiles ? page_of(j + 1) : 0;
+                // row of the box in the pool's (page, kv head, slot) order; self-checks: never past the block-table
+                // row, never outside the pool; a box past the context is filled from a page of zeros
+                const int key0 = j * KT + sub * 16;
+                int row = ex.oob_row;
+                if (key0 < ctx) {
+                    const long rr = (((long)pg * p.hkv + kvh) << ex.page_shift) + (key0 & (page_size - 1));
+                    if ((key0 >> ex.page_shift) >= p.max_blocks)
+                        atomicExch(ex.err, 5);
+                    else if (rr < 0 || rr + 16 > p.pool_rows)
+                        atomicExch(ex.err, 6);
+                    else
+                        row = (int)rr;
                 }
-#pragma unroll
-                for (int s = 0; s < 8; s++) pg[s] = pg_next[s];
-                if (!mbar_wait(k_empty(st), par ^ 1u)) {
+                pg = pg_next;
+                const uint32_t full = is_v ? v_full(st) : k_full(st);
+                // the verdict is taken by the eight lanes of the tile together, so none is left behind at the __syncwarp
+                if (!__all_sync(grp, mbar_wait(is_v ? v_empty(st) : k_empty(st), par ^ 1u))) {
                     alive = false;
                     break;
                 }
-                mbar_expect_tx(k_full(st), TILE_BYTES);
-                const uint32_t kdst = base + OFF_K + st * TILE_BYTES;
-#pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const bool past = row[s] == ex.oob_row;
-                    tma_load_2d(kdst + s * 2048, past ? &map_zero : &map_k, 0, past ? 0 : row[s], k_full(st));
-                    tma_load_2d(kdst + HALF_BYTES + s * 2048, past ? &map_zero : &map_k, 64, past ? 0 : row[s], k_full(st));
-                }
-                if (!mbar_wait(v_empty(st), par ^ 1u)) {
-                    alive = false;
-                    break;
-                }
-                mbar_expect_tx(v_full(st), TILE_BYTES);
-                const uint32_t vdst = base + OFF_V + st * TILE_BYTES;
-#pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const bool past = row[s] == ex.oob_row;
-                    tma_load_2d(vdst + s * 2048, past ? &map_zero : &map_v, 0, past ? 0 : row[s], v_full(st));
-                    tma_load_2d(vdst + HALF_BYTES + s * 2048, past ? &map_zero : &map_v, 64, past ? 0 : row[s], v_full(st));
-                }
+                if (sub == 0) mbar_expect_tx(full, TILE_BYTES);
+                __syncwarp(grp);
+                const bool past = row == ex.oob_row;
+                const CUtensorMap* m = past ? &map_zero : map_kv;
+                const uint32_t dst = dst0 + (uint32_t)st * TILE_BYTES;
+                tma_load_2d(dst, m, 0, past ? 0 : row, full);
+                tma_load_2d(dst + HALF_BYTES, m, 64, past ? 0 : row, full);
+                if (++st == NS) st = 0, par ^= 1u;
             }
-            if (!alive) atomicExch(ex.err, 2);
+            if (!alive && sub == 0) atomicExch(ex.err, 2);
         }
         __syncwarp();
     } else if (warp == kMmaWarp) {
         if (lane == 0) {
-            auto issue_qk = [&](int j) {  // S[j & 1] = Q K_j^T
-                const int st = j & 1;
-                const uint32_t sQ = base + OFF_Q, sK = base + OFF_K + st * TILE_BYTES;
+            // Descriptors are linear in the address (14 bits of address >> 4, no carry inside 227 KB), so the loop
+            // adds offsets instead of rebuilding them: this thread's instruction count per tile sets how soon the next
+            // MMAs are queued.
+            uint64_t dq[HD / 16];
 #pragma unroll
-                for (int k = 0; k < HD / 16; k++) {
-                    const uint32_t off = (uint32_t)(k >> 2) * HALF_BYTES + (uint32_t)(k & 3) * 32;
-                    tc_mma(tmem_base + (uint32_t)st * 128u, desc_kmajor(sQ + off), desc_kmajor(sK + off), kIdescQK, k > 0 ? 1u : 0u);
-                }
-                tc_commit(s_ready(st));
-                tc_commit(k_empty(st));
+            for (int k = 0; k < HD / 16; k++) dq[k] = desc_kmajor(base + OFF_Q + (uint32_t)(k >> 2) * HALF_BYTES + (uint32_t)(k & 3) * 32);
+            const uint64_t dk0 = desc_kmajor(base + OFF_K), dv0 = desc_mnmajor(base + OFF_V);
+            // S[j & 1] = Q K_j^T; `kst` is the K stage of tile j
+            auto issue_qk = [&](int j, int kst) {
+                const uint64_t dk = dk0 + (uint64_t)((uint32_t)kst * (TILE_BYTES >> 4));
+                const uint32_t ts = tmem_base + (uint32_t)(j & 1) * 128u;
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++)
+                    tc_mma(ts, dq[k], dk + (uint64_t)((uint32_t)(k >> 2) * (HALF_BYTES >> 4) + (uint32_t)(k & 3) * 2), kIdescQK, k > 0 ? 1u : 0u);
+                tc_commit(s_ready(j & 1));
+                tc_commit(k_empty(kst));
             };
             alive = mbar_wait(q_full, 0) && mbar_wait(k_full(0), 0);
             if (alive) {
                 tc_fence_after();
-                issue_qk(0);
+                issue_qk(0, 0);
             }
-            for (int j = 0; j < n_tiles && alive; j++) {
-                if (j + 1 < n_tiles) {
-                    const int st = (j + 1) & 1;
-                    alive = mbar_wait(k_full(st), (uint32_t)((j + 1) >> 1) & 1u);
-                    // the softmax of tile j-1 has read the S buffer that tile j+1 is about to overwrite
-                    if (alive && j >= 1) alive = mbar_wait(s_free(st), (uint32_t)((j - 1) >> 1) & 1u);
-                    if (!alive) break;
+            if (alive && n_tiles > 1) {
+                alive = mbar_wait(k_full(1), 0);
+                if (alive) {
                     tc_fence_after();
-                    issue_qk(j + 1);
+                    issue_qk(1, 1);
                 }
-                const int st = j & 1;
-                alive = mbar_wait(v_full(st), (uint32_t)(j >> 1) & 1u) && mbar_wait(p_ready, (uint32_t)j & 1u);
+            }
+            int vst = 0, kst = 2 % NS;  // V stage of tile j, K stage of tile j + 2
+            uint32_t vpar = 0, kpar = (2 / NS) & 1u;
+            for (int j = 0; j < n_tiles && alive; j++) {
+                const int sb = j & 1;
+                alive = mbar_wait(v_full(vst), vpar) && mbar_wait(p_ready(sb), (uint32_t)(j >> 1) & 1u);
                 if (!alive) break;
                 tc_fence_after();
-                const uint32_t sV = base + OFF_V + st * TILE_BYTES;
+                const uint64_t dvs = dv0 + (uint64_t)((uint32_t)vst * (TILE_BYTES >> 4));
+                const uint32_t tP = tmem_base + (uint32_t)sb * 128u;
 #pragma unroll
                 for (int k = 0; k < KT / 16; k++) {  // O += P_hi V + P_lo V, 16 keys per step
-                    const uint32_t poff = (uint32_t)(k >> 2) * HALF_BYTES + (uint32_t)(k & 3) * 32;
-                    const uint64_t dv = desc_mnmajor(sV + (uint32_t)k * 2048u);
-                    tc_mma(tmem_o, desc_kmajor(base + OFF_PH + poff), dv, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
-                    tc_mma(tmem_o, desc_kmajor(base + OFF_PL + poff), dv, kIdescPV, 1u);
+                    // keys 0-63 of the tile: head in columns 0-31 of the buffer, remainder in 32-63; keys 64-127: 64-95, 96-127
+                    const uint32_t ta = tP + (uint32_t)(k >> 2) * 64u + (uint32_t)(k & 3) * 8u;
+                    const uint64_t dv = dvs + (uint64_t)((uint32_t)k * (2048u >> 4));
+                    tc_mma_ts(tmem_o, ta, dv, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem_o, ta + 32u, dv, kIdescPV, 1u);
                 }
-                tc_commit(pv_done);
-                tc_commit(v_empty(st));
+                tc_commit(pv_done(sb));
+                tc_commit(v_empty(vst));
+                if (++vst == NS) vst = 0, vpar ^= 1u;
+                if (j + 2 < n_tiles) {
+                    // S(j+2) goes over P(j): issued after the MMAs above, which the tensor pipe completes first
+                    alive = mbar_wait(k_full(kst), kpar);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_qk(j + 2, kst);
+                    if (++kst == NS) kst = 0, kpar ^= 1u;
+                }
             }
             if (!alive) atomicExch(ex.err, 3);
         }
@@ -327,8 +351,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         // last key this row may see; rows past the chunk see the whole context (their result is dropped)
         const int kvis = row_ok ? min(ctx_before + q_start + r, ctx - 1) : ctx - 1;
         float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's half of the row sum
-        const uint32_t sw = (uint32_t)(r & 7);
-        const uint32_t p_row = (uint32_t)r * 128u;
         volatile float* xb = reinterpret_cast<volatile float*>(smem_raw + OFF_X);  // [2 tiles in flight][2 groups][128 rows]
         for (int j = 0; j < n_tiles && alive; j++) {
             const int st = j & 1;
@@ -340,18 +362,19 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             const int key_base = j * KT + wg * 64;
             const bool need_mask = key_base + 63 > kvis;
-            // pass 1: maximum of this half's visible scores (log2 domain), then of the whole row
+            // this thread's 64 scores (log2 domain, masked), their maximum, then the maximum of the whole row
+            uint32_t v0[32], v1[32];
+            tc_ld32(s_addr, v0);
+            tc_ld32(s_addr + 32u, v1);
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 2; c++) {
-                uint32_t v[32];
-                tc_ld32(s_addr + (uint32_t)c * 32u, v);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float t = __uint_as_float(v[i]) * p.scale_log2;
-                    if (need_mask && key_base + c * 32 + i > kvis) t = -INFINITY;
-                    mx = fmaxf(mx, t);
-                }
+            for (int i = 0; i < 32; i++) {
+                float t0 = __uint_as_float(v0[i]) * p.scale_log2, t1 = __uint_as_float(v1[i]) * p.scale_log2;
+                if (need_mask && key_base + i > kvis) t0 = -INFINITY;
+                if (need_mask && key_base + 32 + i > kvis) t1 = -INFINITY;
+                v0[i] = __float_as_uint(t0);
+                v1[i] = __float_as_uint(t1);
+                mx = fmaxf(mx, fmaxf(t0, t1));
             }
             xb[(st * 2 + wg) * 128 + r] = mx;
             __syncwarp();
@@ -371,13 +394,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 m_run = mx;
                 rescale = true;
             }
-            // P and O belong to the previous tile's P V until it has completed
-            if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(j - 1) & 1u))) {
-                alive = false;
-                break;
-            }
-            tc_fence_after();
             if (__any_sync(0xffffffffu, rescale)) {  // this group rescales its half of the head dimension
+                // O belongs to the previous tile's P V until it has completed (P V of this tile cannot have been
+                // issued yet: it waits for this warp's arrival below)
+                if (!__all_sync(0xffffffffu, mbar_wait(pv_done((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u))) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < 2; c++) {
                     const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)wg * 64u + (uint32_t)c * 32u;
@@ -389,44 +413,26 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             l_run *= alpha;
-            // pass 2: P = exp2(s - m), row sum, bf16 head + remainder into the K-major operand layout
-#pragma unroll 1
-            for (int c = 0; c < 2; c++) {
-                uint32_t v[32];
-                tc_ld32(s_addr + (uint32_t)c * 32u, v);
+            // P = exp2(s - m), row sum; bf16 head and remainder as pairs of consecutive keys, over the scores' own columns
+            uint32_t hi[32], lo[32];
 #pragma unroll
-                for (int g = 0; g < 4; g++) {  // 8 keys = one 16-byte chunk
-                    uint32_t hi[4], lo[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        float pv[2];
-#pragma unroll
-                        for (int h = 0; h < 2; h++) {
-                            const int i = g * 8 + e * 2 + h;
-                            float t = __uint_as_float(v[i]) * p.scale_log2;
-                            if (need_mask && key_base + c * 32 + i > kvis) t = -INFINITY;
-                            pv[h] = fast_exp2(t - m_run);
-                            l_run += pv[h];
-                        }
-                        hi[e] = pack_bf2(pv[0], pv[1]);
-                        lo[e] = pack_bf2(pv[0] - bflo(hi[e]), pv[1] - bfhi(hi[e]));
-                    }
-                    // 16 chunks of 8 keys per row: this group's 8 chunks form one 128-byte row of its key half
-                    const uint32_t off = (uint32_t)wg * HALF_BYTES + p_row + ((((uint32_t)(c * 4 + g)) ^ sw) << 4);
-                    sts128(base + OFF_PH + off, hi[0], hi[1], hi[2], hi[3]);
-                    sts128(base + OFF_PL + off, lo[0], lo[1], lo[2], lo[3]);
-                }
+            for (int i = 0; i < 16; i++) {
+                const float a0 = fast_exp2(__uint_as_float(v0[2 * i]) - m_run), a1 = fast_exp2(__uint_as_float(v0[2 * i + 1]) - m_run);
+                const float b0 = fast_exp2(__uint_as_float(v1[2 * i]) - m_run), b1 = fast_exp2(__uint_as_float(v1[2 * i + 1]) - m_run);
+                l_run += (a0 + a1) + (b0 + b1);
+                hi[i] = pack_bf2(a0, a1);
+                lo[i] = pack_bf2(a0 - bflo(hi[i]), a1 - bfhi(hi[i]));
+                hi[16 + i] = pack_bf2(b0, b1);
+                lo[16 + i] = pack_bf2(b0 - bflo(hi[16 + i]), b1 - bfhi(hi[16 + i]));
             }
-            fence_proxy_async();
+            tc_st32(s_addr, hi);
+            tc_st32(s_addr + 32u, lo);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_free(st));
-                mbar_arrive(p_ready);
-            }
+            if (lane == 0) mbar_arrive(p_ready(st));
         }
         // ---------------- output: O / l, each group its half of the head dimension ----------------
-        if (alive && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u))) alive = false;
+        if (alive && !__all_sync(0xffffffffu, mbar_wait(pv_done((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u))) alive = false;
         // the row sum is the two halves' sums (slot of the tile parity that is not in use any more)
         if (alive) {
             const int slot = n_tiles & 1;
@@ -518,7 +524,8 @@ int32_t get_map(b2_ctx* ctx, const void* ptr, uint64_t rows, uint64_t cols, uint
 }  // namespace
 
 bool b2_prefill_attn_tc_eligible(const PrefillAttnParams& p, int head_dim) {
-    return head_dim == 128 && p.pool_rows > 0 && p.q_rows > 0 && ((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.k_pool & 15) == 0 &&
+    // pages of 16, 32, 64 ... keys: the loader shifts instead of dividing
+    return head_dim == 128 && p.page_tiles > 0 && (p.page_tiles & (p.page_tiles - 1)) == 0 && p.pool_rows > 0 && p.q_rows > 0 && ((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.k_pool & 15) == 0 &&
            ((uintptr_t)p.v_pool & 15) == 0;
 }
 
@@ -545,7 +552,9 @@ int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int g
     B2_CHECK(get_map(ctx, p.q, (uint64_t)p.q_rows, (uint64_t)p.hq * HD, (uint64_t)p.hq * HD, (uint32_t)q_box, &mq));
     B2_CHECK(get_map(ctx, p.k_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mk));
     B2_CHECK(get_map(ctx, p.v_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mv));
-    TcPrefillExtra ex{ctx->dev_err, -1, q_box};
+    int page_shift = 4;
+    while ((16 << (page_shift - 4)) < p.page_tiles * 16) page_shift++;
+    TcPrefillExtra ex{ctx->dev_err, -1, q_box, page_shift};
     dim3 grid(grid_work, p.hq);
     paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv, mz);
     B2_LAUNCHED(ctx);
