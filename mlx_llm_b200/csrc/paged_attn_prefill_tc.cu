@@ -109,6 +109,26 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32_nowait(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+        "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+        "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -125,14 +145,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(map), "r"(x), "r"(y), "r"(mbar)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(mbar)
+        : "memory");
+}
 // K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart (SBO), descriptor version 1.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 // MN-major operand, 128-byte swizzle: 64 contiguous MN elements per 128-byte row, one row per K index,
-// 8-row groups 1024 B apart (SBO), the next 64 MN elements 16 KB further (LBO).
+// 8-row groups 1024 B apart (SBO), the next 64 MN elements 2 KB further (LBO): a V box holds 16 keys as
+// [head_dim half][key][64 dims], and every 16-key MMA step starts its own descriptor at its own box.
+constexpr int V_BOX_BYTES = 4096;
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)(HALF_BYTES >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)((V_BOX_BYTES / 2) >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 // f32 accumulate, bf16 x bf16, M = 128, N = 128; bit 16 set = B is MN-major
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -148,7 +176,7 @@ struct TcPrefillExtra {
 __global__ void __launch_bounds__(kThreads, 1)
     paged_attn_prefill_tc_kernel(const PrefillAttnParams p, const TcPrefillExtra ex, const __grid_constant__ CUtensorMap map_q,
                                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                                 const __grid_constant__ CUtensorMap map_zero) {
+                                 const __grid_constant__ CUtensorMap map_zero, const __grid_constant__ CUtensorMap map_zero_v) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int w = blockIdx.x;
     if (w >= *p.n_work) return;
@@ -235,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const bool is_v = lane >= 8;
             const unsigned grp = is_v ? 0xff00u : 0x00ffu;
             const CUtensorMap* map_kv = is_v ? &map_v : &map_k;
-            const uint32_t dst0 = base + (uint32_t)(is_v ? OFF_V : OFF_K) + (uint32_t)sub * 2048u;
+            const uint32_t dst0 = base + (is_v ? (uint32_t)OFF_V + (uint32_t)sub * V_BOX_BYTES : (uint32_t)OFF_K + (uint32_t)sub * 2048u);
             // page of this lane's box; the index is clamped to the block-table row so the load is unconditional
             auto page_of = [&](int j) {
                 const int blk = (j * KT + sub * 16) >> ex.page_shift;
@@ -269,10 +297,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (sub == 0) mbar_expect_tx(full, TILE_BYTES);
                 __syncwarp(grp);
                 const bool past = row == ex.oob_row;
-                const CUtensorMap* m = past ? &map_zero : map_kv;
                 const uint32_t dst = dst0 + (uint32_t)st * TILE_BYTES;
-                tma_load_2d(dst, m, 0, past ? 0 : row, full);
-                tma_load_2d(dst + HALF_BYTES, m, 64, past ? 0 : row, full);
+                if (is_v) {  // both head_dim halves of the 16 keys in one box
+                    tma_load_3d(dst, past ? &map_zero_v : map_kv, 0, past ? 0 : row, 0, full);
+                } else {
+                    const CUtensorMap* m = past ? &map_zero : map_kv;
+                    tma_load_2d(dst, m, 0, past ? 0 : row, full);
+                    tma_load_2d(dst + HALF_BYTES, m, 64, past ? 0 : row, full);
+                }
                 if (++st == NS) st = 0, par ^= 1u;
             }
             if (!alive && sub == 0) atomicExch(ex.err, 2);
@@ -322,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int k = 0; k < KT / 16; k++) {  // O += P_hi V + P_lo V, 16 keys per step
                     // keys 0-63 of the tile: head in columns 0-31 of the buffer, remainder in 32-63; keys 64-127: 64-95, 96-127
                     const uint32_t ta = tP + (uint32_t)(k >> 2) * 64u + (uint32_t)(k & 3) * 8u;
-                    const uint64_t dv = dvs + (uint64_t)((uint32_t)k * (2048u >> 4));
+                    const uint64_t dv = dvs + (uint64_t)((uint32_t)k * (V_BOX_BYTES >> 4));
                     tc_mma_ts(tmem_o, ta, dv, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
                     tc_mma_ts(tmem_o, ta + 32u, dv, kIdescPV, 1u);
                 }
@@ -364,8 +396,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             const bool need_mask = key_base + 63 > kvis;
             // this thread's 64 scores (log2 domain, masked), their maximum, then the maximum of the whole row
             uint32_t v0[32], v1[32];
-            tc_ld32(s_addr, v0);
-            tc_ld32(s_addr + 32u, v1);
+            tc_ld32_nowait(s_addr, v0);
+            tc_ld32_nowait(s_addr + 32u, v1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             float mx = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 32; i++) {
@@ -413,20 +446,27 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             l_run *= alpha;
-            // P = exp2(s - m), row sum; bf16 head and remainder as pairs of consecutive keys, over the scores' own columns
+            // P = exp2(s - m), row sum; bf16 head and remainder as pairs of consecutive keys, over the scores' own
+            // columns.  The head is the upper 16 bits of the f32 (truncated, not rounded: the remainder carries what is
+            // cut off, and truncating the remainder leaves a relative error below 2^-15), so the split costs integer
+            // and add instructions only -- conversions share the exp2 unit's narrow issue rate.
             uint32_t hi[32], lo[32];
 #pragma unroll
             for (int i = 0; i < 16; i++) {
                 const float a0 = fast_exp2(__uint_as_float(v0[2 * i]) - m_run), a1 = fast_exp2(__uint_as_float(v0[2 * i + 1]) - m_run);
                 const float b0 = fast_exp2(__uint_as_float(v1[2 * i]) - m_run), b1 = fast_exp2(__uint_as_float(v1[2 * i + 1]) - m_run);
                 l_run += (a0 + a1) + (b0 + b1);
-                hi[i] = pack_bf2(a0, a1);
-                lo[i] = pack_bf2(a0 - bflo(hi[i]), a1 - bfhi(hi[i]));
-                hi[16 + i] = pack_bf2(b0, b1);
-                lo[16 + i] = pack_bf2(b0 - bflo(hi[16 + i]), b1 - bfhi(hi[16 + i]));
+                const uint32_t ua0 = __float_as_uint(a0), ua1 = __float_as_uint(a1), ub0 = __float_as_uint(b0), ub1 = __float_as_uint(b1);
+                hi[i] = __byte_perm(ua0, ua1, 0x7632);
+                hi[16 + i] = __byte_perm(ub0, ub1, 0x7632);
+                const float ra0 = a0 - __uint_as_float(ua0 & 0xffff0000u), ra1 = a1 - __uint_as_float(ua1 & 0xffff0000u);
+                const float rb0 = b0 - __uint_as_float(ub0 & 0xffff0000u), rb1 = b1 - __uint_as_float(ub1 & 0xffff0000u);
+                lo[i] = __byte_perm(__float_as_uint(ra0), __float_as_uint(ra1), 0x7632);
+                lo[16 + i] = __byte_perm(__float_as_uint(rb0), __float_as_uint(rb1), 0x7632);
             }
-            tc_st32(s_addr, hi);
-            tc_st32(s_addr + 32u, lo);
+            tc_st32_nowait(s_addr, hi);
+            tc_st32_nowait(s_addr + 32u, lo);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready(st));
@@ -521,6 +561,33 @@ int32_t get_map(b2_ctx* ctx, const void* ptr, uint64_t rows, uint64_t cols, uint
     return B2_OK;
 }
 
+// V rows [rows, 128] bf16 seen as (64 dims, rows, 2 halves): one box = 16 rows with both halves, stored as
+// [half][row][64 dims] (128-byte swizzle), which is the MN-major operand layout of a 16-key MMA step.
+int32_t get_map_v(b2_ctx* ctx, const void* ptr, uint64_t rows, CUtensorMap* out) {
+    static thread_local std::vector<MapEntry> cache;
+    for (auto& e : cache)
+        if (e.ptr == ptr && e.rows == rows && e.device == ctx->device) {
+            *out = e.map;
+            return B2_OK;
+        }
+    EncodeTiledFn fn = encode_fn();
+    B2_REQUIRE(fn != nullptr, B2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    B2_REQUIRE(((uintptr_t)ptr & 15) == 0, B2_ERR_UNSUPPORTED, "tcgen05 attention: operand must be 16-byte aligned");
+    if (cache.size() >= 1024) cache.clear();
+    MapEntry e{ptr, rows, HD, HD, 16, ctx->device, {}};
+    const cuuint64_t dims[3] = {64, rows, 2};
+    const cuuint64_t strides[2] = {HD * 2, 128};
+    const cuuint32_t box[3] = {64, 16, 2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(&e.map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B2_REQUIRE(r == CUDA_SUCCESS, B2_ERR_CUDA, "cuTensorMapEncodeTiled (V, rank 3) failed with code " + std::to_string((int)r));
+    cache.push_back(e);
+    *out = e.map;
+    return B2_OK;
+}
+
 }  // namespace
 
 bool b2_prefill_attn_tc_eligible(const PrefillAttnParams& p, int head_dim) {
@@ -544,19 +611,20 @@ int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int g
         B2_CUDA(cudaMalloc(&zp, 16 * HD * 2));
         B2_CUDA(cudaMemsetAsync(zp, 0, 16 * HD * 2, ctx->stream));
     }
-    CUtensorMap mq, mk, mv, mz;
+    CUtensorMap mq, mk, mv, mz, mzv;
     B2_CHECK(get_map(ctx, zp, 16, HD, HD, 16, &mz));
+    B2_CHECK(get_map_v(ctx, zp, 16, &mzv));
     // a box is never taller than the tensor it reads
     int q_box = QT;
     while (q_box > p.q_rows) q_box >>= 1;
     B2_CHECK(get_map(ctx, p.q, (uint64_t)p.q_rows, (uint64_t)p.hq * HD, (uint64_t)p.hq * HD, (uint32_t)q_box, &mq));
     B2_CHECK(get_map(ctx, p.k_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mk));
-    B2_CHECK(get_map(ctx, p.v_pool, (uint64_t)p.pool_rows, HD, HD, 16, &mv));
+    B2_CHECK(get_map_v(ctx, p.v_pool, (uint64_t)p.pool_rows, &mv));
     int page_shift = 4;
     while ((16 << (page_shift - 4)) < p.page_tiles * 16) page_shift++;
     TcPrefillExtra ex{ctx->dev_err, -1, q_box, page_shift};
     dim3 grid(grid_work, p.hq);
-    paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv, mz);
+    paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv, mz, mzv);
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
