@@ -129,6 +129,13 @@ __device__ __forceinline__ void tc_st32_nowait(uint32_t taddr, const uint32_t (&
         "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
+__device__ __forceinline__ void tc_st16_nowait(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+        "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -399,16 +406,24 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_ld32_nowait(s_addr, v0);
             tc_ld32_nowait(s_addr + 32u, v1);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            float mx = -INFINITY;
+            // raw scores: the scale is positive, so the maximum can be taken first and scaled once, and the
+            // exponent below is one fused multiply-add per score.  Masking (diagonal tiles only) writes -inf.
+            if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                float t0 = __uint_as_float(v0[i]) * p.scale_log2, t1 = __uint_as_float(v1[i]) * p.scale_log2;
-                if (need_mask && key_base + i > kvis) t0 = -INFINITY;
-                if (need_mask && key_base + 32 + i > kvis) t1 = -INFINITY;
-                v0[i] = __float_as_uint(t0);
-                v1[i] = __float_as_uint(t1);
-                mx = fmaxf(mx, fmaxf(t0, t1));
+                for (int i = 0; i < 32; i++) {
+                    if (key_base + i > kvis) v0[i] = 0xff800000u;
+                    if (key_base + 32 + i > kvis) v1[i] = 0xff800000u;
+                }
             }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                mx0 = fmaxf(mx0, __uint_as_float(v0[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(v0[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(v1[i]));
+                mx3 = fmaxf(mx3, __uint_as_float(v1[i + 1]));
+            }
+            float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             xb[(st * 2 + wg) * 128 + r] = mx;
             __syncwarp();
             if (lane == 0) mbar_arrive(x_ready(st));  // (release: the maxima above are visible to whoever sees the phase complete)
@@ -446,26 +461,43 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             l_run *= alpha;
-            // P = exp2(s - m), row sum; bf16 head and remainder as pairs of consecutive keys, over the scores' own
-            // columns.  The head is the upper 16 bits of the f32 (truncated, not rounded: the remainder carries what is
-            // cut off, and truncating the remainder leaves a relative error below 2^-15), so the split costs integer
+            // P = exp2(scale * s - m), row sum; bf16 head and remainder as pairs of consecutive keys, over the scores'
+            // own columns.  The head is the upper 16 bits of the f32 (truncated, not rounded: the remainder carries what
+            // is cut off, and truncating the remainder leaves a relative error below 2^-15), so the split costs integer
             // and add instructions only -- conversions share the exp2 unit's narrow issue rate.
-            uint32_t hi[32], lo[32];
+            // Columns of this thread's 64: head of keys 0-31 in 0-15, of keys 32-63 in 16-31, remainders in 32-47 and
+            // 48-63 (a column holds two consecutive keys); the first half is on its way while the second is computed.
+            const float neg_m = -m_run, sc = p.scale_log2;
+            float l0 = 0.f, l1 = 0.f;
+            {
+                uint32_t hi[16], lo[16];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const float a0 = fast_exp2(__uint_as_float(v0[2 * i]) - m_run), a1 = fast_exp2(__uint_as_float(v0[2 * i + 1]) - m_run);
-                const float b0 = fast_exp2(__uint_as_float(v1[2 * i]) - m_run), b1 = fast_exp2(__uint_as_float(v1[2 * i + 1]) - m_run);
-                l_run += (a0 + a1) + (b0 + b1);
-                const uint32_t ua0 = __float_as_uint(a0), ua1 = __float_as_uint(a1), ub0 = __float_as_uint(b0), ub1 = __float_as_uint(b1);
-                hi[i] = __byte_perm(ua0, ua1, 0x7632);
-                hi[16 + i] = __byte_perm(ub0, ub1, 0x7632);
-                const float ra0 = a0 - __uint_as_float(ua0 & 0xffff0000u), ra1 = a1 - __uint_as_float(ua1 & 0xffff0000u);
-                const float rb0 = b0 - __uint_as_float(ub0 & 0xffff0000u), rb1 = b1 - __uint_as_float(ub1 & 0xffff0000u);
-                lo[i] = __byte_perm(__float_as_uint(ra0), __float_as_uint(ra1), 0x7632);
-                lo[16 + i] = __byte_perm(__float_as_uint(rb0), __float_as_uint(rb1), 0x7632);
+                for (int i = 0; i < 16; i++) {
+                    const float a0 = fast_exp2(fmaf(__uint_as_float(v0[2 * i]), sc, neg_m)), a1 = fast_exp2(fmaf(__uint_as_float(v0[2 * i + 1]), sc, neg_m));
+                    l0 += a0;
+                    l1 += a1;
+                    const uint32_t u0 = __float_as_uint(a0), u1 = __float_as_uint(a1);
+                    hi[i] = __byte_perm(u0, u1, 0x7632);
+                    lo[i] = __byte_perm(__float_as_uint(a0 - __uint_as_float(u0 & 0xffff0000u)), __float_as_uint(a1 - __uint_as_float(u1 & 0xffff0000u)), 0x7632);
+                }
+                tc_st16_nowait(s_addr, hi);
+                tc_st16_nowait(s_addr + 32u, lo);
             }
-            tc_st32_nowait(s_addr, hi);
-            tc_st32_nowait(s_addr + 32u, lo);
+            {
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float a0 = fast_exp2(fmaf(__uint_as_float(v1[2 * i]), sc, neg_m)), a1 = fast_exp2(fmaf(__uint_as_float(v1[2 * i + 1]), sc, neg_m));
+                    l0 += a0;
+                    l1 += a1;
+                    const uint32_t u0 = __float_as_uint(a0), u1 = __float_as_uint(a1);
+                    hi[i] = __byte_perm(u0, u1, 0x7632);
+                    lo[i] = __byte_perm(__float_as_uint(a0 - __uint_as_float(u0 & 0xffff0000u)), __float_as_uint(a1 - __uint_as_float(u1 & 0xffff0000u)), 0x7632);
+                }
+                tc_st16_nowait(s_addr + 16u, hi);
+                tc_st16_nowait(s_addr + 48u, lo);
+            }
+            l_run += l0 + l1;
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
