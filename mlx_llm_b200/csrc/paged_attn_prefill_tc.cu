@@ -250,9 +250,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool alive = true;
 
     if (warp == kTmaWarp) {
-        // Lane 0 loads the Q tile.  Then sixteen lanes share each key tile: lane s < 8 fetches the s-th 16-key box pair
-        // of K, lane 8 + s the same of V, each looking up its own page one tile ahead -- a single thread doing all 32
-        // boxes and their address arithmetic was the slowest actor of the whole CTA.
+        // Lane 0 loads the Q tile.  Then 24 lanes share each key tile, one copy apiece: lanes 0-15 the 16-key x 64-dim
+        // boxes of K (box s = lane % 8, head_dim half = lane / 8), lanes 16-23 the 16-key boxes of V (both halves in
+        // one rank-3 box), each looking up its own page one tile ahead.  Issuing a copy occupies its thread for ~100
+        // cycles whoever issues it; spread over lanes the copies overlap, from one thread they did not.
         const int32_t* bt = p.block_tables + (size_t)p.seq_slot[b] * p.max_blocks;
         if (lane == 0) {
             // the Q tile in as few boxes as the q tensor's height allows (a box is never taller than the tensor and
@@ -265,10 +266,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tma_load_2d(base + OFF_Q + HALF_BYTES + qb * q_box_bytes, &map_q, head * HD + 64, tok0 + q_start + qb * ex.q_box, q_full);
             }
         }
-        if (lane < 16) {
-            const int sub = lane & 7;
-            const bool is_v = lane >= 8;
-            const unsigned grp = is_v ? 0xff00u : 0x00ffu;
+        if (lane < 24) {
+            const int sub = lane & 7, khalf = (lane >> 3) & 1;
+            const bool is_v = lane >= 16;
+            const unsigned grp = is_v ? 0xff0000u : 0xffffu;
             const CUtensorMap* map_kv = is_v ? &map_v : &map_k;
             const uint32_t dst0 = base + (is_v ? (uint32_t)OFF_V + (uint32_t)sub * V_BOX_BYTES : (uint32_t)OFF_K + (uint32_t)sub * 2048u);
             // page of this lane's box; the index is clamped to the block-table row so the load is unconditional
@@ -301,20 +302,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                     alive = false;
                     break;
                 }
-                if (sub == 0) mbar_expect_tx(full, TILE_BYTES);
+                if ((lane & 15) == 0) mbar_expect_tx(full, TILE_BYTES);
                 __syncwarp(grp);
                 const bool past = row == ex.oob_row;
                 const uint32_t dst = dst0 + (uint32_t)st * TILE_BYTES;
                 if (is_v) {  // both head_dim halves of the 16 keys in one box
                     tma_load_3d(dst, past ? &map_zero_v : map_kv, 0, past ? 0 : row, 0, full);
                 } else {
-                    const CUtensorMap* m = past ? &map_zero : map_kv;
-                    tma_load_2d(dst, m, 0, past ? 0 : row, full);
-                    tma_load_2d(dst + HALF_BYTES, m, 64, past ? 0 : row, full);
+                    tma_load_2d(dst + (uint32_t)khalf * HALF_BYTES, past ? &map_zero : map_kv, khalf * 64, past ? 0 : row, full);
                 }
                 if (++st == NS) st = 0, par ^= 1u;
             }
-            if (!alive && sub == 0) atomicExch(ex.err, 2);
+            if (!alive && (lane & 15) == 0) atomicExch(ex.err, 2);
         }
         __syncwarp();
     } else if (warp == kMmaWarp) {
