@@ -399,6 +399,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             for (int j = col_grp; j * 32 < pc.cnt; j += kProducerWarps / 4) {
                 uint32_t v[32];
                 tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(j * 32), v);
+                if (pc.n1 == 0) {  // one block: the sums of the odd K steps sit 256 columns further
+                    uint32_t w[32];
+                    tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + 256u + (uint32_t)(j * 32), w);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
+                }
                 if (f < N) {
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
@@ -510,11 +516,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tc_fence_after();
+                    if (two) {
 #pragma unroll
-                    for (int k = 0; k < TK / 16; k++) {
-                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                        tc_mma_pair(tmem_base, dA + 2 * k, dB + 2 * k, id0, acc);
-                        if (two) tc_mma_pair(tmem_base + 256u, dA + 2 * k, dC + 2 * k, id1, acc);
+                        for (int k = 0; k < TK / 16; k++) {
+                            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                            tc_mma_pair(tmem_base, dA + 2 * k, dB + 2 * k, id0, acc);
+                            tc_mma_pair(tmem_base + 256u, dA + 2 * k, dC + 2 * k, id1, acc);
+                        }
+                    } else {
+                        // One block: even K steps accumulate in columns 0-255, odd ones in 256-511, and the epilogue adds
+                        // the two.  An MMA into the accumulator of the one before it issues ~170 cycles after it whatever
+                        // N is; alternating accumulators brings that to ~90, as in the two-block case.
+#pragma unroll
+                        for (int k = 0; k < TK / 16; k++)
+                            tc_mma_pair(tmem_base + (uint32_t)(k & 1) * 256u, dA + 2 * k, dB + 2 * k, id0, (kb > 0 || k > 1) ? 1u : 0u);
                     }
                     tc_commit_pair(empty(st));
                     st++;
