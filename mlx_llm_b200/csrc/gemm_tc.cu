@@ -51,7 +51,8 @@ constexpr int RING_BYTES = 192 * 1024;  // 4 stages of (A + 2 units) for two-blo
 constexpr int BOX_BIG = 128, BOX_SMALL = 32;  // token rows per TMA box (one big box, or up to two small ones)
 constexpr int A_BYTES = TM * TK * 2, UNIT_BYTES = 128 * TK * 2;  // unit: 128 token rows x 64 K, one MMA instruction's B half
 constexpr int kProducerWarps = 16, kProducerThreads = kProducerWarps * 32;
-constexpr int kTmaWarp = kProducerWarps, kMmaWarp = kProducerWarps + 1, kThreads = kProducerThreads + 64;
+// warps: 16 producers, one for TMA, two MMA issuers (the second shares the slabs of one-block pieces)
+constexpr int kTmaWarp = kProducerWarps, kMmaWarp = kProducerWarps + 1, kThreads = kProducerThreads + 96;
 constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t kSpinLimit = 64;  // try_wait attempts between two looks at the clock
 
@@ -282,7 +283,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             mbar_init(full(s), kFullCount);
             mbar_init(empty(s), 1);
         }
-        mbar_init(accum_full, 1);
+        mbar_init(accum_full, 2);  // one commit from each MMA issuer
         mbar_init(accum_empty, 2 * kProducerWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -399,7 +400,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             for (int j = col_grp; j * 32 < pc.cnt; j += kProducerWarps / 4) {
                 uint32_t v[32];
                 tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(j * 32), v);
-                if (pc.n1 == 0) {  // one block: the sums of the odd K steps sit 256 columns further
+                if (pc.n1 == 0 && pc.nk > 1) {  // one block: the sums of the odd K slabs sit 256 columns further
                     uint32_t w[32];
                     tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + 256u + (uint32_t)(j * 32), w);
 #pragma unroll
@@ -483,7 +484,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
     } else {
-        // ---------------- MMA issuer (leader CTA) ----------------
+        // ---------------- MMA issuers (leader CTA) ----------------
+        // Issuing an MMA occupies its thread (~90 cycles, ~170 when it accumulates into the previous MMA's columns), and
+        // with the barrier round trips around each slab one thread cannot keep the tensor pipe fed when a slab carries
+        // only four MMAs.  So a one-block piece is shared: issuer 0 takes the even K slabs and accumulates in TMEM
+        // columns 0-255, issuer 1 the odd slabs in columns 256-511, and the epilogue adds the two.  A two-block piece
+        // (eight MMAs per slab, alternating between its two accumulators) stays with issuer 0; issuer 1 only keeps the
+        // ring's phases and gives its arrival on accum_full.
+        const int issuer = warp - kMmaWarp;
         if (leader && lane == 0) {
             uint32_t par = 0, n_piece = 0;
             bool alive = true;
@@ -493,7 +501,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const int NS = ring_stages(pc);
                 const uint32_t SB = ring_stage_bytes(pc);
                 if (n_piece > 0) {
-                    // both CTAs' epilogue warps have drained the previous accumulator
+                    // both CTAs' epilogue warps have drained the previous accumulator (this also keeps issuer 1 from
+                    // running a piece ahead and arriving twice in one phase of accum_full)
                     if (!mbar_wait(accum_empty, (n_piece - 1) & 1u)) {
                         alive = false;
                         break;
@@ -506,35 +515,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 // index and its phase are carried, not recomputed, to keep this thread's instruction count low
                 const uint64_t dA0 = umma_desc(base), dB0 = umma_desc(base + A_BYTES), dB1 = umma_desc(base + A_BYTES + UNIT_BYTES);
                 const uint64_t dstep = (uint64_t)(SB >> 4);
-                int st = 0;
-                uint32_t flip = 0;  // toggles each time the stage index wraps
-                uint64_t dA = dA0, dB = dB0, dC = dB1;
-                for (int kb = 0; kb < pc.nk; kb++) {
-                    const uint32_t ph = ((par >> st) ^ flip) & 1u;
-                    if (!mbar_wait(full(st), ph)) {
-                        alive = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    if (two) {
+                if (two) {
+                    if (issuer == 0) {
+                        int st = 0;
+                        uint32_t flip = 0;  // toggles each time the stage index wraps
+                        uint64_t dA = dA0, dB = dB0, dC = dB1;
+                        for (int kb = 0; kb < pc.nk; kb++) {
+                            const uint32_t ph = ((par >> st) ^ flip) & 1u;
+                            if (!mbar_wait(full(st), ph)) {
+                                alive = false;
+                                break;
+                            }
+                            tc_fence_after();
 #pragma unroll
-                        for (int k = 0; k < TK / 16; k++) {
-                            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                            tc_mma_pair(tmem_base, dA + 2 * k, dB + 2 * k, id0, acc);
-                            tc_mma_pair(tmem_base + 256u, dA + 2 * k, dC + 2 * k, id1, acc);
+                            for (int k = 0; k < TK / 16; k++) {
+                                const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                                tc_mma_pair(tmem_base, dA + 2 * k, dB + 2 * k, id0, acc);
+                                tc_mma_pair(tmem_base + 256u, dA + 2 * k, dC + 2 * k, id1, acc);
+                            }
+                            tc_commit_pair(empty(st));
+                            st++;
+                            dA += dstep, dB += dstep, dC += dstep;
+                            if (st == NS) st = 0, flip ^= 1u, dA = dA0, dB = dB0, dC = dB1;
                         }
-                    } else {
-                        // One block: even K steps accumulate in columns 0-255, odd ones in 256-511, and the epilogue adds
-                        // the two.  An MMA into the accumulator of the one before it issues ~170 cycles after it whatever
-                        // N is; alternating accumulators brings that to ~90, as in the two-block case.
-#pragma unroll
-                        for (int k = 0; k < TK / 16; k++)
-                            tc_mma_pair(tmem_base + (uint32_t)(k & 1) * 256u, dA + 2 * k, dB + 2 * k, id0, (kb > 0 || k > 1) ? 1u : 0u);
                     }
-                    tc_commit_pair(empty(st));
-                    st++;
-                    dA += dstep, dB += dstep, dC += dstep;
-                    if (st == NS) st = 0, flip ^= 1u, dA = dA0, dB = dB0, dC = dB1;
+                } else {
+                    // slabs issuer, issuer + 2, ...: stage (kb mod NS), phase flipped once per turn of the ring
+                    const uint32_t td = tmem_base + (uint32_t)issuer * 256u;
+                    int st = issuer % NS;
+                    uint32_t flip = 0;
+                    for (int kb = issuer; kb < pc.nk; kb += 2) {
+                        const uint32_t ph = ((par >> st) ^ flip) & 1u;
+                        if (!mbar_wait(full(st), ph)) {
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint64_t dA = dA0 + (uint64_t)st * dstep, dB = dB0 + (uint64_t)st * dstep;
+#pragma unroll
+                        for (int k = 0; k < TK / 16; k++) tc_mma_pair(td, dA + 2 * k, dB + 2 * k, id0, (kb > issuer || k > 0) ? 1u : 0u);
+                        tc_commit_pair(empty(st));
+                        st += 2;
+                        if (st >= NS) st -= NS, flip ^= 1u;
+                    }
                 }
                 par = ring_advance(par, pc.nk, NS);
                 if (alive) tc_commit_pair(accum_full);
