@@ -388,6 +388,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             // ---------------- epilogue of this piece ----------------
+            // (the residual it reads and the buffers it writes belong to earlier kernels until they have completed)
+            if (n_piece == 0) asm volatile("griddepcontrol.wait;\n" ::: "memory");
             bool ok = mbar_wait(accum_full, n_piece & 1u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -438,6 +440,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             int prev_blocks = 0;
             bool alive = true;
             const uint32_t leader_full0 = map_to_cta(full(0), 0);
+            // Launched with programmatic stream serialisation: everything up to here (barriers, TMEM, and the producers'
+            // first weight slabs, which no earlier kernel writes) may overlap the tail of the kernel before; the
+            // activations are that kernel's output.
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");
             for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
                 const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
                 blk += pc.blocks;
@@ -688,7 +694,17 @@ int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
         B2_CHECK(get_map(ctx, p.w, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, TM, &mw));
         map_w = *mw;
     }
-    gemm_tc_pair_kernel<WK, EPI><<<2 * plan.n_pairs, kThreads, SMEM_BYTES, ctx->stream>>>(p, plan, map_x, map_s, map_w);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * plan.n_pairs);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B2_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<WK, EPI>, p, plan, map_x, map_s, map_w));
     B2_LAUNCHED(ctx);
     if (best > 1) {
         const size_t total = (size_t)p.M * p.N;

@@ -26,6 +26,9 @@ __global__ void __launch_bounds__(kThreads) paged_attn_prefill_kernel(const Pref
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sQ = smem_u32(smem), sK = sQ + QT * ROWB, sV = sK + 2 * TILE_B;
 
+    // lets a dependent launch (the o_proj kernel, launched with programmatic stream serialisation) set itself up and
+    // fetch its first weights now; it still waits for this grid to complete before it reads the attention output
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int w = blockIdx.x;
     if (w >= *p.n_work) return;
     const int head = blockIdx.y, kvh = head / (p.hq / p.hkv);

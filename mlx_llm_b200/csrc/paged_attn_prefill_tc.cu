@@ -185,6 +185,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                  const __grid_constant__ CUtensorMap map_zero, const __grid_constant__ CUtensorMap map_zero_v) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // lets a dependent launch (the o_proj kernel, launched with programmatic stream serialisation) set itself up and
+    // fetch its first weights now; it still waits for this grid to complete before it reads the attention output
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int w = blockIdx.x;
     if (w >= *p.n_work) return;
     const uint32_t raw = smem_u32(smem_raw);
