@@ -104,12 +104,17 @@ __global__ void swiglu_kernel(const uint16_t* __restrict__ gu, int inter, uint16
     const uint16_t* g = gu + (size_t)row * 2 * inter;
     const uint16_t* u = g + inter;
     uint16_t* o = out + (size_t)row * inter;
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
-    if (i + 1 < inter && (inter % 2 == 0)) {
-        const uint32_t gv = *reinterpret_cast<const uint32_t*>(g + i), uv = *reinterpret_cast<const uint32_t*>(u + i);
-        *reinterpret_cast<uint32_t*>(o + i) = pack_bf2(swiglu_one(bflo(gv), bflo(uv)), swiglu_one(bfhi(gv), bfhi(uv)));
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= inter) return;
+    if (inter % 8 == 0) {  // rows and the gate | up boundary are then 16-byte aligned: eight values per thread
+        const uint4 gv = *reinterpret_cast<const uint4*>(g + i), uv = *reinterpret_cast<const uint4*>(u + i);
+        const uint32_t ga[4] = {gv.x, gv.y, gv.z, gv.w}, ua[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) r[j] = pack_bf2(swiglu_one(bflo(ga[j]), bflo(ua[j])), swiglu_one(bfhi(ga[j]), bfhi(ua[j])));
+        *reinterpret_cast<uint4*>(o + i) = make_uint4(r[0], r[1], r[2], r[3]);
     } else {
-        for (int j = i; j < inter && j < i + 2; j++) o[j] = f2bf(swiglu_one(bf2f(g[j]), bf2f(u[j])));
+        for (int j = i; j < inter && j < i + 8; j++) o[j] = f2bf(swiglu_one(bf2f(g[j]), bf2f(u[j])));
     }
 }
 __global__ void swiglu2_kernel(const uint16_t* __restrict__ g, const uint16_t* __restrict__ u, int64_t n, uint16_t* __restrict__ out) {
@@ -273,7 +278,7 @@ int32_t b2_embed_launch(b2_ctx* ctx, const uint16_t* table, const int32_t* ids, 
 }
 int32_t b2_swiglu_launch(b2_ctx* ctx, const uint16_t* gate_up, int rows, int inter, uint16_t* out) {
     if (rows <= 0) return B2_OK;
-    dim3 grid(((inter + 1) / 2 + 255) / 256, rows);
+    dim3 grid(((inter + 7) / 8 + 255) / 256, rows);
     swiglu_kernel<<<grid, 256, 0, ctx->stream>>>(gate_up, inter, out);
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
