@@ -586,6 +586,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 }
 
 // out = epilogue(sum over K ranges of partial)
+// four features per thread (N, the output / residual strides and their base addresses allow 16- and 8-byte accesses)
+template <int EPI>
+__global__ void splitk_reduce4_kernel(const GemmParams p, const float* __restrict__ partial, int splits) {
+    const size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)p.M * p.N;
+    const size_t i = q * 4;
+    if (i >= total) return;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int z = 0; z < splits; z++) {  // same additions in the same order as the one-feature kernel
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + (size_t)z * total + i));
+        a.x += v.x, a.y += v.y, a.z += v.z, a.w += v.w;
+    }
+    const int t = (int)(i / p.N), f = (int)(i % p.N);
+    if (EPI == EPI_F32) {
+        *reinterpret_cast<float4*>(gemm_f32_dst(p, t, f)) = a;
+    } else if (EPI == EPI_BF16) {
+        uint2 o;
+        o.x = pack_bf2(a.x, a.y);
+        o.y = pack_bf2(a.z, a.w);
+        *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + f) = o;
+    } else {
+        const uint2 r = *reinterpret_cast<const uint2*>(p.res + (size_t)t * p.ldres + f);
+        uint2 o;
+        o.x = pack_bf2(bflo(r.x) + rbf(a.x), bfhi(r.x) + rbf(a.y));
+        o.y = pack_bf2(bflo(r.y) + rbf(a.z), bfhi(r.y) + rbf(a.w));
+        *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + f) = o;
+    }
+}
+
 template <int EPI>
 __global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict__ partial, int splits) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -708,7 +737,12 @@ int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
     B2_LAUNCHED(ctx);
     if (best > 1) {
         const size_t total = (size_t)p.M * p.N;
-        splitk_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, plan.partial, best);
+        const bool vec4 = p.N % 4 == 0 && p.ldo % 4 == 0 && (EPI != EPI_BF16_RESADD || (p.ldres % 4 == 0 && ((uintptr_t)p.res & 7) == 0)) &&
+                          (EPI == EPI_F32 ? (((uintptr_t)p.out_f32 & 15) == 0 && p.f32_chunk % 4 == 0) : ((uintptr_t)p.out & 7) == 0);
+        if (vec4)
+            splitk_reduce4_kernel<EPI><<<(unsigned)((total / 4 + 255) / 256), 256, 0, ctx->stream>>>(p, plan.partial, best);
+        else
+            splitk_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, plan.partial, best);
         B2_LAUNCHED(ctx);
     }
     B2_CUDA(cudaGetLastError());
