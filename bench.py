@@ -91,7 +91,7 @@ class ClockSampler:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures whose
 # summaries (with the commands) are under profiles/
 NCU_TRAFFIC = dict(
-    gemm_gate_up_launch=93.5e6,
+    gemm_gate_up_launch=90.9e6,
     gemm_note="gate+up projection launch of gemm_tc_pair_kernel<4,0> (N 28672, K 4096) at ~570 tokens in the 2-layer capture; "
               "algorithmic 66.1 MB of packed weights + activations/outputs that mostly stay in L2",
     attn_decode_config1_launch=578.4e6,
