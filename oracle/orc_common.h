@@ -38,6 +38,42 @@ static inline float bf2f(uint16_t h) {
 // Round an f32 value to the nearest bf16 and return it as f32.
 static inline float rbf(float f) { return bf2f(f2bf(f)); }
 
+// ---- x @ w^T for one weight row against many activation rows ------------------------
+// Every output keeps ONE f32 accumulator that adds x[i][d]*w[d] for d = 0, 1, 2, ... (a multiply, then
+// an add: the build disables contraction), exactly the scalar loop `acc += x[d]*w[d]`.  The rows are
+// only interleaved 32 at a time so that 32 independent accumulators sit in four 8-lane vector
+// registers; no sum is split or reordered, so the result is the scalar loop's bit for bit.
+typedef float orc_v8 __attribute__((vector_size(32), aligned(4)));
+struct RowsT16 {  // activations re-laid as [block of 32 rows][d][32], zero padded
+    int m = 0, k = 0;
+    std::vector<float> t;
+    RowsT16(const float* x, int m_, int k_) : m(m_), k(k_), t((size_t)((m_ + 31) / 32) * k_ * 32, 0.f) {
+        for (int i = 0; i < m; i++)
+            for (int d = 0; d < k; d++) t[((size_t)(i / 32) * k + d) * 32 + (i % 32)] = x[(size_t)i * k + d];
+    }
+};
+static inline void dots_in_order(const RowsT16& x, const float* w, float* acc /* [m] */) {
+    for (int b = 0; b * 32 < x.m; b++) {
+        orc_v8 a0 = {0, 0, 0, 0, 0, 0, 0, 0}, a1 = a0, a2 = a0, a3 = a0;
+        const float* xb = x.t.data() + (size_t)b * x.k * 32;
+        for (int d = 0; d < x.k; d++) {
+            const float wd = w[d];
+            const orc_v8 wv = {wd, wd, wd, wd, wd, wd, wd, wd};
+            const orc_v8* xr = (const orc_v8*)(xb + (size_t)d * 32);
+            a0 += xr[0] * wv;  // a multiply, then an add, per lane (no contraction in this build)
+            a1 += xr[1] * wv;
+            a2 += xr[2] * wv;
+            a3 += xr[3] * wv;
+        }
+        float out[32];
+        std::memcpy(out, &a0, 32);
+        std::memcpy(out + 8, &a1, 32);
+        std::memcpy(out + 16, &a2, 32);
+        std::memcpy(out + 24, &a3, 32);
+        for (int i = 0; i < 32 && b * 32 + i < x.m; i++) acc[b * 32 + i] = out[i];
+    }
+}
+
 // ---- SplitMix64 (src/primitives/sampler.rs:36-61) -----------------------------------
 struct SplitMix64 {
     uint64_t s;

@@ -26,6 +26,7 @@ static void linear(const ModelCfg& c, const Mat& w, const std::vector<float>& x,
     if (unrounded) unrounded->assign((size_t)m * out, 0.f);
     int per = w.bits ? 32 / w.bits : 1;
     uint32_t mask = w.bits ? (1u << w.bits) - 1 : 0;
+    const RowsT16 xt(x.data(), m, in);
 #pragma omp parallel for schedule(dynamic, 32)
     for (int j = 0; j < out; j++) {
         std::vector<float> wf(in);
@@ -41,12 +42,11 @@ static void linear(const ModelCfg& c, const Mat& w, const std::vector<float>& x,
         } else {
             for (int d = 0; d < in; d++) wf[d] = bf2f(w.w[(size_t)j * in + d]);
         }
+        std::vector<float> acc(m);
+        dots_in_order(xt, wf.data(), acc.data());
         for (int i = 0; i < m; i++) {
-            const float* xr = x.data() + (size_t)i * in;
-            float acc = 0.f;
-            for (int d = 0; d < in; d++) acc += xr[d] * wf[d];
-            if (unrounded) (*unrounded)[(size_t)i * out + j] = acc;
-            y[(size_t)i * out + j] = R(c, acc);
+            if (unrounded) (*unrounded)[(size_t)i * out + j] = acc[i];
+            y[(size_t)i * out + j] = R(c, acc[i]);
         }
     }
 }

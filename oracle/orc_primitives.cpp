@@ -134,16 +134,16 @@ void orc_add_bf16(const uint16_t* a, const uint16_t* b, int64_t n, uint16_t* out
 void orc_linear(const uint16_t* x, const uint16_t* w, int m, int n, int k, float* out_f32, uint16_t* out_bf16) {
     std::vector<float> xf((size_t)m * k);
     for (size_t i = 0; i < xf.size(); i++) xf[i] = bf2f(x[i]);
+    const RowsT16 xt(xf.data(), m, k);
 #pragma omp parallel for schedule(static)
     for (int j = 0; j < n; j++) {
         std::vector<float> wf(k);
         for (int d = 0; d < k; d++) wf[d] = bf2f(w[(size_t)j * k + d]);
+        std::vector<float> acc(m);
+        dots_in_order(xt, wf.data(), acc.data());
         for (int i = 0; i < m; i++) {
-            const float* xr = xf.data() + (size_t)i * k;
-            float acc = 0.f;
-            for (int d = 0; d < k; d++) acc += xr[d] * wf[d];
-            if (out_f32) out_f32[(size_t)i * n + j] = acc;
-            if (out_bf16) out_bf16[(size_t)i * n + j] = f2bf(acc);
+            if (out_f32) out_f32[(size_t)i * n + j] = acc[i];
+            if (out_bf16) out_bf16[(size_t)i * n + j] = f2bf(acc[i]);
         }
     }
 }
@@ -260,6 +260,7 @@ void orc_qmm(const uint16_t* x, const uint32_t* packed, const uint16_t* scales, 
     int64_t words = k / per, groups = k / group;
     std::vector<float> xf((size_t)m * k);
     for (size_t i = 0; i < xf.size(); i++) xf[i] = bf2f(x[i]);
+    const RowsT16 xt(xf.data(), m, k);
 #pragma omp parallel for schedule(dynamic, 16)
     for (int j = 0; j < n; j++) {
         std::vector<float> wf(k);
@@ -268,12 +269,11 @@ void orc_qmm(const uint16_t* x, const uint32_t* packed, const uint16_t* scales, 
             wf[d] = rbf(std::fmaf((float)c, bf2f(scales[(int64_t)j * groups + d / group]),
                                   bf2f(biases[(int64_t)j * groups + d / group])));
         }
+        std::vector<float> acc(m);
+        dots_in_order(xt, wf.data(), acc.data());
         for (int i = 0; i < m; i++) {
-            const float* xr = xf.data() + (size_t)i * k;
-            float acc = 0.f;
-            for (int d = 0; d < k; d++) acc += xr[d] * wf[d];
-            if (out_f32) out_f32[(size_t)i * n + j] = acc;
-            if (out_bf16) out_bf16[(size_t)i * n + j] = f2bf(acc);
+            if (out_f32) out_f32[(size_t)i * n + j] = acc[i];
+            if (out_bf16) out_bf16[(size_t)i * n + j] = f2bf(acc[i]);
         }
     }
 }
