@@ -48,6 +48,13 @@ int32_t b2_ctx_sync(b2_ctx* ctx);   /* also reports B2_ERR_TIMEOUT raised by a b
 /* Projection path: 1 = tcgen05 / TMEM kernel for steps with more than 64 tokens (default), 0 = the
  * warp-level mma.sync kernel for every size (kept for comparison). */
 int32_t b2_ctx_set_tensor_path(b2_ctx* ctx, int32_t use_tcgen05);
+/* Limit, in milliseconds, of every device-side wait on ANOTHER rank (the flags of the peer-memory reduction);
+ * default about four seconds.  When a wait runs out the kernel raises the context's error word and returns,
+ * b2_ctx_sync and the engine's step return B2_ERR_TIMEOUT, and reductions launched before the error is read
+ * return at once.  The waits on on-chip barriers of the tcgen05 kernels keep a fixed limit of about two seconds.
+ * No counterpart in the reference (single device; its only failure path is cooperative cancel,
+ * src/decode/continuous.rs:138-140, :198-214). */
+int32_t b2_ctx_set_wait_limit_ms(b2_ctx* ctx, int32_t ms);
 int32_t b2_device_count(int32_t* out);
 int32_t b2_malloc(b2_ctx* ctx, size_t bytes, void** out_dev);
 int32_t b2_free(b2_ctx* ctx, void* dev);
@@ -75,7 +82,8 @@ int32_t b2_launch_count(b2_ctx* ctx, int64_t* out);
  * Decode: one query token per sequence, causal over its ctx_lens[i] cached positions (the query's
  * own K/V already appended).  GQA: q head h reads kv head h / (hq/hkv) (adjacent grouping,
  * attention.rs:300-301).  Split-K over chunks of `chunk_tokens` positions followed by a
- * log-sum-exp merge; chunk_tokens == 0 picks a size from the batch.  fp32 accumulate, bf16 I/O.
+ * log-sum-exp merge; chunk_tokens == 0 means 256.  fp32 accumulate, bf16 I/O.  A ctx_lens[i] larger than
+ * max_blocks * page_size is read as that maximum; a sequence with ctx_lens[i] == 0 gets rows of zeros.
  *   q_dev            [num_seqs, hq, head_dim]
  *   block_tables_dev [num_seqs, max_blocks] physical page per logical block
  *   ctx_lens_dev     [num_seqs]
@@ -103,7 +111,8 @@ int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host, const uin
  * exceeds 16 MiB is rejected with B2_ERR_MSG and a text that names both sizes; nothing is launched then.
  * (Llama-3-8B shapes, 16 K-token tables, chunk 512: up to 31 sequences; chunk 2048: up to 125.)
  * The first call on each device looks the array's address up and sets the kernels' shared-memory limit;
- * make that call before any stream capture begins.  All calls on one device share the array and it keeps
+ * make that call before any stream capture begins (two host threads making their first call on one device
+ * at the same time both do this set-up, with the same result).  All calls on one device share the array and it keeps
  * whatever the last call left: two calls that may run at the same time (different streams, different
  * host threads) race on it, so order them on one stream or with events. */
 int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_dev, const uint16_t* k_pool_dev, const uint16_t* v_pool_dev,
@@ -209,6 +218,13 @@ typedef struct {
     int32_t qk_norm;                  /* Qwen3 per-head q/k RMSNorm */
     int32_t quant_bits, quant_group;  /* `quantization` block of a pre-quantized snapshot, 0 if dense */
     int32_t tie_word_embeddings;
+    /* 0 (default): every tensor is cast to bf16 and every op rounds to bf16, as CausalLm::from_weights does
+     * (src/models/llama.rs:29-30, :71).  1: weights, activations, KV pages and logits stay f32 and every
+     * projection adds its products in index order (one multiply and one add per term, no fused multiply-add),
+     * so two implementations of the same arithmetic agree to the last bits; attention accumulates in f64.
+     * A plain-CUDA-core path for small dense checkpoints (no quantization, no q/k norm, no tensor parallelism,
+     * contexts up to 4096): it exists so that a tiny f32 decoder can be compared token for token. */
+    int32_t compute_f32;
 } b2_model_config;
 
 enum { B2_DTYPE_F32 = 0, B2_DTYPE_BF16 = 1, B2_DTYPE_F16 = 2, B2_DTYPE_U32 = 3, B2_DTYPE_I32 = 4 };
@@ -337,13 +353,16 @@ int32_t b2_cache_shareable_prefix_blocks(b2_cache* c, int64_t tokens, int64_t* o
 /* What KvCache::update returns (kv_cache.rs:31-33), materialised for tests: K and V of `layer`
  * as [n_kv_heads, len, head_dim] bf16 host arrays. */
 int32_t b2_cache_gather(b2_cache* c, int32_t layer, uint16_t* k_host, uint16_t* v_host);
+/* The same for a pool of an f32 model (b2_model_config::compute_f32): [n_kv_heads, len, head_dim] f32. */
+int32_t b2_cache_gather_f32(b2_cache* c, int32_t layer, float* k_host, float* v_host);
 
 /* One forward over a ragged batch: sequence i contributes n_tokens[i] ids at positions
- * offset(caches[i])..; returns last-position logits [num_seqs, vocab] bf16 on the host and advances
+ * offset(caches[i])..; returns last-position logits [num_seqs, vocab] (bf16; f32 for an f32 model) on the host and advances
  * the caches.  Covers Decode::step (src/decode/stream.rs:22-29), CausalLm::decode_logits
  * (llama.rs:351-370) and decode_logits_per_seq (llama.rs:530-558). */
 int32_t b2_model_step(b2_model* m, const int32_t* ids_host, const int32_t* n_tokens, int32_t num_seqs, b2_cache** caches,
-                      uint16_t* logits_host /* nullable */, int32_t* argmax_host /* nullable */);
+                      void* logits_host /* nullable; uint16_t (bf16) rows, float rows for an f32 model */,
+                      int32_t* argmax_host /* nullable */);
 
 /* FinishReason (src/decode/stream.rs:31-46). */
 enum { B2_FINISH_STOP_TOKEN = 0, B2_FINISH_MAX_TOKENS = 1, B2_FINISH_CANCELLED = 2, B2_FINISH_STOPPED = 3 };

@@ -47,7 +47,10 @@ struct b2_ctx {
     // tcgen05 GEMM: split-K partial sums and the device error word its bounded waits raise
     float* tc_partial = nullptr;
     size_t tc_partial_bytes = 0;
-    int* dev_err = nullptr;
+    int* dev_err = nullptr;        // raised by a bounded device-side wait that gave up (allocated with the context)
+    int* err_host = nullptr;       // pinned copy the engine step reads back with its sampled ids
+    long long wait_cycles = 8000000000LL;  // limit of a wait on another rank (b2_ctx_set_wait_limit_ms), ~4 s
+    int clock_khz = 1965000;
     int* tile_counters = nullptr;  // per row-tile arrival counters of the split-K streaming kernel (self-resetting)
     bool use_tc = true;
     // optional per-kernel-class timing with CUDA events on the launching stream

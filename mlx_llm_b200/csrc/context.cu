@@ -44,6 +44,12 @@ int32_t b2_ctx_create(int32_t device, b2_ctx** out) {
     b2_ctx* c = new b2_ctx();
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
+    if (prop.clockRate > 0) c->clock_khz = prop.clockRate;
+    c->wait_cycles = 4000ll * c->clock_khz;
+    B2_CUDA(cudaMalloc((void**)&c->dev_err, 16));
+    B2_CUDA(cudaMemset(c->dev_err, 0, 16));
+    B2_CUDA(cudaHostAlloc((void**)&c->err_host, 16, cudaHostAllocDefault));
+    c->err_host[0] = 0;
     B2_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     B2_CUDA(cudaEventCreate(&c->ev0));
     B2_CUDA(cudaEventCreate(&c->ev1));
@@ -60,6 +66,7 @@ int32_t b2_ctx_free(b2_ctx* ctx) {
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->tc_partial) cudaFree(ctx->tc_partial);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->err_host) cudaFreeHost(ctx->err_host);
     if (ctx->tile_counters) cudaFree(ctx->tile_counters);
     for (auto e : ctx->prof_ev) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev0);
@@ -81,6 +88,14 @@ int32_t b2_ctx_sync(b2_ctx* ctx) {
             return b2_fail(B2_ERR_TIMEOUT, "a bounded device-side wait ran out (tcgen05 pipeline barrier or a peer-memory reduction flag)");
         }
     }
+    return B2_OK;
+}
+
+// Limit of the device-side waits on another rank's flags (the peer-memory reduction).
+int32_t b2_ctx_set_wait_limit_ms(b2_ctx* ctx, int32_t ms) {
+    B2_REQUIRE(ctx, B2_ERR_MSG, "b2_ctx_set_wait_limit_ms: null context");
+    B2_REQUIRE(ms >= 1 && ms <= 60000, B2_ERR_MSG, "b2_ctx_set_wait_limit_ms: the limit must lie between 1 ms and 60 s");
+    ctx->wait_cycles = (long long)ms * ctx->clock_khz;
     return B2_OK;
 }
 

@@ -104,6 +104,9 @@ struct b2_model {
     std::vector<void*> allocs;
     int64_t weight_bytes = 0;
     bool quantized = false;
+    bool f32 = false;  // cfg.compute_f32: every weight pointer above then holds float, not bf16
+    float *cos_f32 = nullptr, *sin_f32 = nullptr;  // f32 RoPE tables of the f32 path
+    struct F32Work* w32 = nullptr;                 // its activations (engine_step_f32.cu)
     Workspace ws;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     // accumulated by every forward
@@ -130,7 +133,8 @@ struct b2_pool {  // BlockPool (paged_kv_cache.rs:72-160) + bounded physical pag
     int64_t max_pages = 0;
     int max_seqs = 0, max_blocks = 0;
     int layers = 0, hkv = 0, hd = 0;
-    uint16_t* kv = nullptr;        // [layers][2][pages][hkv][block][hd]
+    uint16_t* kv = nullptr;        // [layers][2][pages][hkv][block][hd], bf16 (f32 for an f32 model)
+    int esz = 2;                   // bytes per element
     size_t page_elems = 0;         // hkv*block*hd
     int32_t* block_tables = nullptr;  // device [max_seqs][max_blocks]
     std::vector<int32_t> free_pages;  // stack, back() is handed out next
@@ -140,14 +144,17 @@ struct b2_pool {  // BlockPool (paged_kv_cache.rs:72-160) + bounded physical pag
     std::vector<int32_t> free_slots;
     std::vector<int32_t> upd_slot, upd_index, upd_page;  // block-table updates not yet on the device
     int64_t live_caches = 0;
-    uint16_t* k_layer(int l) const { return kv + ((size_t)l * 2) * (size_t)max_pages * page_elems; }
-    uint16_t* v_layer(int l) const { return kv + ((size_t)l * 2 + 1) * (size_t)max_pages * page_elems; }
+    uint64_t step_stamp = 0;  // number of the last forward over this pool (duplicate-cache check)
+    size_t page_bytes() const { return page_elems * (size_t)esz; }
+    uint16_t* k_layer(int l) const { return reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(kv) + ((size_t)l * 2) * (size_t)max_pages * page_bytes()); }
+    uint16_t* v_layer(int l) const { return reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(kv) + ((size_t)l * 2 + 1) * (size_t)max_pages * page_bytes()); }
 };
 
 struct b2_cache {  // PagedKvCache (paged_kv_cache.rs:168-516)
     b2_pool* pool = nullptr;
     int slot = -1;
     int len = 0;                     // KvCache::offset
+    uint64_t step_stamp = 0;         // pool->step_stamp of the last forward this cache took part in
     std::vector<int32_t> pages;      // physical page of every started block (incl. the partial tail)
     std::vector<int64_t> block_ids;  // reference-view ids of the frozen (full) blocks
 };
@@ -159,5 +166,11 @@ struct SeqStep {
     bool want_logits;
 };
 // One forward over a ragged batch.  argmax_out[i] (per sequence that wants logits, in batch order)
-// and logits_out (bf16 rows in the same order) are host pointers, nullable.
-int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* logits_out, int32_t* argmax_out);
+// and logits_out (rows in the same order: bf16, or f32 for an f32 model) are host pointers, nullable.
+int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_out, int32_t* argmax_out);
+// The f32 path's layers (engine_step_f32.cu): from the step's ids to f32 logits + greedy ids for the n_logits sampled rows;
+// *logits_dev receives the device address of the [n_logits, vocab] f32 logits.
+struct BatchMetaOut;
+int32_t b2_forward_f32(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const int32_t* seq_slot_dev, const int32_t* ids_dev, int T, int B,
+                       int n_logits, int max_ctx, float** logits_dev);
+void b2_forward_f32_release(b2_model* m);

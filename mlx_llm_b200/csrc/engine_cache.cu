@@ -52,7 +52,15 @@ int32_t pool_alloc_page(b2_pool* p, int32_t* out) {
 void pool_unref_page(b2_pool* p, int32_t page) {
     if (--p->page_ref[page] == 0) p->free_pages.push_back(page);
 }
+// Queue table[slot][index] = page for the next step's packer.  The packer applies the queue with many threads in no
+// particular order, so the queue never holds two entries for one (slot, index): a later write (a private copy
+// replacing a shared page before any step ran, a freed row handed to a new cache) replaces the earlier one here.
 void push_update(b2_pool* p, int slot, int index, int page) {
+    for (size_t i = p->upd_slot.size(); i-- > 0;)
+        if (p->upd_slot[i] == slot && p->upd_index[i] == index) {
+            p->upd_page[i] = page;
+            return;
+        }
     p->upd_slot.push_back(slot);
     p->upd_index.push_back(index);
     p->upd_page.push_back(page);
@@ -117,7 +125,8 @@ int32_t b2_pool_new(b2_ctx* ctx, const b2_model* m, int32_t block_size, int64_t 
     p->hkv = m->hkv_l;  // pages hold this rank's KV heads only
     p->hd = m->cfg.head_dim;
     p->page_elems = (size_t)p->hkv * block_size * p->hd;
-    const size_t bytes = (size_t)p->layers * 2 * (size_t)max_pages * p->page_elems * 2;
+    p->esz = m->f32 ? 4 : 2;
+    const size_t bytes = (size_t)p->layers * 2 * (size_t)max_pages * p->page_bytes();
     cudaError_t e = cudaMalloc((void**)&p->kv, bytes);
     if (e != cudaSuccess) {
         delete p;
@@ -257,10 +266,12 @@ int32_t b2_cache_truncate(b2_cache* c, int32_t len) {
         B2_CHECK(pool_alloc_page(p, &fresh));
         const int32_t old = c->pages[keep_full];
         for (int l = 0; l < p->layers; l++) {
-            B2_CUDA(cudaMemcpyAsync(p->k_layer(l) + (size_t)fresh * p->page_elems, p->k_layer(l) + (size_t)old * p->page_elems,
-                                    p->page_elems * 2, cudaMemcpyDeviceToDevice, p->ctx->stream));
-            B2_CUDA(cudaMemcpyAsync(p->v_layer(l) + (size_t)fresh * p->page_elems, p->v_layer(l) + (size_t)old * p->page_elems,
-                                    p->page_elems * 2, cudaMemcpyDeviceToDevice, p->ctx->stream));
+            uint8_t* kl = reinterpret_cast<uint8_t*>(p->k_layer(l));
+            uint8_t* vl = reinterpret_cast<uint8_t*>(p->v_layer(l));
+            B2_CUDA(cudaMemcpyAsync(kl + (size_t)fresh * p->page_bytes(), kl + (size_t)old * p->page_bytes(), p->page_bytes(),
+                                    cudaMemcpyDeviceToDevice, p->ctx->stream));
+            B2_CUDA(cudaMemcpyAsync(vl + (size_t)fresh * p->page_bytes(), vl + (size_t)old * p->page_bytes(), p->page_bytes(),
+                                    cudaMemcpyDeviceToDevice, p->ctx->stream));
         }
         pool_unref_page(p, old);
         c->pages[keep_full] = fresh;
@@ -277,27 +288,33 @@ int32_t b2_cache_shareable_prefix_blocks(b2_cache* c, int64_t tokens, int64_t* o
     return (int32_t)n;
 }
 
-int32_t b2_cache_gather(b2_cache* c, int32_t layer, uint16_t* k_host, uint16_t* v_host) {
+static int32_t cache_gather(b2_cache* c, int32_t layer, void* k_host, void* v_host, int esz) {
     B2_REQUIRE(c && k_host && v_host, B2_ERR_MSG, "b2_cache_gather: null argument");
     b2_pool* p = c->pool;
+    B2_REQUIRE(p->esz == esz, B2_ERR_MSG, esz == 2 ? "b2_cache_gather: the pool holds f32 pages, use b2_cache_gather_f32"
+                                                  : "b2_cache_gather_f32: the pool holds bf16 pages, use b2_cache_gather");
     B2_REQUIRE(layer >= 0 && layer < p->layers, B2_ERR_MSG, "b2_cache_gather: layer out of range");
     B2_REQUIRE(c->len > 0, B2_ERR_MSG, "gather on an empty paged cache");
     const int bs = p->block_size, hd = p->hd, hkv = p->hkv;
-    std::vector<uint16_t> pk(p->page_elems), pv(p->page_elems);
+    std::vector<uint8_t> pk(p->page_bytes()), pv(p->page_bytes());
     B2_CUDA(cudaStreamSynchronize(p->ctx->stream));
+    const uint8_t* kl = reinterpret_cast<const uint8_t*>(p->k_layer(layer));
+    const uint8_t* vl = reinterpret_cast<const uint8_t*>(p->v_layer(layer));
     for (size_t b = 0; b < c->pages.size(); b++) {
         const int tokens = std::min(bs, c->len - (int)b * bs);
         if (tokens <= 0) break;
-        B2_CUDA(cudaMemcpy(pk.data(), p->k_layer(layer) + (size_t)c->pages[b] * p->page_elems, p->page_elems * 2, cudaMemcpyDeviceToHost));
-        B2_CUDA(cudaMemcpy(pv.data(), p->v_layer(layer) + (size_t)c->pages[b] * p->page_elems, p->page_elems * 2, cudaMemcpyDeviceToHost));
+        B2_CUDA(cudaMemcpy(pk.data(), kl + (size_t)c->pages[b] * p->page_bytes(), p->page_bytes(), cudaMemcpyDeviceToHost));
+        B2_CUDA(cudaMemcpy(pv.data(), vl + (size_t)c->pages[b] * p->page_bytes(), p->page_bytes(), cudaMemcpyDeviceToHost));
         for (int h = 0; h < hkv; h++)
             for (int t = 0; t < tokens; t++) {
-                const size_t src = ((size_t)h * bs + t) * hd, dst = ((size_t)h * c->len + b * bs + t) * hd;
-                memcpy(k_host + dst, pk.data() + src, (size_t)hd * 2);
-                memcpy(v_host + dst, pv.data() + src, (size_t)hd * 2);
+                const size_t src = ((size_t)h * bs + t) * hd * esz, dst = ((size_t)h * c->len + b * bs + t) * hd * esz;
+                memcpy((uint8_t*)k_host + dst, pk.data() + src, (size_t)hd * esz);
+                memcpy((uint8_t*)v_host + dst, pv.data() + src, (size_t)hd * esz);
             }
     }
     return B2_OK;
 }
+int32_t b2_cache_gather(b2_cache* c, int32_t layer, uint16_t* k_host, uint16_t* v_host) { return cache_gather(c, layer, k_host, v_host, 2); }
+int32_t b2_cache_gather_f32(b2_cache* c, int32_t layer, float* k_host, float* v_host) { return cache_gather(c, layer, k_host, v_host, 4); }
 
 }  // extern "C"

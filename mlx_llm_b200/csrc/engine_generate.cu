@@ -163,7 +163,7 @@ struct b2_continuous {
         }
         return rc;
     }
-    bool has_work() const { return !lanes.empty() || (chunked && next_req < n); }
+    bool has_work() const { return !lanes.empty() || next_req < n; }
 
     // One iteration of the loop (continuous.rs:167-190).  *done is set when nothing is left.
     int32_t step(bool* done) {
@@ -177,7 +177,7 @@ struct b2_continuous {
             *done = true;
             return B2_OK;
         }
-        if (chunked) B2_CHECK(fill_slots());
+        if (chunked || lanes.empty()) B2_CHECK(fill_slots());  // lanes can be empty while requests have yet to arrive
         if (lanes.empty()) {
             if (next_req >= n) {
                 *done = true;

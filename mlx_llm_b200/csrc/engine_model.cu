@@ -122,7 +122,7 @@ int32_t alloc_proj(b2_model* m, Proj& p, int N, int K, int bits) {
     p.K = K;
     p.bits = bits;
     if (bits == 0) {
-        B2_CHECK(dev_alloc(m, (size_t)N * K * 2, &p.w));
+        B2_CHECK(dev_alloc(m, (size_t)N * K * (m->f32 ? 4 : 2), &p.w));
     } else {
         B2_REQUIRE(K % 64 == 0, B2_ERR_UNSUPPORTED, "quantized projection: group size 64 must divide the input dimension");
         B2_CHECK(dev_alloc(m, (size_t)N * K * bits / 8, &p.w));
@@ -144,6 +144,8 @@ int32_t validate_cfg(const b2_model_config& c) {
                "model config: hidden and intermediate sizes must be multiples of 8");
     B2_REQUIRE(c.quant_bits == 0 || c.quant_bits == 4 || c.quant_bits == 8, B2_ERR_UNSUPPORTED, "model config: quantization bits must be 4 or 8");
     B2_REQUIRE(c.quant_bits == 0 || c.quant_group == 64, B2_ERR_UNSUPPORTED, "model config: quantization group size must be 64");
+    B2_REQUIRE(!c.compute_f32 || (c.quant_bits == 0 && c.qk_norm == 0), B2_ERR_UNSUPPORTED,
+               "model config: the f32 path takes dense projections without q/k norm only");
     return B2_OK;
 }
 
@@ -159,6 +161,7 @@ int32_t set_local_dims(b2_model* m, b2_tp_group* tp) {
         B2_REQUIRE((c.num_heads / world * c.head_dim) % 64 == 0, B2_ERR_UNSUPPORTED,
                    "tensor parallelism: every rank's slice of the attention width must be a multiple of 64");
     }
+    B2_REQUIRE(world == 1 || !c.compute_f32, B2_ERR_UNSUPPORTED, "tensor parallelism: not available on the f32 path");
     m->tp = world > 1 ? tp : nullptr;
     m->hq_l = c.num_heads / world;
     m->hkv_l = c.num_kv_heads / world;
@@ -191,6 +194,21 @@ int32_t b2_model_ensure_rope(b2_model* m, int positions) {
     B2_CUDA(cudaMalloc((void**)&m->sin_tab, s.size() * 2));
     B2_CUDA(cudaMemcpyAsync(m->cos_tab, c.data(), c.size() * 2, cudaMemcpyHostToDevice, m->ctx->stream));
     B2_CUDA(cudaMemcpyAsync(m->sin_tab, s.data(), s.size() * 2, cudaMemcpyHostToDevice, m->ctx->stream));
+    if (m->f32) {  // the f32 path rotates with unrounded tables: angle = pos*inv_freq in f32, cosf / sinf on the host (rope.rs:183-208)
+        std::vector<float> cf((size_t)n * half), sf((size_t)n * half);
+        for (int pos = 0; pos < n; pos++)
+            for (int i = 0; i < half; i++) {
+                const float ang = (float)pos * m->inv_freq[i];
+                cf[(size_t)pos * half + i] = std::cos(ang);
+                sf[(size_t)pos * half + i] = std::sin(ang);
+            }
+        if (m->cos_f32) cudaFree(m->cos_f32);
+        if (m->sin_f32) cudaFree(m->sin_f32);
+        B2_CUDA(cudaMalloc((void**)&m->cos_f32, cf.size() * 4));
+        B2_CUDA(cudaMalloc((void**)&m->sin_f32, sf.size() * 4));
+        B2_CUDA(cudaMemcpyAsync(m->cos_f32, cf.data(), cf.size() * 4, cudaMemcpyHostToDevice, m->ctx->stream));
+        B2_CUDA(cudaMemcpyAsync(m->sin_f32, sf.data(), sf.size() * 4, cudaMemcpyHostToDevice, m->ctx->stream));
+    }
     B2_CUDA(cudaStreamSynchronize(m->ctx->stream));  // ordered on the context stream; host buffers die here
     m->rope_positions = n;
     return B2_OK;
@@ -396,11 +414,35 @@ int32_t b2_model_config_from_json(const char* json, b2_model_config* out) {
 }
 
 // ---- CausalLm::from_weights_with (src/models/llama.rs:57-303) ---------------------------------------
+// `dst` receives bf16 (every tensor is cast as llama.rs:71 does), or f32 for an f32 model (F32 sources unchanged,
+// BF16 / F16 sources widened).
 static int32_t upload_bf16(b2_model* m, const b2_weights* w, const std::string& key, int64_t expect_elems, uint16_t* dst) {
     auto it = w->t.find(key);
     B2_REQUIRE(it != w->t.end(), B2_ERR_MISSING_TENSOR, "missing tensor `" + key + "`");
     const HostTensor& t = it->second;
     B2_REQUIRE(t.numel() == expect_elems, B2_ERR_CONFIG, "tensor `" + key + "` has an unexpected size");
+    if (m->f32) {
+        B2_REQUIRE(t.dtype == B2_DTYPE_F32 || t.dtype == B2_DTYPE_F16 || t.dtype == B2_DTYPE_BF16, B2_ERR_CONFIG,
+                   "tensor `" + key + "` is not a floating-point tensor");
+        std::vector<float> tmp;
+        const float* src = (const float*)t.ptr;
+        if (t.dtype != B2_DTYPE_F32) {
+            tmp.resize((size_t)expect_elems);
+            const uint16_t* h = (const uint16_t*)t.ptr;
+            for (int64_t i = 0; i < expect_elems; i++) {
+                if (t.dtype == B2_DTYPE_F16) {
+                    tmp[i] = h_half2f(h[i]);
+                } else {
+                    const uint32_t u = (uint32_t)h[i] << 16;
+                    memcpy(&tmp[i], &u, 4);
+                }
+            }
+            src = tmp.data();
+        }
+        B2_CUDA(cudaMemcpyAsync(dst, src, (size_t)expect_elems * 4, cudaMemcpyHostToDevice, m->ctx->stream));
+        B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        return B2_OK;
+    }
     if (t.dtype == B2_DTYPE_BF16) {
         // every copy goes through the context stream (a plain cudaMemcpy is not ordered against it)
         B2_CUDA(cudaMemcpyAsync(dst, t.ptr, (size_t)expect_elems * 2, cudaMemcpyHostToDevice, m->ctx->stream));
@@ -443,7 +485,8 @@ static int32_t load_proj_rows(b2_model* m, const b2_weights* w, const std::strin
         B2_CHECK(upload_bf16(m, w, base + ".biases", (int64_t)N * (K / 64), dst.biases + (size_t)row0 * (K / 64)));
         return B2_OK;
     }
-    if (dst.bits == 0) return upload_bf16(m, w, key, (int64_t)N * K, (uint16_t*)dst.w + (size_t)row0 * K);
+    if (dst.bits == 0)
+        return upload_bf16(m, w, key, (int64_t)N * K, reinterpret_cast<uint16_t*>((uint8_t*)dst.w + (size_t)row0 * K * (m->f32 ? 4 : 2)));
     // quantize-on-load (Projection::load_with_bias, projection.rs:57-71)
     (void)quant;
     uint16_t* tmp = nullptr;
@@ -522,6 +565,8 @@ int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* p
     m->ctx = ctx;
     m->cfg = c;
     m->quantized = bits != 0;
+    m->f32 = c.compute_f32 != 0;
+    const size_t es = m->f32 ? 4 : 2;  // bytes per element of every dense tensor
     auto fail = [&](int32_t rc) {
         b2_model_free(m);
         return rc;
@@ -534,14 +579,14 @@ int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* p
     TRY(set_local_dims(m, tp));
     const int rank = m->tp ? m->tp->rank : 0, world = m->tp ? m->tp->world : 1;
     const int H = c.hidden_size, V = c.vocab_size, hd = c.head_dim;
-    TRY(dev_alloc(m, (size_t)V * H * 2, (void**)&m->embed));
+    TRY(dev_alloc(m, (size_t)V * H * es, (void**)&m->embed));
     TRY(upload_bf16(m, w, P("embed_tokens.weight"), (int64_t)V * H, m->embed));
-    TRY(dev_alloc(m, (size_t)H * 2, (void**)&m->norm));
+    TRY(dev_alloc(m, (size_t)H * es, (void**)&m->norm));
     TRY(upload_bf16(m, w, P("norm.weight"), H, m->norm));
     if (c.tie_word_embeddings) {
         m->lm_head = m->embed;  // llama.rs:124-128
     } else {
-        TRY(dev_alloc(m, (size_t)V * H * 2, (void**)&m->lm_head));
+        TRY(dev_alloc(m, (size_t)V * H * es, (void**)&m->lm_head));
         TRY(upload_bf16(m, w, join(pre, "lm_head.weight"), (int64_t)V * H, m->lm_head));
     }
     m->layers.resize(c.num_layers);
@@ -549,14 +594,14 @@ int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* p
     for (int l = 0; l < c.num_layers; l++) {
         LayerW& L = m->layers[l];
         auto LP = [&](const std::string& s) { return P("layers." + std::to_string(l) + "." + s); };
-        TRY(dev_alloc(m, (size_t)H * 2, (void**)&L.input_ln));
+        TRY(dev_alloc(m, (size_t)H * es, (void**)&L.input_ln));
         TRY(upload_bf16(m, w, LP("input_layernorm.weight"), H, L.input_ln));
-        TRY(dev_alloc(m, (size_t)H * 2, (void**)&L.post_ln));
+        TRY(dev_alloc(m, (size_t)H * es, (void**)&L.post_ln));
         TRY(upload_bf16(m, w, LP("post_attention_layernorm.weight"), H, L.post_ln));
         if (c.qk_norm) {
-            TRY(dev_alloc(m, (size_t)hd * 2, (void**)&L.q_norm));
+            TRY(dev_alloc(m, (size_t)hd * es, (void**)&L.q_norm));
             TRY(upload_bf16(m, w, LP("self_attn.q_norm.weight"), hd, L.q_norm));
-            TRY(dev_alloc(m, (size_t)hd * 2, (void**)&L.k_norm));
+            TRY(dev_alloc(m, (size_t)hd * es, (void**)&L.k_norm));
             TRY(upload_bf16(m, w, LP("self_attn.k_norm.weight"), hd, L.k_norm));
         }
         const int qd_l = qd / world, kvd_l = kvd / world, I_l = I / world;  // this rank's rows / columns
@@ -590,6 +635,7 @@ int32_t b2_model_synthetic_tp(b2_ctx* ctx, const b2_model_config* cfg, uint64_t 
     b2_model_config c = *cfg;
     if (c.quant_bits && !c.quant_group) c.quant_group = 64;
     B2_CHECK(validate_cfg(c));
+    B2_REQUIRE(!c.compute_f32, B2_ERR_UNSUPPORTED, "b2_model_synthetic: the synthetic recipe draws bf16 weights; the f32 path loads weights");
     b2_model* m = new b2_model();
     m->ctx = ctx;
     m->cfg = c;
@@ -681,6 +727,9 @@ int32_t b2_model_free(b2_model* m) {
     for (void* p : m->allocs) cudaFree(p);
     if (m->cos_tab) cudaFree(m->cos_tab);
     if (m->sin_tab) cudaFree(m->sin_tab);
+    if (m->cos_f32) cudaFree(m->cos_f32);
+    if (m->sin_f32) cudaFree(m->sin_f32);
+    b2_forward_f32_release(m);
     Workspace& w = m->ws;
     void* dev[] = {w.x_in_peer_region ? nullptr : (void*)w.x, w.tp_part, w.xn, w.qkv, w.q, w.attn, w.gu, w.act, w.last, w.logits, w.argmax, w.ids, w.meta, w.stage_dev, w.attn_scratch};
     for (void* p : dev)

@@ -148,101 +148,12 @@ int pick_chunk_tiles(long dec_ctx_sum, int hkv, int sm_count) {
     return chunk / 16;
 }
 
-}  // namespace
-
-int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* logits_out, int32_t* argmax_out) {
+// The bf16 layers of one step: embedding, every decoder layer, the sampled rows' final norm, lm_head and argmax.
+int32_t forward_bf16_layers(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const BatchMetaIn& in, const int32_t* ids_dev, int T, int n_dec,
+                            long dec_ctx_sum, int W, int P, double pf_flops, int chunk_tiles, int q_tile, int n_logits) {
     b2_ctx* ctx = m->ctx;
     const b2_model_config& c = m->cfg;
-    const int B = (int)seqs.size();
-    if (B == 0) return B2_OK;
-    B2_CUDA(cudaSetDevice(ctx->device));
-    b2_pool* pool = seqs[0].cache->pool;
-    int T = 0, max_pos = 0, n_logits = 0, n_dec = 0;
-    long dec_ctx_sum = 0;
-    for (auto& s : seqs) {
-        B2_REQUIRE(s.cache && s.cache->pool == pool, B2_ERR_MSG, "forward: all caches of a step must share one pool");
-        B2_REQUIRE(s.n > 0, B2_ERR_MSG, "forward: a sequence contributes no token");
-        T += s.n;
-        max_pos = std::max(max_pos, s.cache->len + s.n);
-        n_logits += s.want_logits ? 1 : 0;
-        if (s.n == 1) {
-            n_dec++;
-            dec_ctx_sum += s.cache->len + 1;
-        }
-    }
-    for (int i = 0; i < B; i++)
-        for (int j = i + 1; j < B && B <= 64; j++)
-            B2_REQUIRE(seqs[i].cache != seqs[j].cache, B2_ERR_MSG, "forward: a cache appears twice in one step");
-    B2_CHECK(b2_model_ensure_rope(m, max_pos));
-    // pages for the new tokens (host allocator), then the step descriptors
-    for (auto& s : seqs) B2_CHECK(b2_cache_reserve(s.cache, s.n));
-    const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, m->hkv_l, ctx->sm_count);
-    const int q_tile = b2_prefill_q_tile(ctx, c.head_dim);
-    int W = 0, P = 0;
-    double pf_flops = 0;  // 4*hd*hq flops per (query, visible key) pair
-    for (auto& s : seqs) {
-        if (s.n > 1) pf_flops += 4.0 * c.head_dim * m->hq_l * ((double)s.n * s.cache->len + 0.5 * (double)s.n * (s.n + 1));
-        if (s.n == 1) {
-            const int tiles = (s.cache->len + 1 + 15) / 16;
-            W += (tiles + chunk_tiles - 1) / chunk_tiles;
-        } else {
-            P += (s.n + q_tile - 1) / q_tile;
-        }
-    }
-    const int U = (int)pool->upd_slot.size();
-    const size_t stage_ints = 4 * (size_t)B + 3 * (size_t)U + (size_t)T;
-    B2_CHECK(ensure_workspace(m, T, B, W, P, stage_ints));
     Workspace& w = m->ws;
-    int32_t* sh = w.stage_host;
-    for (int i = 0; i < B; i++) {
-        sh[i] = seqs[i].cache->slot;
-        sh[B + i] = seqs[i].n;
-        sh[2 * B + i] = seqs[i].cache->len;
-        sh[3 * B + i] = seqs[i].want_logits ? 1 : 0;
-    }
-    if (U) {
-        memcpy(sh + 4 * B, pool->upd_slot.data(), (size_t)U * 4);
-        memcpy(sh + 4 * B + U, pool->upd_index.data(), (size_t)U * 4);
-        memcpy(sh + 4 * B + 2 * U, pool->upd_page.data(), (size_t)U * 4);
-    }
-    {
-        int32_t* ids = sh + 4 * B + 3 * U;
-        for (auto& s : seqs) {
-            memcpy(ids, s.ids, (size_t)s.n * 4);
-            ids += s.n;
-        }
-    }
-    cudaStream_t st = ctx->stream;
-    B2_CUDA(cudaEventRecord(m->ev0, st));
-    b2_prof_mark(ctx, B2_CLS_META);
-    B2_CUDA(cudaMemcpyAsync(w.stage_dev, sh, stage_ints * 4, cudaMemcpyHostToDevice, st));
-    m->h2d_bytes += (int64_t)stage_ints * 4;
-    pool->upd_slot.clear();
-    pool->upd_index.clear();
-    pool->upd_page.clear();
-
-    BatchMetaIn in{};
-    const int32_t* d = w.stage_dev;
-    in.seq_slot = d;
-    in.q_len = d + B;
-    in.ctx_before = d + 2 * B;
-    in.want_logits = d + 3 * B;
-    in.upd_slot = d + 4 * B;
-    in.upd_index = d + 4 * B + U;
-    in.upd_page = d + 4 * B + 2 * U;
-    const int32_t* ids_dev = d + 4 * B + 3 * U;
-    in.B = B;
-    in.T = T;
-    in.U = U;
-    in.chunk_tiles = chunk_tiles;
-    in.q_tile = q_tile;
-    in.page_size = pool->block_size;
-    in.max_blocks = pool->max_blocks;
-    BatchMetaOut mo{};
-    mo.block_tables = pool->block_tables;
-    b2_batch_meta_carve(w.meta, B, T, W, P, mo);
-    B2_CHECK(b2_batch_meta_launch(ctx, in, mo));
-
     const int H = c.hidden_size, hq = m->hq_l, hkv = m->hkv_l, hd = c.head_dim, I = m->inter_l;  // this rank's heads / columns
     const bool tp = m->tp && m->tp->world > 1;
     const int qkv_w = (hq + 2 * hkv) * hd;
@@ -357,21 +268,134 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
         B2_CHECK(gemm(m, head, w.last, n_logits, H, w.logits, c.vocab_size, nullptr, w.b_cap));
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
         B2_CHECK(b2_argmax_launch(ctx, w.logits, n_logits, c.vocab_size, w.argmax));
+    }
+    return B2_OK;
+}
+
+}  // namespace
+
+int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_out, int32_t* argmax_out) {
+    b2_ctx* ctx = m->ctx;
+    const b2_model_config& c = m->cfg;
+    const int B = (int)seqs.size();
+    if (B == 0) return B2_OK;
+    B2_CUDA(cudaSetDevice(ctx->device));
+    b2_pool* pool = seqs[0].cache->pool;
+    int T = 0, max_pos = 0, n_logits = 0, n_dec = 0;
+    long dec_ctx_sum = 0;
+    for (auto& s : seqs) {
+        B2_REQUIRE(s.cache && s.cache->pool == pool, B2_ERR_MSG, "forward: all caches of a step must share one pool");
+        B2_REQUIRE(s.n > 0, B2_ERR_MSG, "forward: a sequence contributes no token");
+        T += s.n;
+        max_pos = std::max(max_pos, s.cache->len + s.n);
+        n_logits += s.want_logits ? 1 : 0;
+        if (s.n == 1) {
+            n_dec++;
+            dec_ctx_sum += s.cache->len + 1;
+        }
+    }
+    {  // a cache may appear once per step: stamp each with the number of this step
+        const uint64_t stamp = ++pool->step_stamp;
+        for (auto& s : seqs) {
+            B2_REQUIRE(s.cache->step_stamp != stamp, B2_ERR_MSG, "forward: a cache appears twice in one step");
+            s.cache->step_stamp = stamp;
+        }
+    }
+    B2_CHECK(b2_model_ensure_rope(m, max_pos));
+    // pages for the new tokens (host allocator), then the step descriptors
+    for (auto& s : seqs) B2_CHECK(b2_cache_reserve(s.cache, s.n));
+    const int chunk_tiles = pick_chunk_tiles(dec_ctx_sum, m->hkv_l, ctx->sm_count);
+    const int q_tile = b2_prefill_q_tile(ctx, c.head_dim);
+    int W = 0, P = 0;
+    double pf_flops = 0;  // 4*hd*hq flops per (query, visible key) pair
+    for (auto& s : seqs) {
+        if (s.n > 1) pf_flops += 4.0 * c.head_dim * m->hq_l * ((double)s.n * s.cache->len + 0.5 * (double)s.n * (s.n + 1));
+        if (s.n == 1) {
+            const int tiles = (s.cache->len + 1 + 15) / 16;
+            W += (tiles + chunk_tiles - 1) / chunk_tiles;
+        } else {
+            P += (s.n + q_tile - 1) / q_tile;
+        }
+    }
+    const int U = (int)pool->upd_slot.size();
+    const size_t stage_ints = 4 * (size_t)B + 3 * (size_t)U + (size_t)T;
+    B2_CHECK(ensure_workspace(m, T, B, W, P, stage_ints));
+    Workspace& w = m->ws;
+    int32_t* sh = w.stage_host;
+    for (int i = 0; i < B; i++) {
+        sh[i] = seqs[i].cache->slot;
+        sh[B + i] = seqs[i].n;
+        sh[2 * B + i] = seqs[i].cache->len;
+        sh[3 * B + i] = seqs[i].want_logits ? 1 : 0;
+    }
+    if (U) {
+        memcpy(sh + 4 * B, pool->upd_slot.data(), (size_t)U * 4);
+        memcpy(sh + 4 * B + U, pool->upd_index.data(), (size_t)U * 4);
+        memcpy(sh + 4 * B + 2 * U, pool->upd_page.data(), (size_t)U * 4);
+    }
+    {
+        int32_t* ids = sh + 4 * B + 3 * U;
+        for (auto& s : seqs) {
+            memcpy(ids, s.ids, (size_t)s.n * 4);
+            ids += s.n;
+        }
+    }
+    cudaStream_t st = ctx->stream;
+    B2_CUDA(cudaEventRecord(m->ev0, st));
+    b2_prof_mark(ctx, B2_CLS_META);
+    B2_CUDA(cudaMemcpyAsync(w.stage_dev, sh, stage_ints * 4, cudaMemcpyHostToDevice, st));
+    m->h2d_bytes += (int64_t)stage_ints * 4;
+    pool->upd_slot.clear();
+    pool->upd_index.clear();
+    pool->upd_page.clear();
+
+    BatchMetaIn in{};
+    const int32_t* d = w.stage_dev;
+    in.seq_slot = d;
+    in.q_len = d + B;
+    in.ctx_before = d + 2 * B;
+    in.want_logits = d + 3 * B;
+    in.upd_slot = d + 4 * B;
+    in.upd_index = d + 4 * B + U;
+    in.upd_page = d + 4 * B + 2 * U;
+    const int32_t* ids_dev = d + 4 * B + 3 * U;
+    in.B = B;
+    in.T = T;
+    in.U = U;
+    in.chunk_tiles = chunk_tiles;
+    in.q_tile = q_tile;
+    in.page_size = pool->block_size;
+    in.max_blocks = pool->max_blocks;
+    BatchMetaOut mo{};
+    mo.block_tables = pool->block_tables;
+    b2_batch_meta_carve(w.meta, B, T, W, P, mo);
+    B2_CHECK(b2_batch_meta_launch(ctx, in, mo));
+
+    float* logits_f32_dev = nullptr;
+    if (m->f32) {
+        B2_CHECK(b2_forward_f32(m, pool, mo, in.seq_slot, ids_dev, T, B, n_logits, max_pos, &logits_f32_dev));
+    } else {
+        B2_CHECK(forward_bf16_layers(m, pool, mo, in, ids_dev, T, n_dec, dec_ctx_sum, W, P, pf_flops, chunk_tiles, q_tile, n_logits));
+    }
+    if (n_logits > 0) {
         b2_prof_mark(ctx, B2_CLS_META);
         B2_CUDA(cudaMemcpyAsync(w.argmax_host, w.argmax, (size_t)n_logits * 4, cudaMemcpyDeviceToHost, st));
         m->d2h_bytes += (int64_t)n_logits * 4;
         if (logits_out) {
-            const size_t bytes = (size_t)n_logits * c.vocab_size * 2;
+            const size_t bytes = (size_t)n_logits * c.vocab_size * (m->f32 ? 4 : 2);
             if (bytes > w.logits_host_cap) {
                 B2_CUDA(cudaStreamSynchronize(st));
                 if (w.logits_host) cudaFreeHost(w.logits_host);
                 B2_CUDA(cudaHostAlloc((void**)&w.logits_host, bytes, cudaHostAllocDefault));
                 w.logits_host_cap = bytes;
             }
-            B2_CUDA(cudaMemcpyAsync(w.logits_host, w.logits, bytes, cudaMemcpyDeviceToHost, st));
+            B2_CUDA(cudaMemcpyAsync(w.logits_host, m->f32 ? (const void*)logits_f32_dev : (const void*)w.logits, bytes, cudaMemcpyDeviceToHost, st));
             m->d2h_bytes += (int64_t)bytes;
         }
     }
+    // the error word a bounded device-side wait raises travels back with the sampled ids
+    B2_CUDA(cudaMemcpyAsync(ctx->err_host, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    m->d2h_bytes += (int64_t)sizeof(int);
     b2_prof_mark(ctx, -1);
     B2_CUDA(cudaEventRecord(m->ev1, st));
     B2_CUDA(cudaStreamSynchronize(st));
@@ -380,16 +404,25 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, uint16_t* log
     float ms = 0.f;
     B2_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->device_ms += ms;
+    if (ctx->err_host[0] != 0) {
+        // the step's hidden state is incomplete: nothing is sampled and the caches do not advance (their pages
+        // stay reserved and are reused by the next step or released with the cache)
+        const int code = ctx->err_host[0];
+        ctx->err_host[0] = 0;
+        B2_CUDA(cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), st));
+        return b2_fail(B2_ERR_TIMEOUT, "forward: a bounded device-side wait ran out (code " + std::to_string(code) +
+                                           "): the step was abandoned, no token was sampled and no cache advanced");
+    }
     if (n_logits > 0) {
         if (argmax_out) memcpy(argmax_out, w.argmax_host, (size_t)n_logits * 4);
-        if (logits_out) memcpy(logits_out, w.logits_host, (size_t)n_logits * c.vocab_size * 2);
+        if (logits_out) memcpy(logits_out, w.logits_host, (size_t)n_logits * c.vocab_size * (m->f32 ? 4 : 2));
     }
     for (auto& s : seqs) b2_cache_commit(s.cache, s.n);
     return B2_OK;
 }
 
 extern "C" int32_t b2_model_step(b2_model* m, const int32_t* ids_host, const int32_t* n_tokens, int32_t num_seqs, b2_cache** caches,
-                                 uint16_t* logits_host, int32_t* argmax_host) {
+                                 void* logits_host, int32_t* argmax_host) {
     B2_REQUIRE(m && ids_host && n_tokens && caches, B2_ERR_MSG, "b2_model_step: null argument");
     std::vector<SeqStep> seqs;
     const int32_t* cur = ids_host;

@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
     if (w >= *p.n_work) return;
     const int kvh = blockIdx.y;
     const int seq = p.work_seq[w], chunk = p.work_chunk[w];
-    const int ctx = p.ctx_lens[seq];
+    const int ctx = min(p.ctx_lens[seq], p.max_blocks * p.page_tiles * 16);  // never past the block-table row
     const int tiles_total = (ctx + 15) >> 4;
     const int tile0 = chunk * p.chunk_tiles;
     const int n_tiles = min(p.chunk_tiles, tiles_total - tile0);
@@ -229,9 +229,14 @@ __global__ void paged_attn_merge_kernel(const DecodeAttnParams p) {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int seq = blockIdx.x, kvh = blockIdx.y;
     const int w0 = p.seq_work_off[seq], n = p.seq_work_off[seq + 1] - w0;
-    if (n <= 1) return;
+    if (n == 1) return;  // written by the decode kernel itself
     const int group = p.hq / p.hkv;
     const int qrow = p.q_rows ? p.q_rows[seq] : seq;
+    if (n <= 0) {  // an empty context attends to nothing: its rows are zeros
+        for (int e = threadIdx.x; e < group * HD; e += blockDim.x)
+            p.out[((size_t)qrow * p.hq + (size_t)kvh * group + e / HD) * HD + e % HD] = 0;
+        return;
+    }
     for (int e = threadIdx.x; e < group * HD; e += blockDim.x) {
         const int h = e / HD, d = e % HD;
         float M = -INFINITY;
@@ -249,7 +254,9 @@ __global__ void paged_attn_merge_kernel(const DecodeAttnParams p) {
 
 // Split-K work list for a plain [num_seqs] batch (the engine's packer builds the same list
 // together with the rest of the step metadata).
-__global__ void decode_worklist_kernel(const int32_t* ctx_lens, int num_seqs, int chunk_tiles, int32_t* work_seq,
+// A context length beyond what the block-table row can address is clamped to `per_seq` chunks (the lists and
+// the partial sums are sized for per_seq chunks per sequence; the decode kernel clamps the same way).
+__global__ void decode_worklist_kernel(const int32_t* ctx_lens, int num_seqs, int chunk_tiles, int per_seq, int32_t* work_seq,
                                        int32_t* work_chunk, int32_t* seq_work_off, int32_t* n_work) {
     __shared__ int sh[1024];
     __shared__ int carry;
@@ -259,8 +266,8 @@ __global__ void decode_worklist_kernel(const int32_t* ctx_lens, int num_seqs, in
         const int i = base + threadIdx.x;
         int n = 0;
         if (i < num_seqs) {
-            const int tiles = (ctx_lens[i] + 15) >> 4;
-            n = (tiles + chunk_tiles - 1) / chunk_tiles;
+            const int tiles = (max(ctx_lens[i], 0) + 15) >> 4;
+            n = min((tiles + chunk_tiles - 1) / chunk_tiles, per_seq);
         }
         sh[threadIdx.x] = n;
         __syncthreads();
@@ -372,7 +379,7 @@ extern "C" int32_t b2_paged_attn_decode(b2_ctx* ctx, const uint16_t* q_dev, cons
     p.seq_work_off = seq_off;
     p.n_work = n_work;
     p.out = out_dev;
-    decode_worklist_kernel<<<1, 1024, 0, ctx->stream>>>(ctx_lens_dev, num_seqs, chunk_tiles, work_seq, work_chunk, seq_off, n_work);
+    decode_worklist_kernel<<<1, 1024, 0, ctx->stream>>>(ctx_lens_dev, num_seqs, chunk_tiles, (int)per_seq, work_seq, work_chunk, seq_off, n_work);
     B2_LAUNCHED(ctx);
     return b2_decode_attn_launch(ctx, p, head_dim, (int)max_work, num_seqs);
 }
@@ -410,7 +417,9 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBy
 namespace {
 // Device address of g_decode_scratch per device.  In host code the array's name is only a handle
 // for the runtime, not an address a kernel could use, so it is resolved once per device with
-// cudaGetSymbolAddress while that device is current.
+// cudaGetSymbolAddress while that device is current.  The two caches below are plain globals: two host
+// threads that make their FIRST call on one device at the same moment both run the set-up and store the
+// same values, which is harmless; after that the call only reads them.
 unsigned char* g_scratch_addr[64] = {};
 bool g_static_smem_set[64][2] = {};
 }  // namespace
@@ -486,7 +495,7 @@ extern "C" int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_d
     // Nothing in the array has to start at zero: the work list (and its count) is rewritten by the
     // first kernel of every call, and every partial the merge reads is written by this call's decode
     // kernel first.
-    decode_worklist_kernel<<<1, 1024, 0, st>>>(ctx_lens_dev, num_seqs, chunk_tiles, work_seq, work_chunk, seq_off, n_work);
+    decode_worklist_kernel<<<1, 1024, 0, st>>>(ctx_lens_dev, num_seqs, chunk_tiles, (int)per_seq, work_seq, work_chunk, seq_off, n_work);
     const dim3 grid((unsigned)max_work, hkv);
     int threads = group * head_dim > 1024 ? 1024 : group * head_dim;
     if (head_dim == 128) {

@@ -38,7 +38,6 @@ constexpr size_t kFlag1Off = 0;                         // u32 [kMaxWorld]
 constexpr size_t kFlag2Off = 128;                       // u32 [kMaxWorld][kMaxCtas]
 constexpr size_t kDataOff = 128 + (size_t)kMaxWorld * kMaxCtas * 4 + 128;  // partial sums start here (256-byte aligned)
 static_assert(kDataOff % 256 == 0, "data offset alignment");
-constexpr long long kWaitCycles = 8000000000LL;         // ~4 s at 1.9 GHz
 
 struct PeerReduceParams {
     unsigned char* base[kMaxWorld];  // every rank's region as mapped in this process
@@ -50,6 +49,7 @@ struct PeerReduceParams {
     size_t slot_bytes;               // slot s of a region sits at kDataOff + s * slot_bytes
     size_t x_off;                    // offset of x in a region
     int* err;                        // the error word of the context (of rank 0's context when emulating)
+    long long wait_cycles;           // limit of every wait on another rank (the context's setting)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -66,10 +66,10 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* p) {
     return v;
 }
 // Spins until *flag has reached `seq` (wrap-safe); false when the limit ran out.
-__device__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
+__device__ bool wait_flag(const uint32_t* flag, uint32_t seq, long long limit) {
     const long long t0 = clock64();
     while ((int32_t)(ld_acquire_sys(flag) - seq) < 0) {
-        if (clock64() - t0 > kWaitCycles) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(64);
     }
     return true;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_residual_kernel(const Peer
         st_release_sys(reinterpret_cast<uint32_t*>(p.base[tid] + kFlag1Off) + r, p.seq);
     }
     if (tid < p.world && tid != r) {
-        if (!wait_flag(reinterpret_cast<const uint32_t*>(p.base[r] + kFlag1Off) + tid, p.seq)) {
+        if (!wait_flag(reinterpret_cast<const uint32_t*>(p.base[r] + kFlag1Off) + tid, p.seq, p.wait_cycles)) {
             atomicExch(p.err, 7);
             gave_up = 1;
         }
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_residual_kernel(const Peer
     __syncthreads();
     if (tid < p.world && tid != r) {
         st_release_sys(reinterpret_cast<uint32_t*>(p.base[tid] + kFlag2Off) + (size_t)r * kMaxCtas + g, p.seq);
-        if (!wait_flag(reinterpret_cast<const uint32_t*>(p.base[r] + kFlag2Off) + (size_t)tid * kMaxCtas + g, p.seq)) atomicExch(p.err, 8);
+        if (!wait_flag(reinterpret_cast<const uint32_t*>(p.base[r] + kFlag2Off) + (size_t)tid * kMaxCtas + g, p.seq, p.wait_cycles)) atomicExch(p.err, 8);
     }
 }
 
@@ -177,6 +177,7 @@ int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M) {
     p.slot_bytes = g->peer_slot_bytes;
     p.x_off = g->peer_x_off;
     p.err = g->ctx->dev_err;
+    p.wait_cycles = g->ctx->wait_cycles;
     tp_peer_reduce_residual_kernel<<<grid_for(M, p.chunk, kMaxCtas), 256, 0, g->ctx->stream>>>(p);
     B2_LAUNCHED(g->ctx);
     B2_CUDA(cudaGetLastError());
@@ -325,6 +326,7 @@ int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, 
     p.slot_bytes = g0->peer_slot_bytes;
     p.x_off = g0->peer_x_off;
     p.err = g0->ctx->dev_err;
+    p.wait_cycles = g0->ctx->wait_cycles;
     // every block of every rank resident at once: a cooperative launch, sized to fit
     int per_sm = 0;
     B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_peer_reduce_residual_kernel, 256, 0));

@@ -31,6 +31,7 @@ class CModelConfig(C.Structure):
         ("rope_factor", C.c_float), ("rope_low_freq_factor", C.c_float), ("rope_high_freq_factor", C.c_float),
         ("rope_original_context", C.c_float),
         ("qk_norm", C.c_int32), ("quant_bits", C.c_int32), ("quant_group", C.c_int32), ("tie_word_embeddings", C.c_int32),
+        ("compute_f32", C.c_int32),
     ]
 
 
@@ -174,13 +175,14 @@ class CausalLm:
         return PagedKvCache(pool)
 
     def step(self, seqs, want_logits=True):
-        """One ragged forward.  seqs: list of (ids, PagedKvCache).  Returns (logits bf16 [n, vocab] as
-        uint16, argmax int32 [n]).  Covers decode_logits / decode_logits_per_seq / Decode::step."""
+        """One ragged forward.  seqs: list of (ids, PagedKvCache).  Returns (logits [n, vocab]: bf16 as uint16, or
+        float32 for an f32 model; argmax int32 [n]).  Covers decode_logits / decode_logits_per_seq / Decode::step."""
         ids = np.concatenate([np.ascontiguousarray(s[0], np.int32) for s in seqs])
         n = np.array([len(s[0]) for s in seqs], np.int32)
         arr = (C.c_void_p * len(seqs))(*[s[1].h for s in seqs])
-        vocab = self.config().vocab_size
-        logits = np.empty((len(seqs), vocab), np.uint16) if want_logits else None
+        cfg = self.config()
+        vocab = cfg.vocab_size
+        logits = np.empty((len(seqs), vocab), np.float32 if cfg.compute_f32 else np.uint16) if want_logits else None
         am = np.empty(len(seqs), np.int32)
         check(load().b2_model_step(self.h, ids.ctypes.data_as(C.c_void_p), n.ctypes.data_as(C.c_void_p), len(seqs), arr,
                                    logits.ctypes.data_as(C.c_void_p) if want_logits else None, am.ctypes.data_as(C.c_void_p)))
@@ -377,6 +379,14 @@ class PagedKvCache:
         k = np.empty((n_kv_heads, n, head_dim), np.uint16)
         v = np.empty_like(k)
         check(load().b2_cache_gather(self.h, int(layer), k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)))
+        return k, v
+
+    def gather_f32(self, layer, n_kv_heads, head_dim):
+        """The same for a pool of an f32 model: float32 arrays."""
+        n = self.offset()
+        k = np.empty((n_kv_heads, n, head_dim), np.float32)
+        v = np.empty_like(k)
+        check(load().b2_cache_gather_f32(self.h, int(layer), k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)))
         return k, v
 
     def free(self):

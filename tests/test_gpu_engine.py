@@ -384,3 +384,160 @@ def test_quantize_on_load_q4_q8(env):
     from mlx_llm_b200._lib import B2Error
     with pytest.raises(B2Error):  # group size must divide the input dimension (688 % 64 != 0)
         H.build_engine_model(eng, ctx, H.CONFIG0, H.tiny_weights(), quant=eng.QuantSpec(64, 4))
+
+
+def test_seeded_then_truncated_before_any_step(env):
+    """A seeded cache truncated into its shared block BEFORE any forward: two block-table writes for one
+    (row, index) are pending at once, and the private copy must win, or the sequence would append into a page its
+    donor still reads.  Then a seeded cache freed before its first step, whose row goes to a new cache."""
+    ctx, eng, orc, model, omodel = env
+    rng = np.random.default_rng(15)
+    ids = rng.integers(0, 1024, size=40).astype(np.int32)
+    pool = eng.BlockPool(ctx, model, 16, 32, 2, 8)
+    a = eng.PagedKvCache(pool)
+    la, _ = model.step([(ids, a)])
+    donor = [a.gather(l, 2, 64) for l in range(2)]
+    b = eng.PagedKvCache.new_seeded(pool, a.shareable_prefix_blocks(40))
+    b.truncate(20)                      # no step in between: (row, 1) -> shared page, then -> private copy
+    other = rng.integers(0, 1024, size=20).astype(np.int32)
+    model.step([(other, b)])            # overwrites positions 20..39 of b's private copy
+    for l in range(2):
+        k, v = a.gather(l, 2, 64)
+        assert np.array_equal(k, donor[l][0]) and np.array_equal(v, donor[l][1]), "the donor's pages were written"
+    b.truncate(20)
+    lb, _ = model.step([(ids[20:], b)])
+    assert np.array_equal(lb, la)
+    b.free()
+    c = eng.PagedKvCache.new_seeded(pool, a.shareable_prefix_blocks(40))   # takes the row b had
+    c.free()                                                                # freed before its first step
+    d = eng.PagedKvCache(pool)                                              # same row again, cold
+    ld, _ = model.step([(ids, d)])
+    assert np.array_equal(ld, la)
+    for l in range(2):
+        k, v = a.gather(l, 2, 64)
+        assert np.array_equal(k, donor[l][0]) and np.array_equal(v, donor[l][1])
+    for x in (a, d):
+        x.free()
+    pool.free()
+
+
+@pytest.mark.parametrize("mode", ["exact", "chunked"])
+def test_staggered_arrivals_are_all_served(env, mode):
+    """Requests that arrive later than the lanes drain (arrival_s extension): the loop must idle until the next
+    arrival instead of ending, in the reference's schedule as well as in the chunked one."""
+    ctx, eng, orc, model, omodel = env
+    prompts = H.config0_prompts()[:3]
+    reqs = [eng.BatchRequest(p.tolist(), 4, arrival_s=0.05 + 0.15 * i) for i, p in enumerate(prompts)]  # none at t = 0
+    events = []
+    cfg = eng.ContinuousConfig(max_batch=2, block_size=16, exactness=eng.EXACT, prefill_chunk_tokens=32 if mode == "chunked" else 0)
+    outs = eng.generate_continuous(model, reqs, cfg, on_event=lambda i, e: events.append((i,) + e))
+    assert [o.finish_reason for o in outs] == [eng.MAX_TOKENS] * 3 and all(len(o.tokens) == 4 for o in outs)
+    assert sorted(e[0] for e in events if e[1] == "done") == [0, 1, 2]
+    for p, o in zip(prompts, outs):
+        assert o.tokens == eng.generate(model, p.tolist(), 4).tokens
+
+
+def test_duplicate_cache_in_a_large_step_is_rejected(env):
+    ctx, eng, orc, model, omodel = env
+    from mlx_llm_b200._lib import B2Error
+
+    pool = eng.BlockPool(ctx, model, 16, 200, 80, 2)
+    caches = [eng.PagedKvCache(pool) for _ in range(70)]
+    seqs = [([1, 2, 3], c) for c in caches] + [([4], caches[68])]
+    with pytest.raises(B2Error) as e:
+        model.step(seqs)
+    assert e.value.code == -7 and all(c.offset() == 0 for c in caches)
+    model.step([([1, 2, 3], c) for c in caches])   # the pool is still consistent
+    assert all(c.offset() == 3 for c in caches)
+    for c in caches:
+        c.free()
+    pool.free()
+
+
+# ---- configuration 0 as BASELINE words it: fp32 -----------------------------------------------------------------------
+CONFIG0_F32 = dict(H.CONFIG0, f32_mode=1)
+
+
+@pytest.fixture(scope="module")
+def env32():
+    """The tiny decoder with f32 weights, activations, pages and logits on both sides.  Engine and oracle then run
+    the same arithmetic in the same order (see csrc/engine_step_f32.cu), so the stated targets hold strictly."""
+    from mlx_llm_b200 import _lib, engine
+    from oracle import oracle as orc
+
+    ctx = _lib.Context(0)
+    weights = H.tiny_weights()
+    model = H.build_engine_model(engine, ctx, CONFIG0_F32, weights=weights)
+    omodel = H.build_oracle_model(orc, CONFIG0_F32, weights=weights)
+    yield ctx, engine, orc, model, omodel
+    model.free()
+    ctx.close()
+
+
+def test_config0_f32_logits_and_pages_strict(env32):
+    ctx, eng, orc, model, omodel = env32
+    assert model.config().compute_f32 == 1 and not model.is_quantized()
+    prompts = H.config0_prompts()
+    pool = eng.BlockPool(ctx, model, 16, 64, 4, 16)
+    caches = [eng.PagedKvCache(pool) for _ in prompts]
+    ocs = [orc.Cache(2, block_size=16) for _ in prompts]
+    feed, worst = prompts, 0.0
+    for step in range(6):   # one ragged prefill, then five decode steps over all four sequences
+        logits, am = model.step(list(zip(feed, caches)))
+        assert logits.dtype == np.float32
+        _, ref = omodel.forward([(f, c, c.offset()) for f, c in zip(feed, ocs)])
+        err = float(np.abs(logits - ref).max())
+        worst = max(worst, err)
+        assert err <= 2e-3, f"step {step}: logits max-abs {err}"
+        assert am.tolist() == [int(np.argmax(r)) for r in ref]
+        feed = [[int(a)] for a in am]
+    print(f"[config0 f32] worst logits max-abs over 6 steps: {worst:.3e}")
+    assert worst <= 1e-4   # in practice the two sides differ by the last bits of exp() only
+    for c, oc in zip(caches, ocs):
+        for layer in range(2):
+            k, v = c.gather_f32(layer, 2, 64)
+            ok_, ov_ = oc.gather(layer)
+            ok_ = ok_.view(np.float32).reshape(-1, 2, 64).transpose(1, 0, 2)
+            ov_ = ov_.view(np.float32).reshape(-1, 2, 64).transpose(1, 0, 2)
+            assert np.abs(k - ok_).max() <= 1e-5 and np.abs(v - ov_).max() <= 1e-5
+            if layer == 0:
+                assert np.array_equal(v, ov_)   # before any exp(): the same multiplies and adds in the same order
+    from mlx_llm_b200._lib import B2Error
+    with pytest.raises(B2Error):
+        caches[0].gather(0, 2, 64)   # bf16 view of f32 pages
+    for c in caches:
+        c.free()
+    pool.free()
+
+
+@pytest.mark.parametrize("mode", ["exact", "throughput", "chunked"])
+def test_config0_f32_greedy_streams_identical(env32, mode):
+    """The stated target: greedy token streams identical to the reference loop's for all 32 tokens of all four
+    sequences (tests/continuous.rs:92-118), in every schedule."""
+    ctx, eng, orc, model, omodel = env32
+    prompts = H.config0_prompts()
+    ref = omodel.generate_continuous(prompts, [32] * 4, max_batch=8, block_size=16)
+    reqs = [eng.BatchRequest(p.tolist(), 32) for p in prompts]
+    cfg = eng.ContinuousConfig(max_batch=8, block_size=16, exactness=eng.EXACT if mode == "exact" else eng.THROUGHPUT,
+                               prefill_chunk_tokens=48 if mode == "chunked" else 0)
+    events = []
+    outs, stats = eng.generate_continuous(model, reqs, cfg, on_event=lambda i, e: events.append((i,) + e), return_stats=True)
+    identical = sum(o.tokens == r for o, r in zip(outs, ref["tokens"]))
+    assert identical == 4, [next((j for j in range(32) if o.tokens[j] != r[j]), None) for o, r in zip(outs, ref["tokens"])]
+    assert [o.finish_reason for o in outs] == [eng.MAX_TOKENS] * 4
+    if mode != "chunked":
+        assert stats["peak_live_blocks"] == 22
+        assert events == [(r, "token" if k == 0 else "done", a, b) for r, k, a, b in ref["events"]]
+    for p, o in zip(prompts[:2], outs[:2]):   # and equal to the single-sequence loop (generate)
+        assert eng.generate(model, p.tolist(), 32).tokens == o.tokens
+
+
+def test_f32_model_limits(env32):
+    ctx, eng, orc, model, omodel = env32
+    from mlx_llm_b200._lib import B2Error
+
+    with pytest.raises(B2Error) as e:   # no quantize-on-load on the f32 path
+        H.build_engine_model(eng, ctx, dict(CONFIG0_F32, inter=640), H.tiny_weights(dict(H.CONFIG0, inter=640)), quant=eng.QuantSpec(64, 4))
+    assert e.value.code == -5
+    with pytest.raises(B2Error):
+        eng.CausalLm.synthetic(ctx, H.engine_config(eng, CONFIG0_F32), seed=0)

@@ -2,8 +2,9 @@
 
 Tolerance: max-abs 2e-3 against the oracle's f64-accumulated result (BASELINE's bound), strictly, on
 every configuration-1 shaped case (contexts >= 128, outputs well below 1).  Very short contexts give
-outputs of magnitude 2-4, where the rounding of the bf16 OUTPUT alone is up to 7.8e-3; there the rule
-is 2e-3 plus that rounding (helpers.close_bf16_out)."""
+outputs of magnitude 2-4, where the rounding of the bf16 OUTPUT alone is up to 7.8e-3; there the bound
+applies to the value before that rounding: the output must be a bf16 number that a value within 2e-3 of
+the reference rounds to (helpers.close_bf16_out)."""
 import numpy as np
 import pytest
 
@@ -105,8 +106,8 @@ def test_decode_config1_shape_scaled(env):
 
 
 def test_decode_linearity_full_size(env):
-    """Full configuration-1 size (64 sequences) through a size-independent property: attention is
-    linear in V, so out(V) + out(V') == out(V + V') within tolerance when V' = 2V."""
+    """Full configuration-1 size (64 sequences, contexts uniform in [128, 4096]): all 64 outputs against the
+    oracle, and a size-independent property: attention is linear in V, so out(2V) == 2 out(V) within tolerance."""
     ctx, kernels, _ = env
     rng = np.random.default_rng(0)
     ctx_lens = rng.integers(128, 4097, size=64)
@@ -122,13 +123,9 @@ def test_decode_linearity_full_size(env):
         outs.append(H.bf16_to_f32_np(o.download()))
         vp.free(); o.free()
     assert np.abs(2.0 * outs[0] - outs[1]).max() <= 2 * TOL  # outputs here are < 0.5 in magnitude
-    # spot-check 3 sequences against the oracle
-    for i in (0, 31, 63):
-        sub = dict(case)
-        sub["ctx_lens"] = case["ctx_lens"][i:i + 1]
-        sub["block_tables"] = case["block_tables"][i:i + 1]
-        sub["q"] = case["q"][i:i + 1]
-        from oracle import oracle as orc
-        ref = orc.paged_attention(sub["q"], case["kpool"], case["vpool"], sub["block_tables"], np.array([0, 1], np.int32),
-                                  sub["ctx_lens"], case["scale"])
-        assert np.abs(outs[0][i:i + 1] - ref).max() <= TOL
+    # every one of the 64 sequences against the oracle's f64-accumulated attention, at the strict bound
+    from oracle import oracle as orc
+    ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"], case["ctx_lens"],
+                              case["scale"])
+    err = np.abs(outs[0] - ref).max(axis=(1, 2))
+    assert err.shape == (64,) and err.max() <= TOL, f"worst sequence {int(err.argmax())}: max-abs {err.max()}"

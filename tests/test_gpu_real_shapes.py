@@ -1,0 +1,162 @@
+"""Engine against oracle on the shapes the benchmark runs, composed end to end (through the C ABI).
+
+Two-layer cuts of the real architectures keep every per-layer kernel, tile shape and dispatch decision of the
+full models while the CPU oracle still finishes in seconds:
+  * Llama-3-8B cut (hidden 4096, 32 q / 8 kv heads, head_dim 128, SwiGLU 14336, llama3-scaled RoPE, Q4 group 64,
+    vocabulary cut to 8192): a first ragged prefill, then a step that packs a 512-token prefill chunk with decode
+    rows (CausalLm::decode_logits_per_seq, src/models/llama.rs:530-558, over the chunked schedule), the rest of the
+    prompt, and a decode-only step;
+  * Qwen3-32B cut (hidden 5120, 64 q / 8 kv heads, per-head q/k RMSNorm before RoPE -- llama.rs:814-819 --, SwiGLU
+    25600, Q8 group 64);
+  * the four projection shapes of BASELINE configuration 2 (QuantizedLinear::forward, src/primitives/quant.rs:56-70)
+    at 1, 8, 32, 128 and 256 tokens, Q4 and Q8.
+Both sides generate the same weights from the counter-based recipe (no file travels).
+
+Gates.  Matmuls: the unrounded f32 accumulation within max-abs 2e-3 of the oracle.  Whole-decoder logits are bf16
+numbers behind dozens of bf16 roundings; the gate is the one configuration 0 uses (rms <= 2e-3, worst <= 1e-2 on
+logits whose rms is 0.32) scaled by the logits' rms, i.e. rms error <= 0.625 % and worst error <= 3.1 % of the
+logits' rms.  K/V pages: layer 0 sees identical inputs (values bit-exact, rotated keys within one bf16 ulp of the
+projection's rounding); layer 1 inherits layer 0's roundings."""
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+LLAMA_CUT = dict(layers=2, hidden=4096, heads=32, kv_heads=8, head_dim=128, inter=14336, vocab=8192, eps=1e-5, theta=500000.0,
+                 rope_kind=1, rope_factor=8.0, rope_low=1.0, rope_high=4.0, rope_orig=8192.0, qk_norm=0, quant_bits=4, group=64,
+                 f32_mode=0)
+QWEN_CUT = dict(layers=2, hidden=5120, heads=64, kv_heads=8, head_dim=128, inter=25600, vocab=8192, eps=1e-6, theta=1000000.0,
+                rope_kind=0, rope_factor=1.0, rope_low=1.0, rope_high=4.0, rope_orig=8192.0, qk_norm=1, quant_bits=8, group=64,
+                f32_mode=0)
+
+
+@pytest.fixture(scope="module")
+def env():
+    from mlx_llm_b200 import _lib, engine, kernels
+    from oracle import oracle as orc
+
+    ctx = _lib.Context(0)
+    yield ctx, engine, kernels, orc
+    ctx.close()
+
+
+def scaled_logits_gate(got_bf16, ref_f32):
+    got = H.bf16_to_f32_np(got_bf16)
+    err = got - ref_f32
+    scale = float(np.sqrt(np.mean(ref_f32 * ref_f32)))
+    rms, worst = float(np.sqrt(np.mean(err * err))) / scale, float(np.abs(err).max()) / scale
+    return bool(np.isfinite(got).all() and rms <= 2e-3 / 0.32 and worst <= 1e-2 / 0.32), rms, worst
+
+
+def run_schedule(env, cfg, steps, seed=0):
+    """steps: list of lists of (sequence index, number of new tokens).  Runs the same ragged schedule through the
+    engine and the oracle, compares the logits of every step and, at the end, every K/V page."""
+    ctx, eng, _, orc = env
+    model = eng.CausalLm.synthetic(ctx, H.engine_config(eng, cfg, quant_bits=cfg["quant_bits"]), seed=seed)
+    omodel = orc.Model(**cfg)
+    omodel.fill_synthetic(seed)
+    n_seq = 1 + max(s for st in steps for s, _ in st)
+    total = [sum(n for st in steps for s, n in st if s == i) for i in range(n_seq)]
+    rng = np.random.default_rng(11)
+    toks = [rng.integers(0, cfg["vocab"], size=t).astype(np.int32) for t in total]
+    pool = eng.BlockPool(ctx, model, 16, sum((t + 15) // 16 + 1 for t in total), n_seq, max((t + 15) // 16 + 1 for t in total))
+    caches = [eng.PagedKvCache(pool) for _ in range(n_seq)]
+    ocs = [orc.Cache(cfg["layers"], block_size=16) for _ in range(n_seq)]
+    report = []
+    for si, st in enumerate(steps):
+        feed = [(toks[s][caches[s].offset():caches[s].offset() + n], s) for s, n in st]
+        launches0 = ctx.launch_count()
+        logits, am = model.step([(ids, caches[s]) for ids, s in feed])
+        _, ref_f32 = omodel.forward([(ids, ocs[s], ocs[s].offset()) for ids, s in feed])
+        ok, rms, worst = scaled_logits_gate(logits, ref_f32)
+        # greedy choice: equal wherever the oracle's own top-2 margin exceeds what the gate can resolve
+        scale = float(np.sqrt(np.mean(ref_f32 * ref_f32)))
+        agree = 0
+        for r in range(len(st)):
+            order = np.argsort(-ref_f32[r])
+            margin = float(ref_f32[r][order[0]] - ref_f32[r][order[1]])
+            if int(am[r]) == int(order[0]):
+                agree += 1
+            else:
+                assert margin <= 2 * 1e-2 / 0.32 * scale, f"step {si} row {r}: argmax {int(am[r])} vs {int(order[0])} at margin {margin}"
+        report.append((si, sum(n for _, n in st), ctx.launch_count() - launches0, rms, worst, agree, len(st)))
+        assert ok, f"step {si} ({st}): relative rms {rms:.3e}, worst {worst:.3e}"
+    print(f"[{cfg['hidden']}-wide cut] (step, tokens, launches, rel rms, rel worst, argmax agree, rows): {report}")
+    hkv, hd = cfg["kv_heads"], cfg["head_dim"]
+    for c, oc in zip(caches, ocs):
+        assert c.offset() == oc.offset()
+        for layer in range(cfg["layers"]):
+            k, v = c.gather(layer, hkv, hd)
+            ok_, ov_ = oc.gather(layer)
+            ok_ = ok_.reshape(-1, hkv, hd).transpose(1, 0, 2)
+            ov_ = ov_.reshape(-1, hkv, hd).transpose(1, 0, 2)
+            if layer == 0:
+                # identical inputs: the only freedom is the f32 summation order inside the projection (and the
+                # q/k norm), i.e. isolated one-ulp roundings
+                assert H.bf16_ulp_diff(v, ov_).max() <= 1 and (v != ov_).mean() < 0.02
+                assert (k != ok_).mean() < 0.1
+            for got_, ref_ in ((k, ok_), (v, ov_)):
+                g32, r32 = H.bf16_to_f32_np(got_), H.bf16_to_f32_np(ref_)
+                err = np.abs(g32 - r32)
+                s = float(np.sqrt(np.mean(r32 * r32)))
+                assert np.sqrt(np.mean(err * err)) <= 2e-3 / 0.32 * s and err.max() <= 2e-2 / 0.32 * s, (layer, s, err.max())
+    for c in caches:
+        c.free()
+    pool.free()
+    model.free()
+    omodel.free()
+
+
+def test_llama3_8b_cut_q4_chunked_prefill_with_decode_rows(env):
+    # step 0: three short prompts in one ragged prefill (tcgen05 GEMM + prefill attention);
+    # step 1: the first 512 tokens of a 700-token prompt packed with three decode rows (515 tokens: the CTA-pair GEMM
+    #         with its split-K down_proj, the tcgen05 prefill attention and the decode attention in one step);
+    # step 2: the remaining 188 prompt tokens behind 512 cached ones + decode rows;
+    # step 3: four decode rows only (the weight-streaming GEMM);  step 4: the same once more.
+    steps = [[(0, 40), (1, 100), (2, 17)],
+             [(0, 1), (1, 1), (2, 1), (3, 512)],
+             [(0, 1), (1, 1), (2, 1), (3, 188)],
+             [(0, 1), (1, 1), (2, 1), (3, 1)],
+             [(0, 1), (1, 1), (2, 1), (3, 1)]]
+    run_schedule(env, LLAMA_CUT, steps)
+
+
+def test_qwen3_32b_cut_q8_qk_norm(env):
+    # 8 q heads per kv head, per-head q/k RMSNorm, eps 1e-6, standard RoPE at theta 1e6
+    steps = [[(0, 130), (1, 33)],
+             [(0, 1), (1, 1), (2, 160)],
+             [(0, 1), (1, 1), (2, 1)]]
+    run_schedule(env, QWEN_CUT, steps)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_config2_projection_shapes(env, n, k, bits):
+    """BASELINE configuration 2 at full size: codes uniform, scales |N(0,0.02)|/7.5, biases -8*scale + N(0,1e-3),
+    activations N(0,1) in bf16; f32 accumulation within max-abs 2e-3 of the oracle, bf16 output a rounding of such
+    a value."""
+    ctx, _, K, orc = env
+    rng = np.random.default_rng(100 + bits)
+    packed = rng.integers(0, 2**32, size=(n, k * bits // 32), dtype=np.uint32)
+    scales = H.f32_to_bf16_np(np.abs(rng.standard_normal((n, k // 64)).astype(np.float32) * 0.02) / 7.5)
+    biases = H.f32_to_bf16_np(-8.0 * H.bf16_to_f32_np(scales) + rng.standard_normal((n, k // 64)).astype(np.float32) * 1e-3)
+    dp, ds, db = ctx.buf(packed), ctx.buf(scales), ctx.buf(biases)
+    worst = {}
+    for m in (1, 8, 32, 128, 256):
+        x = H.f32_to_bf16_np(rng.standard_normal((m, k)).astype(np.float32))
+        dx = ctx.buf(x)
+        yb, yf = ctx.empty((m, n), np.uint16), ctx.empty((m, n), np.float32)
+        K.qmm(ctx, dx, dp, ds, db, m, n, k, bits, yb, None)
+        K.qmm(ctx, dx, dp, ds, db, m, n, k, bits, None, yf)
+        ctx.sync()
+        rf, _ = orc.qmm(x, packed, scales, biases, 64, bits)
+        worst[m] = float(np.abs(yf.download() - rf).max())
+        assert worst[m] <= 2e-3, (n, k, bits, m, worst[m])
+        assert H.close_bf16_out(yb.download(), rf)[0], (n, k, bits, m)
+        for b in (dx, yb, yf):
+            b.free()
+    for b in (dp, ds, db):
+        b.free()
+    print(f"[configuration 2] {n}x{k} Q{bits}: max-abs error of the f32 accumulation per token count {worst}")

@@ -142,3 +142,49 @@ def test_projection_and_reduction_fused(world, m, hidden, k_local, bits, push):
     for g in groups:
         g.free()
     ctx.close()
+
+
+def test_wait_on_a_missing_rank_runs_out_and_the_context_survives():
+    """Failure detection without a fault: rank 0 of a two-rank group reduces ALONE (nothing ever sets rank 1's flag),
+    with the wait limit lowered to 50 ms.  The kernel must return by itself, the context must report
+    B2_ERR_TIMEOUT, a reduction launched while the error is still pending must return at once, and the context
+    must still compute afterwards."""
+    import time
+
+    from mlx_llm_b200 import _lib, engine as eng, kernels as K
+
+    lib = _lib.load()
+    ctx = _lib.Context(0)
+    _lib.check(lib.b2_ctx_set_wait_limit_ms(ctx.h, 50))
+    with pytest.raises(_lib.B2Error):
+        _lib.check(lib.b2_ctx_set_wait_limit_ms(ctx.h, 0))
+    groups = [eng.TpGroup(ctx, None, r, 2) for r in range(2)]
+    for g in groups:
+        g.peer_alloc(64, 256)
+    eng.TpGroup.peer_attach_local(groups)
+    t0 = time.time()
+    groups[0].peer_reduce_residual(64)      # waits for rank 1, which never comes
+    ctx.timer_start()
+    groups[0].peer_reduce_residual(64)      # error word already raised: no second wait
+    second_ms = ctx.timer_stop_ms()
+    with pytest.raises(_lib.B2Error) as e:
+        ctx.sync()
+    waited = time.time() - t0
+    assert e.value.code == -9               # B2_ERR_TIMEOUT
+    assert 0.03 <= waited < 2.0, waited     # about the 50 ms limit, far from the 4 s default
+    assert second_ms < 20.0, second_ms
+    ctx.sync()                              # the error was reported once and cleared
+    # the context still works: a projection against the oracle
+    from oracle import oracle as orc
+
+    rng = np.random.default_rng(1)
+    m, n, k = 8, 256, 512
+    x = H.f32_to_bf16_np(rng.standard_normal((m, k)).astype(np.float32))
+    w = H.f32_to_bf16_np(rng.standard_normal((n, k)).astype(np.float32) * 0.05)
+    yf = ctx.empty((m, n), np.float32)
+    K.linear(ctx, ctx.buf(x), ctx.buf(w), m, n, k, None, yf)
+    ctx.sync()
+    assert np.abs(yf.download() - orc.linear(x, w)[0]).max() <= 2e-3
+    for g in groups:
+        g.free()
+    ctx.close()
