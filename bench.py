@@ -11,6 +11,10 @@ Prints ONE JSON line (rank 0).  Workloads:
                            independent replica per GPU, requests sharded id mod N, no collective.
   paged_attn_decode        BASELINE configuration 1: paged-attention decode microbenchmark
                            (64 sequences, 32 q / 8 kv heads, head_dim 128, page 16, ctx U[128,4096]).
+  qmm                      BASELINE configuration 2: MLX group-64 Q4 / Q8 dequant GEMV / GEMM on the four
+                           Llama-3-8B projection shapes at 1, 8, 32, 128 and 256 tokens.
+  decode_only              decode iterations without prefill (the weight-streaming regime).
+  qwen3_32b_q8_tp          BASELINE configuration 4: one Qwen3-32B-architecture Q8 model over N ranks.
 A "step" is one iteration of the serving loop (one ragged forward over one batch).  The engine is
 first rolled to its steady state (`ramp` iterations, untimed, all requests available at t = 0), then W
 warm-up and K timed iterations follow.  `value` = generated tokens / device time of the K forwards
@@ -88,22 +92,29 @@ class ClockSampler:
                     samples=len(sm))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures whose
-# summaries (with the commands) are under profiles/
-NCU_TRAFFIC = dict(
-    gemm_gate_up_launch=90.9e6,
-    gemm_note="gate+up projection launch of gemm_tc_pair_kernel<4,0> (N 28672, K 4096) at ~570 tokens in the 2-layer capture; "
-              "algorithmic 66.1 MB of packed weights + activations/outputs that mostly stay in L2",
-    attn_decode_config1_launch=578.4e6,
-    attn_note="paged_attn_decode_kernel<128> on the configuration-1 batch (algorithmic 565.0 MB)",
-)
+def ncu_traffic(key):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of a dominant kernel, read from profiles/ncu_traffic.json
+    (written beside the ncu summaries it is taken from, which give the capturing commands).  Returns (bytes, note)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            e = json.load(f)[key]
+        return float(e["bytes_per_launch"]), f"{e['kernel']}: {e['note']} (summary: profiles/{e['summary']})"
+    except (OSError, KeyError, ValueError):
+        return None, "no ncu capture recorded for this kernel"
+
+
+def host_threads():
+    """Threads the CPU legs really use: every core this process may run on, set explicitly."""
+    from oracle import oracle as orc
+
+    return orc.use_host_cores()
 
 
 # ------------------------------------------------------------------------------------------------
 # BASELINE configuration 3: Llama-3-8B-architecture Q4 continuous batching
 def continuous_setup(args, rank, world, local_rank):
     from mlx_llm_b200 import _lib, engine as eng, workloads as wl
-    from mlx_llm_b200.replica import shard_indices, weak_scaled_requests
+    from mlx_llm_b200.replica import replica_requests
 
     if args.workload == "qwen3_32b_q8_tp":
         return tp_setup(args, rank, world, local_rank)
@@ -111,11 +122,11 @@ def continuous_setup(args, rank, world, local_rank):
     ctx = _lib.Context(local_rank)
     cfg = eng.model_config(**shape, quant_bits=4, quant_group=64)
     model = eng.CausalLm.synthetic(ctx, cfg, seed=0)
-    # weak scaling: every replica serves its own `requests` requests (ids r, r+N, r+2N, ... of N*requests)
-    prompts, outs, arrival = weak_scaled_requests(args.requests, world, 50.0, seed=0, vocab=shape["vocab_size"],
-                                                  poisson=args.arrivals == "poisson")
-    idx = shard_indices(len(prompts), rank, world)
-    reqs = [eng.BatchRequest(prompts[i], int(outs[i]), arrival_s=float(arrival[i])) for i in idx]
+    # weak scaling: the job is N x `requests` requests, replica r serves the r-th block of them, and every block is
+    # the same seeded draw, so that all replicas do identical work and the per-GPU figures are comparable across N
+    prompts, outs, arrival = replica_requests(args.requests, rank, world, 50.0, seed=0, vocab=shape["vocab_size"],
+                                              poisson=args.arrivals == "poisson")
+    reqs = [eng.BatchRequest(p, int(o), arrival_s=float(a)) for p, o, a in zip(prompts, outs, arrival)]
     ccfg = eng.ContinuousConfig(max_batch=args.max_batch, block_size=16, exactness=eng.THROUGHPUT, prefill_chunk_tokens=args.chunk,
                                 max_pages=args.max_pages, max_blocks_per_seq=(8192 + 512) // 16 + 2)
     return ctx, model, reqs, ccfg, shape
@@ -180,7 +191,16 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     if args.profiler_range:
         ctx.profiler_range(True)
     t0 = time.perf_counter()
-    done, s1 = engine.step(args.steps)
+    seg_ms, prev, left = [], s0, args.steps   # exactly K iterations, read out in four consecutive parts
+    for part in range(4):
+        k = left // (4 - part)
+        left -= k
+        if k == 0:
+            continue
+        done, s1 = engine.step(k)
+        if s1["steps"] > prev["steps"]:
+            seg_ms.append((s1["device_ms"] - prev["device_ms"]) / (s1["steps"] - prev["steps"]))
+        prev = s1
     ctx.sync()
     wall_ms = (time.perf_counter() - t0) * 1e3
     if args.profiler_range:
@@ -206,6 +226,7 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     # replicas: tokens add up over ranks; tensor parallelism: every rank produced the SAME tokens, count them once
     all_gen, all_dev, all_wall = (gen if tp_mode else reduce_sum(gen)), reduce_max(dev_ms), reduce_max(wall_ms)
     peaks = measured_peaks()
+    traffic, traffic_note = (None, None) if tp_mode else ncu_traffic("gemm_gate_up")
     gemm_ms = prof["ms"]["gemm"]
     tfl = prof["gemm_flops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     total_prof_ms = sum(prof["ms"].values())
@@ -213,7 +234,8 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     out = dict(
         metric="continuous-batch decode tok/s, Qwen3-32B-arch Q8, tensor-parallel" if tp_mode else "continuous-batch decode tok/s, Llama-3-8B-arch Q4",
         value=all_gen / (all_dev * 1e-3), unit="tok/s", n_gpus=world,
-        steps=int(steps), warmup=warm, ms_per_step=all_dev / max(steps, 1), higher_is_better=True, scaling="strong" if tp_mode else "weak",
+        steps=int(steps), warmup=warm, ms_per_step=all_dev / max(steps, 1),
+        ms_per_step_by_quarter=[round(x, 4) for x in seg_ms], higher_is_better=True, scaling="strong" if tp_mode else "weak",
         vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload="qwen3_32b_q8_tp (BASELINE configuration 4)" if tp_mode else "llama3_8b_q4_continuous (BASELINE configuration 3)",
                     layers=shape["num_layers"], requests=len(reqs) if tp_mode else args.requests,
@@ -224,12 +246,11 @@ def run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_su
                                     "peer memory, pushed": "projection epilogues storing each column range into its owner's memory + one kernel (sum + residual add, stores to every rank)",
                                     "nccl": "NCCL all-reduce + residual-add kernel", "none": "nothing (one rank)"}[getattr(model._tp, "reduce_path", "none")]
                                  if tp_mode
-                                 else f"replica x{world}, requests sharded id mod N"),
+                                 else f"replica x{world}: {world} x {args.requests} requests, one block of {args.requests} per replica, no collective"),
                     l2="per-step working set (weights + KV) exceeds L2",
                     prefill_tokens_per_step=pre / max(steps, 1), generated_tokens_per_step=gen / max(steps, 1)),
         roofline=dict(bound="tensor", achieved=tfl, peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
-                      frac=tfl / peaks["bf16_tflops_sustained"], traffic=None if tp_mode else NCU_TRAFFIC["gemm_gate_up_launch"],
-                      traffic_note=None if tp_mode else NCU_TRAFFIC["gemm_note"], peak_source=peaks["source"] + " (sustained)",
+                      frac=tfl / peaks["bf16_tflops_sustained"], traffic=traffic, traffic_note=traffic_note, peak_source=peaks["source"] + " (sustained)",
                       kernel=("projection GEMMs (Q8 dequant fused) + bf16 lm_head" if tp_mode else "projection GEMMs (Q4 dequant fused) + bf16 lm_head"), launches_per_step=prof["launches"]["gemm"] / prof_steps,
                       ms_per_step=gemm_ms / prof_steps, share_of_step=gemm_ms / total_prof_ms if total_prof_ms else None,
                       algorithmic_flops_per_step=prof["gemm_flops"] / prof_steps),
@@ -253,6 +274,7 @@ def cpu_baseline_continuous(args, seconds=20.0):
     from mlx_llm_b200 import workloads as wl
     from oracle import oracle as orc
 
+    threads = host_threads()
     shape = dict(wl.LLAMA3_8B, num_layers=args.cpu_layers)
     m = orc.Model(layers=shape["num_layers"], hidden=shape["hidden_size"], heads=shape["num_heads"], kv_heads=shape["num_kv_heads"],
                   head_dim=shape["head_dim"], inter=shape["intermediate_size"], vocab=shape["vocab_size"], eps=1e-5, theta=500000.0,
@@ -268,7 +290,7 @@ def cpu_baseline_continuous(args, seconds=20.0):
     # head are counted once)
     full = dt * 32.0 / args.cpu_layers
     m.free()
-    return dict(value=gen / full, unit="tok/s", cores=os.cpu_count(), kind="port",
+    return dict(value=gen / full, unit="tok/s", cores=threads, kind="port",
                 sample=f"{len(prompts)} requests, prompts clipped to 64 tokens, 8 new tokens each, {args.cpu_layers} of 32 layers timed "
                        f"({dt:.1f} s) and scaled to 32 layers", measured_seconds=dt)
 
@@ -354,15 +376,158 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_su
         config=dict(workload="paged_attn_decode (BASELINE configuration 1): 64 seqs, 32q/8kv heads, hd 128, page 16, ctx U[128,4096]",
                     l2="flushed between timed iterations", parallelism=f"replica x{world}", chunk_tokens=args.chunk_tokens or 512),
         roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"],
-                      traffic=NCU_TRAFFIC["attn_decode_config1_launch"], traffic_note=NCU_TRAFFIC["attn_note"],
+                      traffic=ncu_traffic("paged_attn_decode_config1")[0], traffic_note=ncu_traffic("paged_attn_decode_config1")[1],
                       peak_source=peaks["source"], algorithmic_bytes=alg, kernel="paged_attn_decode_kernel<128> (+ work list, merge)"),
         e2e=dict(value=n * world / (t_e2e / args.steps * 1e-3), unit="tok/s", h2d_bytes_per_step=case["q"].nbytes,
                  d2h_bytes_per_step=case["q"].nbytes),
         gpu_launches=int(launches), clocks=clocks,
     )
-    if rank == 0:
+    if rank == 0 and world == 1 and args.cpu_baseline:
         out["cpu_baseline"] = cpu_baseline_paged_attn(case)
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# BASELINE configuration 2: group-64 affine Q4 / Q8 dequant GEMV / GEMM (QuantizedLinear::forward, quant.rs:56-70)
+QMM_SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]   # out x in
+QMM_TOKENS = [1, 8, 32, 128, 256]
+
+
+def qmm_case(n, k, bits, seed=0):
+    rng = np.random.default_rng(seed + 7 * bits + n + k)
+    packed = rng.integers(0, 2**32, size=(n, k * bits // 32), dtype=np.uint32)
+    from tests import helpers as H
+
+    scales = H.f32_to_bf16_np(np.abs(rng.standard_normal((n, k // 64)).astype(np.float32) * 0.02) / 7.5)
+    biases = H.f32_to_bf16_np(-8.0 * H.bf16_to_f32_np(scales) + rng.standard_normal((n, k // 64)).astype(np.float32) * 1e-3)
+    x = H.f32_to_bf16_np(rng.standard_normal((max(QMM_TOKENS), k)).astype(np.float32))
+    return packed, scales, biases, x
+
+
+def qmm_alg_bytes(n, k, bits, m):
+    return n * k * bits // 8 + n * (k // 64) * 4 + m * k * 2 + m * n * 2
+
+
+def run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
+    """One step = one pass over all 40 (shape, bits, tokens) cases, L2 flushed before every call, each call timed with
+    CUDA events on the launching stream.  The headline value is the weight-streaming rate of the small-token cases
+    (algorithmic bytes of all cases with <= 32 tokens / their summed time); every case is listed under `cases` with its
+    own GB/s (HBM bound) and TFLOP/s (tensor bound)."""
+    import ctypes as C
+
+    from mlx_llm_b200 import _lib, kernels
+
+    ctx = _lib.Context(local_rank)
+    lib = _lib.load()
+    peaks = measured_peaks()
+    cases = []
+    for bits in (4, 8):
+        for n, k in QMM_SHAPES:
+            packed, scales, biases, x = qmm_case(n, k, bits)
+            dev = dict(p=ctx.buf(packed), s=ctx.buf(scales), b=ctx.buf(biases), x=ctx.buf(x), y=ctx.empty((max(QMM_TOKENS), n), np.uint16))
+            hx, hy = C.c_void_p(), C.c_void_p()
+            _lib.check(lib.b2_host_alloc_pinned(C.c_size_t(x.nbytes), C.byref(hx)))
+            _lib.check(lib.b2_host_alloc_pinned(C.c_size_t(max(QMM_TOKENS) * n * 2), C.byref(hy)))
+            C.memmove(hx, x.ctypes.data, x.nbytes)
+            for m in QMM_TOKENS:
+                cases.append(dict(n=n, k=k, bits=bits, m=m, dev=dev, hx=hx, hy=hy, ms=0.0, e2e_ms=0.0))
+    run = lambda c: kernels.qmm(ctx, c["dev"]["x"], c["dev"]["p"], c["dev"]["s"], c["dev"]["b"], c["m"], c["n"], c["k"], c["bits"], c["dev"]["y"], None)
+    run_host = lambda c: kernels.qmm_host(ctx, c["hx"].value, c["dev"]["p"], c["dev"]["s"], c["dev"]["b"], c["m"], c["n"], c["k"], c["bits"], c["hy"].value)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        for c in cases:
+            run(c)
+            run_host(c)
+    ctx.sync()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = ctx.launch_count()
+    barrier()
+    for _ in range(args.steps):
+        for c in cases:
+            ctx.flush_l2()
+            ctx.timer_start()
+            run(c)
+            c["ms"] += ctx.timer_stop_ms()
+    ctx.sync()
+    launches = ctx.launch_count() - l0
+    barrier()
+    for _ in range(args.steps):
+        for c in cases:
+            ctx.flush_l2()
+            ctx.sync()
+            t0 = time.perf_counter()
+            run_host(c)
+            c["e2e_ms"] += (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop()
+    barrier()
+    rows, small_bytes, small_ms, small_e2e, small_tok, dom = [], 0.0, 0.0, 0.0, 0, None
+    for c in cases:
+        ms, e2e = c["ms"] / args.steps, c["e2e_ms"] / args.steps
+        alg = qmm_alg_bytes(c["n"], c["k"], c["bits"], c["m"])
+        gbs, tfl = alg / (ms * 1e-3) / 1e9, 2.0 * c["m"] * c["n"] * c["k"] / (ms * 1e-3) / 1e12
+        row = dict(out=c["n"], inp=c["k"], bits=c["bits"], tokens=c["m"], us=round(ms * 1e3, 2), gbs=round(gbs, 1), tflops=round(tfl, 2),
+                   frac_hbm=round(gbs / peaks["hbm_gbs"], 4), frac_tensor=round(tfl / peaks["bf16_tflops"], 4), e2e_us=round(e2e * 1e3, 2),
+                   algorithmic_bytes=alg)
+        rows.append(row)
+        if c["m"] <= 32:
+            small_bytes += alg
+            small_ms += ms
+            small_e2e += e2e
+            small_tok += c["m"]
+        if (c["n"], c["k"], c["bits"], c["m"]) == (14336, 4096, 4, 1):
+            dom = row
+    total_ms = reduce_max(sum(c["ms"] for c in cases) / args.steps)
+    gbs = small_bytes / (reduce_max(small_ms) * 1e-3) / 1e9
+    traffic, note = ncu_traffic("gemm_stream_gate_up")
+    out = dict(
+        metric="Q4/Q8 group-64 dequant GEMV weight-streaming GB/s (cases with <= 32 tokens)", value=gbs * world, unit="GB/s", n_gpus=world,
+        steps=args.steps, warmup=warm, ms_per_step=total_ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+        data="synthetic",
+        config=dict(workload="qmm (BASELINE configuration 2): out x in 4096x4096, 1024x4096, 14336x4096, 4096x14336; Q4 and Q8; 1, 8, 32, 128, 256 tokens",
+                    l2="flushed before every call", parallelism=f"replica x{world}"),
+        roofline=dict(bound="hbm", achieved=dom["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=dom["gbs"] / peaks["hbm_gbs"], traffic=traffic,
+                      traffic_note=note, peak_source=peaks["source"], kernel="gemm_stream_kernel, Q4 14336x4096 at 1 token",
+                      algorithmic_bytes=dom["algorithmic_bytes"], us_per_launch=dom["us"]),
+        cases=rows,
+        e2e=dict(value=small_bytes / (reduce_max(small_e2e) * 1e-3) / 1e9 * world, unit="GB/s",
+                 h2d_bytes_per_step=int(sum(c["m"] * c["k"] * 2 for c in cases)), d2h_bytes_per_step=int(sum(c["m"] * c["n"] * 2 for c in cases))),
+        gpu_launches=int(launches), clocks=clocks,
+    )
+    if rank == 0 and world == 1 and args.cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline_qmm()
+    return out
+
+
+def cpu_baseline_qmm(seconds=10.0):
+    """Oracle quantized matmul (dequantize on the fly, f32 accumulate, OpenMP over output rows) on the cases with
+    <= 32 tokens of two shapes, repeated for about ten seconds."""
+    from oracle import oracle as orc
+
+    threads = host_threads()
+    todo = [(n, k, bits, m) for bits in (4, 8) for n, k in QMM_SHAPES[:2] for m in QMM_TOKENS[:3]]
+    data = {(n, k, bits): qmm_case(n, k, bits) for n, k, bits, _ in todo}
+    t0, reps, nbytes = time.perf_counter(), 0, 0
+    while time.perf_counter() - t0 < seconds:
+        for n, k, bits, m in todo:
+            packed, scales, biases, x = data[(n, k, bits)]
+            orc.qmm(x[:m], packed, scales, biases, 64, bits)
+            nbytes += qmm_alg_bytes(n, k, bits, m)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return dict(value=nbytes / dt / 1e9, unit="GB/s", cores=threads, kind="port",
+                sample=f"Q4 and Q8, shapes 4096x4096 and 1024x4096, 1 / 8 / 32 tokens, {reps} passes in {dt:.1f} s")
+
+
+def run_reference_qmm(args, world, threads):
+    r = [cpu_baseline_qmm(seconds=4.0) for _ in range(max(1, min(args.steps, 3)))]
+    v = float(np.mean([x["value"] for x in r]))
+    return dict(impl="reference", metric="Q4/Q8 group-64 dequant GEMV weight-streaming GB/s (cases with <= 32 tokens)", value=v, unit="GB/s",
+                n_gpus=world, steps=len(r), warmup=0, ms_per_step=4000.0, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                data="synthetic", config=dict(workload="qmm (BASELINE configuration 2)", parallelism="host cores (OpenMP)",
+                                              note="CPU restatement of the reference path; the reference itself (Rust + MLX/Metal) is unavailable on this box"),
+                cpu_baseline=dict(value=v, unit="GB/s", cores=threads, kind="port", sample=r[0]["sample"]),
+                e2e=dict(value=v, unit="GB/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -434,6 +599,7 @@ def cpu_baseline_paged_attn(case, sample=16, seconds=5.0):
     sequences of the same batch."""
     from oracle import oracle as orc
 
+    threads = host_threads()
     n = min(sample, case["ctx_lens"].size)
     f = lambda k: orc.paged_attention(case["q"][:k], case["kpool"], case["vpool"], case["block_tables"][:k], None, case["ctx_lens"][:k],
                                       case["scale"], fast_decode=True)
@@ -443,7 +609,7 @@ def cpu_baseline_paged_attn(case, sample=16, seconds=5.0):
         f(n)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
-    return dict(value=n / dt, unit="tok/s", cores=os.cpu_count(), kind="port",
+    return dict(value=n / dt, unit="tok/s", cores=threads, kind="port",
                 sample=f"first {n} of {case['ctx_lens'].size} sequences of the same batch, {reps} repetitions")
 
 
@@ -453,6 +619,9 @@ def run_reference(args, rank, world):
     only).  Every step is one bounded sample of the same workload."""
     if rank != 0:
         return None
+    threads = host_threads()
+    if args.workload == "qmm":
+        return run_reference_qmm(args, world, threads)
     if args.workload == "paged_attn_decode":
         case = config1_case()
         from oracle import oracle as orc
@@ -486,7 +655,7 @@ def run_reference(args, rank, world):
                 ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
                 config=dict(workload=wl_name, parallelism="host cores (OpenMP)",
                             note="CPU restatement of the reference path; the reference itself (Rust + MLX/Metal) is unavailable on this box"),
-                cpu_baseline=dict(value=v, unit="tok/s", cores=os.cpu_count(), kind="port", sample=sample),
+                cpu_baseline=dict(value=v, unit="tok/s", cores=threads, kind="port", sample=sample),
                 e2e=dict(value=v, unit="tok/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
 
 
@@ -496,7 +665,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode", "qwen3_32b_q8_tp", "decode_only"])
+    ap.add_argument("--workload", default="llama3_8b_q4_continuous", choices=["llama3_8b_q4_continuous", "paged_attn_decode", "qwen3_32b_q8_tp", "decode_only", "qmm"])
     ap.add_argument("--chunk-tokens", dest="chunk_tokens", type=int, default=0, help="paged_attn_decode: split-K chunk")
     ap.add_argument("--requests", type=int, default=2048)
     ap.add_argument("--arrivals", default="saturated", choices=["saturated", "poisson"])
@@ -532,11 +701,13 @@ def main():
 
     if args.workload == "paged_attn_decode":
         out = run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
+    elif args.workload == "qmm":
+        out = run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
     elif args.workload == "decode_only":
         out = run_decode_only(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
     else:
         out = run_continuous(args, rank, world, local_rank, barrier, reduce_max, reduce_sum)
-        if rank == 0 and args.cpu_baseline:
+        if rank == 0 and world == 1 and args.cpu_baseline:   # a reported baseline, timed at N = 1 only
             out["cpu_baseline"] = cpu_baseline_continuous(args)
     if rank == 0:
         print(json.dumps(out), flush=True)

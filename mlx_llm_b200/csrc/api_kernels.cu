@@ -87,6 +87,23 @@ int32_t b2_qmm(b2_ctx* ctx, const uint16_t* x_dev, const uint32_t* packed_dev, c
     return gemm_both(ctx, p, y_bf16_dev, y_f32_dev);
 }
 
+// The same with HOST activations and a host result (pinned or pageable): x in, kernel, y out, then a stream sync.
+int32_t b2_qmm_host(b2_ctx* ctx, const uint16_t* x_host, const uint32_t* packed_dev, const uint16_t* scales_dev, const uint16_t* biases_dev,
+                    int32_t m, int32_t out_dim, int32_t in_dim, int32_t group, int32_t bits, uint16_t* y_bf16_host) {
+    B2_REQUIRE(ctx && x_host && y_bf16_host, B2_ERR_MSG, "b2_qmm_host: null argument");
+    B2_REQUIRE(m >= 0 && out_dim > 0 && in_dim > 0, B2_ERR_MSG, "b2_qmm_host: bad shape");
+    const size_t xb = ((size_t)m * in_dim * 2 + 255) & ~(size_t)255, yb = (size_t)m * out_dim * 2;
+    void* stage = nullptr;
+    B2_CHECK(b2_ctx_stage(ctx, xb + yb, &stage));
+    uint16_t* xd = reinterpret_cast<uint16_t*>(stage);
+    uint16_t* yd = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(stage) + xb);
+    B2_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)m * in_dim * 2, cudaMemcpyHostToDevice, ctx->stream));
+    B2_CHECK(b2_qmm(ctx, xd, packed_dev, scales_dev, biases_dev, m, out_dim, in_dim, group, bits, yd, nullptr));
+    B2_CUDA(cudaMemcpyAsync(y_bf16_host, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    return B2_OK;
+}
+
 int32_t b2_linear(b2_ctx* ctx, const uint16_t* x_dev, const uint16_t* w_dev, int32_t m, int32_t out_dim, int32_t in_dim,
                   uint16_t* y_bf16_dev, float* y_f32_dev) {
     B2_REQUIRE(ctx && x_dev && w_dev, B2_ERR_MSG, "b2_linear: null argument");

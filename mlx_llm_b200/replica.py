@@ -1,8 +1,9 @@
 """Replica data-parallelism: one process per GPU, independent request shards, no data-path collective.
 
-The continuous-batching path shards by REQUEST: replica r of N serves requests r, r+N, r+2N, ... with its
-own weights, page pool and scheduler, exactly as N independent instances of the reference's
-`generate_continuous` (src/decode/continuous.rs:186-414) would.  The only cross-rank traffic is
+The continuous-batching path shards by REQUEST: every replica serves its own requests with its own weights,
+page pool and scheduler, exactly as N independent instances of the reference's `generate_continuous`
+(src/decode/continuous.rs:117-229) would.  A request list is cut id mod N (shard_indices); the benchmark gives
+every replica the same seeded block of requests (replica_requests) so that per-GPU work does not depend on N.  The only cross-rank traffic is
 measurement: a barrier on both sides of a timed region and a max / sum of a few scalars.  The process
 group is NCCL when the ranks own GPUs and gloo otherwise (CPU tests of this host logic).
 """
@@ -91,3 +92,15 @@ def weak_scaled_requests(requests_per_replica, world, rate_per_replica, **kw):
     from . import workloads as wl
 
     return wl.serving_requests(n=requests_per_replica * world, rate=rate_per_replica * world, **kw)
+
+
+def replica_requests(requests_per_replica, rank, world, rate_per_replica, **kw):
+    """Weak scaling with identical work per replica: the N-replica job is N blocks of `requests_per_replica`
+    requests, replica r serves block r, and every block is the same seeded draw (same prompts, output budgets and
+    arrival times).  Each replica therefore repeats the single-GPU workload exactly, and tokens per iteration do
+    not drift with N.  Returns (prompts, max_new, arrival_s) of replica `rank`."""
+    from . import workloads as wl
+
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of {world}")
+    return wl.serving_requests(n=requests_per_replica, rate=rate_per_replica, **kw)

@@ -37,11 +37,6 @@ def long_context_requests(n=512, seed=0, vocab=151936, min_prompt=1024, max_prom
     return prompts, np.full(n, max_new, np.int64), np.zeros(n)
 
 
-def shard(items, rank, world):
-    """Replica sharding: request id mod world (independent units, no collective)."""
-    return [x for i, x in enumerate(items) if i % world == rank]
-
-
 def projection_params(cfg):
     """Weights every token is multiplied with in the projections (per token: 2 flops each)."""
     h, qd, kvd, i = cfg["hidden_size"], cfg["num_heads"] * cfg["head_dim"], cfg["num_kv_heads"] * cfg["head_dim"], cfg["intermediate_size"]

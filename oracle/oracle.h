@@ -18,7 +18,11 @@ typedef struct {
     int32_t rope_kind; /* 0 standard, 1 llama3 */
     float rope_factor, rope_low, rope_high, rope_orig;
     int32_t qk_norm, quant_bits, group, f32_mode;
+    int32_t sum_order; /* 0: index order; 1: another equally valid f32 summation order (sizes the rounding noise) */
 } orc_model_cfg;
+
+int orc_max_threads(void);
+void orc_set_threads(int n);
 
 uint64_t orc_splitmix64_next(uint64_t* state);
 float orc_splitmix64_next_f32(uint64_t* state);

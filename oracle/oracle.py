@@ -36,6 +36,7 @@ class ModelCfg(C.Structure):
         ("eps", C.c_float), ("theta", C.c_float), ("rope_kind", C.c_int32),
         ("rope_factor", C.c_float), ("rope_low", C.c_float), ("rope_high", C.c_float), ("rope_orig", C.c_float),
         ("qk_norm", C.c_int32), ("quant_bits", C.c_int32), ("group", C.c_int32), ("f32_mode", C.c_int32),
+        ("sum_order", C.c_int32),
     ]
 
 
@@ -58,6 +59,21 @@ def lib():
         _lib.orc_cache_gather.restype = C.c_int64
         _lib.orc_cache_offset.restype = C.c_int32
     return _lib
+
+
+def use_host_cores():
+    """Give the OpenMP loops every core this process may run on (launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1 to their children) and return the thread count they will really use."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().orc_set_threads(int(n))
+    return int(lib().orc_max_threads())
+
+
+def threads():
+    return int(lib().orc_max_threads())
 
 
 def _p(a, t):

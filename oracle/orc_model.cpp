@@ -19,6 +19,9 @@ namespace orc {
 static inline float R(const ModelCfg& c, float x) { return c.f32_mode ? x : rbf(x); }
 
 // y[m, out] = x[m, in] @ W^T, f32 accumulate in index order; rounded per mode.
+// With cfg.sum_order == 1 every dot product is formed as four sums over the quarters of the input dimension, added
+// as (s0 + s1) + (s2 + s3): a second, equally faithful f32 order.  The distance between the two orders' logits is
+// the rounding noise any two correct bf16 implementations show, which sizes the end-to-end parity gates.
 static void linear(const ModelCfg& c, const Mat& w, const std::vector<float>& x, int m, std::vector<float>& y,
                    std::vector<float>* unrounded = nullptr) {
     int in = w.in, out = w.out;
@@ -26,7 +29,21 @@ static void linear(const ModelCfg& c, const Mat& w, const std::vector<float>& x,
     if (unrounded) unrounded->assign((size_t)m * out, 0.f);
     int per = w.bits ? 32 / w.bits : 1;
     uint32_t mask = w.bits ? (1u << w.bits) - 1 : 0;
-    const RowsT16 xt(x.data(), m, in);
+    const int parts = (c.sum_order == 1 && in >= 4) ? 4 : 1;
+    std::vector<int> cut(parts + 1);
+    for (int q = 0; q <= parts; q++) cut[q] = (int)((long)in * q / parts);
+    std::vector<RowsT16> xt;
+    xt.reserve(parts);
+    for (int q = 0; q < parts; q++) {
+        if (parts == 1) {
+            xt.emplace_back(x.data(), m, in);
+        } else {
+            std::vector<float> sub((size_t)m * (cut[q + 1] - cut[q]));
+            for (int i = 0; i < m; i++)
+                std::memcpy(sub.data() + (size_t)i * (cut[q + 1] - cut[q]), x.data() + (size_t)i * in + cut[q], sizeof(float) * (cut[q + 1] - cut[q]));
+            xt.emplace_back(sub.data(), m, cut[q + 1] - cut[q]);
+        }
+    }
 #pragma omp parallel for schedule(dynamic, 32)
     for (int j = 0; j < out; j++) {
         std::vector<float> wf(in);
@@ -43,7 +60,16 @@ static void linear(const ModelCfg& c, const Mat& w, const std::vector<float>& x,
             for (int d = 0; d < in; d++) wf[d] = bf2f(w.w[(size_t)j * in + d]);
         }
         std::vector<float> acc(m);
-        dots_in_order(xt, wf.data(), acc.data());
+        if (parts == 1) {
+            dots_in_order(xt[0], wf.data(), acc.data());
+        } else {
+            std::vector<float> s[4];
+            for (int q = 0; q < 4; q++) {
+                s[q].resize(m);
+                dots_in_order(xt[q], wf.data() + cut[q], s[q].data());
+            }
+            for (int i = 0; i < m; i++) acc[i] = (s[0][i] + s[1][i]) + (s[2][i] + s[3][i]);
+        }
         for (int i = 0; i < m; i++) {
             if (unrounded) (*unrounded)[(size_t)i * out + j] = acc[i];
             y[(size_t)i * out + j] = R(c, acc[i]);
@@ -237,6 +263,7 @@ static ModelCfg cfg_from_c(const orc_model_cfg* c) {
     k.inter = c->inter; k.vocab = c->vocab; k.eps = c->eps; k.theta = c->theta; k.rope_kind = c->rope_kind;
     k.rope_factor = c->rope_factor; k.rope_low = c->rope_low; k.rope_high = c->rope_high; k.rope_orig = c->rope_orig;
     k.qk_norm = c->qk_norm; k.quant_bits = c->quant_bits; k.group = c->group ? c->group : 64; k.f32_mode = c->f32_mode;
+    k.sum_order = c->sum_order;
     return k;
 }
 

@@ -20,6 +20,7 @@ struct ModelCfg {
     int quant_bits = 0;  // 0 dense, 4, 8
     int group = 64;
     int f32_mode = 0;    // 1: no bf16 rounding anywhere (weights f32)
+    int sum_order = 0;   // projections: 0 = one accumulator in index order; 1 = four quarter sums, (s0+s1)+(s2+s3)
 };
 
 // A projection / dense matrix [out, in].

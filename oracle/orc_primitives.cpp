@@ -1,5 +1,7 @@
 // CPU oracle (test infrastructure): leaf arithmetic of the decode path.
 // Each function names the reference code it restates (paths inside SceneWorks/mlx-llm).
+#include <omp.h>
+
 #include "oracle.h"
 #include "orc_common.h"
 
@@ -425,3 +427,10 @@ void orc_synth_dense(uint64_t seed, int64_t n, float std_, uint16_t* out) {
 }
 
 }  // extern "C"
+
+// Threads the OpenMP loops above will use, and a way to set them: a launcher may export OMP_NUM_THREADS=1 to its
+// children, so the timed CPU legs set the count themselves and report what they really got.
+extern "C" int orc_max_threads(void) { return omp_get_max_threads(); }
+extern "C" void orc_set_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}

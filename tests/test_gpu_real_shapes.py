@@ -13,10 +13,13 @@ full models while the CPU oracle still finishes in seconds:
 Both sides generate the same weights from the counter-based recipe (no file travels).
 
 Gates.  Matmuls: the unrounded f32 accumulation within max-abs 2e-3 of the oracle.  Whole-decoder logits are bf16
-numbers behind dozens of bf16 roundings; the gate is the one configuration 0 uses (rms <= 2e-3, worst <= 1e-2 on
-logits whose rms is 0.32) scaled by the logits' rms, i.e. rms error <= 0.625 % and worst error <= 3.1 % of the
-logits' rms.  K/V pages: layer 0 sees identical inputs (values bit-exact, rotated keys within one bf16 ulp of the
-projection's rounding); layer 1 inherits layer 0's roundings."""
+numbers behind dozens of bf16 roundings, each of which may fall the other way when an f32 sum is formed in another
+order.  That noise is measured, not guessed: the oracle runs the schedule a second time with every projection summed
+in another, equally valid f32 order (four quarter sums), and the distance between its two runs is what two correct
+implementations show on this shape.  The engine must be as close to the oracle as that: error rms and worst entry
+within twice the oracle's own order-to-order distance (and never held to less than configuration 0's gate, rms
+2e-3 / worst 1e-2 on logits of rms 0.32, scaled by the logits' rms).  K/V pages: layer 0 sees identical inputs (values
+within one bf16 ulp on isolated elements); layer 1 inherits layer 0's roundings."""
 import numpy as np
 import pytest
 
@@ -42,12 +45,11 @@ def env():
     ctx.close()
 
 
-def scaled_logits_gate(got_bf16, ref_f32):
-    got = H.bf16_to_f32_np(got_bf16)
-    err = got - ref_f32
+def rel_err(got_f32, ref_f32):
+    """(rms, worst) of got - ref relative to the rms of ref."""
+    err = got_f32 - ref_f32
     scale = float(np.sqrt(np.mean(ref_f32 * ref_f32)))
-    rms, worst = float(np.sqrt(np.mean(err * err))) / scale, float(np.abs(err).max()) / scale
-    return bool(np.isfinite(got).all() and rms <= 2e-3 / 0.32 and worst <= 1e-2 / 0.32), rms, worst
+    return float(np.sqrt(np.mean(err * err))) / scale, float(np.abs(err).max()) / scale
 
 
 def run_schedule(env, cfg, steps, seed=0):
@@ -57,6 +59,8 @@ def run_schedule(env, cfg, steps, seed=0):
     model = eng.CausalLm.synthetic(ctx, H.engine_config(eng, cfg, quant_bits=cfg["quant_bits"]), seed=seed)
     omodel = orc.Model(**cfg)
     omodel.fill_synthetic(seed)
+    omodel_b = orc.Model(**dict(cfg, sum_order=1))   # the same weights, projections summed in another f32 order
+    omodel_b.fill_synthetic(seed)
     n_seq = 1 + max(s for st in steps for s, _ in st)
     total = [sum(n for st in steps for s, n in st if s == i) for i in range(n_seq)]
     rng = np.random.default_rng(11)
@@ -64,13 +68,20 @@ def run_schedule(env, cfg, steps, seed=0):
     pool = eng.BlockPool(ctx, model, 16, sum((t + 15) // 16 + 1 for t in total), n_seq, max((t + 15) // 16 + 1 for t in total))
     caches = [eng.PagedKvCache(pool) for _ in range(n_seq)]
     ocs = [orc.Cache(cfg["layers"], block_size=16) for _ in range(n_seq)]
+    ocs_b = [orc.Cache(cfg["layers"], block_size=16) for _ in range(n_seq)]
     report = []
     for si, st in enumerate(steps):
         feed = [(toks[s][caches[s].offset():caches[s].offset() + n], s) for s, n in st]
         launches0 = ctx.launch_count()
         logits, am = model.step([(ids, caches[s]) for ids, s in feed])
-        _, ref_f32 = omodel.forward([(ids, ocs[s], ocs[s].offset()) for ids, s in feed])
-        ok, rms, worst = scaled_logits_gate(logits, ref_f32)
+        ref_bf, ref_f32 = omodel.forward([(ids, ocs[s], ocs[s].offset()) for ids, s in feed])
+        refb_bf, _ = omodel_b.forward([(ids, ocs_b[s], ocs_b[s].offset()) for ids, s in feed])
+        got = H.bf16_to_f32_np(logits)
+        assert np.isfinite(got).all()
+        rms, worst = rel_err(got, ref_f32)
+        noise_rms, noise_worst = rel_err(refb_bf, ref_f32)   # bf16 logits of the second order against the same reference
+        gate_rms, gate_worst = max(2e-3 / 0.32, 2 * noise_rms), max(1e-2 / 0.32, 2 * noise_worst)
+        ok = rms <= gate_rms and worst <= gate_worst
         # greedy choice: equal wherever the oracle's own top-2 margin exceeds what the gate can resolve
         scale = float(np.sqrt(np.mean(ref_f32 * ref_f32)))
         agree = 0
@@ -80,33 +91,36 @@ def run_schedule(env, cfg, steps, seed=0):
             if int(am[r]) == int(order[0]):
                 agree += 1
             else:
-                assert margin <= 2 * 1e-2 / 0.32 * scale, f"step {si} row {r}: argmax {int(am[r])} vs {int(order[0])} at margin {margin}"
-        report.append((si, sum(n for _, n in st), ctx.launch_count() - launches0, rms, worst, agree, len(st)))
-        assert ok, f"step {si} ({st}): relative rms {rms:.3e}, worst {worst:.3e}"
-    print(f"[{cfg['hidden']}-wide cut] (step, tokens, launches, rel rms, rel worst, argmax agree, rows): {report}")
+                assert margin <= 2 * gate_worst * scale, f"step {si} row {r}: argmax {int(am[r])} vs {int(order[0])} at margin {margin}"
+        report.append((si, sum(n for _, n in st), ctx.launch_count() - launches0, f"{rms:.2e}/{noise_rms:.2e}", f"{worst:.2e}/{noise_worst:.2e}",
+                       agree, len(st)))
+        assert ok, (f"step {si} ({st}): relative rms {rms:.3e} (oracle order-to-order {noise_rms:.3e}), worst {worst:.3e} "
+                    f"(order-to-order {noise_worst:.3e})")
+    print(f"[{cfg['hidden']}-wide cut] (step, tokens, launches, rel rms engine/oracle-orders, rel worst engine/oracle-orders, "
+          f"argmax agree, rows): {report}")
     hkv, hd = cfg["kv_heads"], cfg["head_dim"]
-    for c, oc in zip(caches, ocs):
+    for c, oc, ob in zip(caches, ocs, ocs_b):
         assert c.offset() == oc.offset()
         for layer in range(cfg["layers"]):
             k, v = c.gather(layer, hkv, hd)
-            ok_, ov_ = oc.gather(layer)
-            ok_ = ok_.reshape(-1, hkv, hd).transpose(1, 0, 2)
-            ov_ = ov_.reshape(-1, hkv, hd).transpose(1, 0, 2)
+            ref_kv = [a.reshape(-1, hkv, hd).transpose(1, 0, 2) for a in oc.gather(layer)]
+            alt_kv = [a.reshape(-1, hkv, hd).transpose(1, 0, 2) for a in ob.gather(layer)]
             if layer == 0:
                 # identical inputs: the only freedom is the f32 summation order inside the projection (and the
                 # q/k norm), i.e. isolated one-ulp roundings
-                assert H.bf16_ulp_diff(v, ov_).max() <= 1 and (v != ov_).mean() < 0.02
-                assert (k != ok_).mean() < 0.1
-            for got_, ref_ in ((k, ok_), (v, ov_)):
-                g32, r32 = H.bf16_to_f32_np(got_), H.bf16_to_f32_np(ref_)
-                err = np.abs(g32 - r32)
-                s = float(np.sqrt(np.mean(r32 * r32)))
-                assert np.sqrt(np.mean(err * err)) <= 2e-3 / 0.32 * s and err.max() <= 2e-2 / 0.32 * s, (layer, s, err.max())
+                assert H.bf16_ulp_diff(v, ref_kv[1]).max() <= 1 and (v != ref_kv[1]).mean() < 0.02
+                assert (k != ref_kv[0]).mean() < 0.1
+            for got_, ref_, alt_ in zip((k, v), ref_kv, alt_kv):
+                r32 = H.bf16_to_f32_np(ref_)
+                rms, worst = rel_err(H.bf16_to_f32_np(got_), r32)
+                n_rms, n_worst = rel_err(H.bf16_to_f32_np(alt_), r32)
+                assert rms <= max(2e-3 / 0.32, 2 * n_rms) and worst <= max(2e-2 / 0.32, 2 * n_worst), (layer, rms, n_rms, worst, n_worst)
     for c in caches:
         c.free()
     pool.free()
     model.free()
     omodel.free()
+    omodel_b.free()
 
 
 def test_llama3_8b_cut_q4_chunked_prefill_with_decode_rows(env):

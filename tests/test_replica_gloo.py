@@ -78,4 +78,22 @@ def test_single_replica_needs_no_process_group():
     p4, o4, a4 = replica.weak_scaled_requests(32, 4, 50.0, seed=0, vocab=100, max_prompt=32)
     assert len(p1) == 32 and len(p4) == 128
     assert np.all(np.diff(a4) >= 0) and a4[-1] / 128 < a1[-1] / 32 * 0.6
+    # the benchmark's weak scaling: every replica gets the same seeded block, whatever N
+    blocks = [replica.replica_requests(16, r, 4, 50.0, seed=0, vocab=100, max_prompt=32) for r in range(4)]
+    one = replica.replica_requests(16, 0, 1, 50.0, seed=0, vocab=100, max_prompt=32)
+    for pr, out, arr in blocks:
+        assert all(np.array_equal(a, b) for a, b in zip(pr, one[0])) and np.array_equal(out, one[1]) and np.array_equal(arr, one[2])
+    with pytest.raises(ValueError):
+        replica.replica_requests(16, 4, 4, 50.0)
     g.close()
+
+
+def test_cpu_legs_take_every_core_they_may_use():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its children; the timed CPU legs must not inherit it."""
+    import subprocess
+
+    code = ("import os, sys; sys.path.insert(0, %r); from oracle import oracle as orc; "
+            "print(orc.threads(), orc.use_host_cores(), len(os.sched_getaffinity(0)))" % ROOT)
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, OMP_NUM_THREADS="1"), capture_output=True, text=True, check=True)
+    before, after, cores = (int(x) for x in out.stdout.split())
+    assert before == 1 and after == cores
