@@ -346,6 +346,13 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_su
     barrier()
     launches = ctx.launch_count() - l0
     t_dev = reduce_max(t_dev)
+    # The same K iterations back to back without the flush: every iteration streams 565 MB out of a 1.1 GB pool, more than
+    # four times L2, so nothing of it survives from one iteration to the next; the difference to the flushed figure is what
+    # the write-backs of the flush buffer's dirty lines cost the kernel that follows it.
+    ctx.timer_start()
+    for _ in range(args.steps):
+        call()
+    t_unflushed = reduce_max(ctx.timer_stop_ms())
     hq, ho = C.c_void_p(), C.c_void_p()
     lib = _lib.load()
     _lib.check(lib.b2_host_alloc_pinned(C.c_size_t(case["q"].nbytes), C.byref(hq)))
@@ -377,7 +384,10 @@ def run_paged_attn(args, rank, world, local_rank, barrier, reduce_max, reduce_su
                     l2="flushed between timed iterations", parallelism=f"replica x{world}", chunk_tokens=args.chunk_tokens or 512),
         roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"],
                       traffic=ncu_traffic("paged_attn_decode_config1")[0], traffic_note=ncu_traffic("paged_attn_decode_config1")[1],
-                      peak_source=peaks["source"], algorithmic_bytes=alg, kernel="paged_attn_decode_kernel<128> (+ work list, merge)"),
+                      peak_source=peaks["source"], algorithmic_bytes=alg, kernel="paged_attn_decode_kernel<128> (work list and merge inside: one launch)",
+                      unflushed=dict(ms_per_step=t_unflushed / args.steps, achieved=alg / (t_unflushed / args.steps * 1e-3) / 1e9,
+                                     frac=alg / (t_unflushed / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                     note="the same iterations back to back, no flush: the inputs (565 MB of a 1.1 GB pool per iteration) exceed L2")),
         e2e=dict(value=n * world / (t_e2e / args.steps * 1e-3), unit="tok/s", h2d_bytes_per_step=case["q"].nbytes,
                  d2h_bytes_per_step=case["q"].nbytes),
         gpu_launches=int(launches), clocks=clocks,
@@ -421,8 +431,11 @@ def run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
     lib = _lib.load()
     peaks = measured_peaks()
     cases = []
+    only = [tuple(int(v) for v in item.split("x")) for item in args.qmm_only.split(",") if item]   # e.g. "14336x4096x4x1"
     for bits in (4, 8):
         for n, k in QMM_SHAPES:
+            if only and not any(o[:3] == (n, k, bits) for o in only):
+                continue
             packed, scales, biases, x = qmm_case(n, k, bits)
             dev = dict(p=ctx.buf(packed), s=ctx.buf(scales), b=ctx.buf(biases), x=ctx.buf(x), y=ctx.empty((max(QMM_TOKENS), n), np.uint16))
             hx, hy = C.c_void_p(), C.c_void_p()
@@ -430,6 +443,8 @@ def run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
             _lib.check(lib.b2_host_alloc_pinned(C.c_size_t(max(QMM_TOKENS) * n * 2), C.byref(hy)))
             C.memmove(hx, x.ctypes.data, x.nbytes)
             for m in QMM_TOKENS:
+                if only and (n, k, bits, m) not in only:
+                    continue
                 cases.append(dict(n=n, k=k, bits=bits, m=m, dev=dev, hx=hx, hy=hy, ms=0.0, e2e_ms=0.0))
     run = lambda c: kernels.qmm(ctx, c["dev"]["x"], c["dev"]["p"], c["dev"]["s"], c["dev"]["b"], c["m"], c["n"], c["k"], c["bits"], c["dev"]["y"], None)
     run_host = lambda c: kernels.qmm_host(ctx, c["hx"].value, c["dev"]["p"], c["dev"]["s"], c["dev"]["b"], c["m"], c["n"], c["k"], c["bits"], c["hy"].value)
@@ -443,6 +458,8 @@ def run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
     sampler.start()
     l0 = ctx.launch_count()
     barrier()
+    if args.profiler_range:
+        ctx.profiler_range(True)
     for _ in range(args.steps):
         for c in cases:
             ctx.flush_l2()
@@ -450,6 +467,8 @@ def run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
             run(c)
             c["ms"] += ctx.timer_stop_ms()
     ctx.sync()
+    if args.profiler_range:
+        ctx.profiler_range(False)
     launches = ctx.launch_count() - l0
     barrier()
     for _ in range(args.steps):
@@ -475,7 +494,7 @@ def run_qmm(args, rank, world, local_rank, barrier, reduce_max, reduce_sum):
             small_ms += ms
             small_e2e += e2e
             small_tok += c["m"]
-        if (c["n"], c["k"], c["bits"], c["m"]) == (14336, 4096, 4, 1):
+        if (c["n"], c["k"], c["bits"], c["m"]) == (14336, 4096, 4, 1) or dom is None:
             dom = row
     total_ms = reduce_max(sum(c["ms"] for c in cases) / args.steps)
     gbs = small_bytes / (reduce_max(small_ms) * 1e-3) / 1e9
@@ -681,6 +700,7 @@ def main():
                     help="qwen3_32b_q8_tp: the reduction after o_proj / down_proj (peer falls back to nccl when a region cannot be mapped)")
     ap.add_argument("--profiler-range", dest="profiler_range", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
+    ap.add_argument("--qmm-only", dest="qmm_only", default="", help="qmm: comma-separated OUTxINxBITSxTOKENS cases to run (profiling); not a valid bench line")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
 

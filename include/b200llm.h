@@ -45,7 +45,7 @@ int32_t b2_version(void);
 int32_t b2_ctx_create(int32_t device, b2_ctx** out);
 int32_t b2_ctx_free(b2_ctx* ctx);
 int32_t b2_ctx_sync(b2_ctx* ctx);   /* also reports B2_ERR_TIMEOUT raised by a bounded device-side wait */
-/* Projection path: 1 = tcgen05 / TMEM kernel for steps with more than 64 tokens (default), 0 = the
+/* Projection path: 1 = tcgen05 / TMEM kernel for steps with more than 32 tokens (default), 0 = the
  * warp-level mma.sync kernel for every size (kept for comparison). */
 int32_t b2_ctx_set_tensor_path(b2_ctx* ctx, int32_t use_tcgen05);
 /* Limit, in milliseconds, of every device-side wait on ANOTHER rank (the flags of the peer-memory reduction);
@@ -107,9 +107,10 @@ int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host, const uin
  * without synchronising; chunk_tokens == 0 means 512.
  * The split-K scratch is a fixed 16 MiB array that lives in the library's device image, one copy per GPU.
  * A batch whose scratch need,
- *     ceil(max_blocks*page_size / chunk_tokens) * num_seqs * (hq*(head_dim+2)*4 + 8) + (num_seqs+2)*4  bytes,
- * exceeds 16 MiB is rejected with B2_ERR_MSG and a text that names both sizes; nothing is launched then.
- * (Llama-3-8B shapes, 16 K-token tables, chunk 512: up to 31 sequences; chunk 2048: up to 125.)
+ *     65536 + ceil(max_blocks*page_size / chunk_tokens) * num_seqs * hq*(head_dim+2)*4  bytes,
+ * exceeds 16 MiB, or that has more than 1024 sequences, is rejected with B2_ERR_MSG and a text that names the
+ * sizes; nothing is launched then.  (Llama-3-8B shapes, 16 K-token tables, chunk 512: up to 31 sequences; chunk
+ * 2048: up to 125.)  The whole call is one kernel launch.
  * The first call on each device looks the array's address up and sets the kernels' shared-memory limit;
  * make that call before any stream capture begins (two host threads making their first call on one device
  * at the same time both do this set-up, with the same result).  All calls on one device share the array and it keeps
@@ -405,6 +406,40 @@ typedef struct {
 /* generate (src/decode/stream.rs:113-121 + decode_loop :259-327). cancel may be null. */
 int32_t b2_generate(b2_model* m, const b2_request* req, const volatile int32_t* cancel, b2_event_cb cb, void* user,
                     b2_gen_output* out);
+/* PrefixCache / generate_cached (src/decode/prefix.rs:56-188): shared-prefix KV reuse for the single-sequence loop.
+ * The cache keeps up to `capacity` finished sequences (prompt + generated) as paged caches in a pool of its own
+ * (`max_pages` pages, least recently used sequences are dropped past the capacity or when the pool runs out); a
+ * request reuses the longest stored prefix of its prompt -- the full blocks by reference, a partly covered last block
+ * by one page copy -- and prefills only the rest.  The result is token for token that of b2_generate.  PrefixStats
+ * (:34-47). */
+typedef struct b2_prefix_cache b2_prefix_cache;
+typedef struct { int64_t lookups, hits, reused_prefix_tokens, computed_prefill_tokens; } b2_prefix_stats;
+int32_t b2_prefix_cache_new(b2_ctx* ctx, b2_model* m, int32_t capacity, int64_t max_pages, int32_t max_blocks_per_seq,
+                            b2_prefix_cache** out);                            /* PrefixCache::new :66-72 */
+int32_t b2_prefix_cache_free(b2_prefix_cache* pc);
+int32_t b2_prefix_cache_stats(const b2_prefix_cache* pc, b2_prefix_stats* out); /* PrefixCache::stats :75-77 */
+int32_t b2_prefix_cache_len(const b2_prefix_cache* pc);                          /* PrefixCache::len :80-82 */
+int32_t b2_generate_cached(b2_model* m, const b2_request* req, const volatile int32_t* cancel, b2_event_cb cb, void* user,
+                           b2_prefix_cache* pc, b2_gen_output* out);            /* generate_cached :144-188 */
+/* A new cache of the same pool holding the first `len` positions of `src` (len <= offset(src)): whole blocks shared by
+ * reference count as PagedKvCache::new_seeded does (src/primitives/paged_kv_cache.rs:221-235), a partly covered last
+ * block copied into a private page.  Neither cache sees the other's later writes. */
+int32_t b2_cache_fork(const b2_cache* src, int32_t len, b2_cache** out);
+
+/* generate_prompt_lookup (src/decode/speculative.rs:73-171): prompt-lookup (n-gram) speculative decoding, greedy.
+ * Every step verifies [last token, drafts...] in ONE forward with the logits of every position, accepts the longest
+ * draft prefix the target agrees with plus one bonus token, and rolls the rejected positions back with
+ * KvCache::truncate.  SpeculativeConfig (:45-60) / SpeculativeStats (:62-71).  With num_draft == 0 the result is the
+ * plain greedy loop's. */
+typedef struct { int32_t max_ngram, num_draft; } b2_speculative_config;
+typedef struct { int64_t forwards, proposed, accepted; } b2_speculative_stats;
+int32_t b2_generate_prompt_lookup(b2_model* m, const b2_request* req, const b2_speculative_config* spec,
+                                  const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_gen_output* out,
+                                  b2_speculative_stats* stats /* nullable */);
+/* The proposer on its own (core_llm::speculative::ngram_propose as speculative.rs:3-8 describes it): up to k tokens
+ * that followed the most recent earlier occurrence of the history's trailing n-gram, n = max_ngram .. 1. */
+int32_t b2_ngram_propose(const int32_t* history, int32_t n_history, int32_t max_ngram, int32_t k, int32_t* out, int32_t* n_out);
+
 /* generate_continuous (src/decode/continuous.rs:117-229). outs has n entries; stats may be null. */
 int32_t b2_generate_continuous(b2_model* m, const b2_request* reqs, int32_t n, const b2_continuous_config* cfg,
                                const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_gen_output* outs,

@@ -51,6 +51,8 @@ struct b2_ctx {
     int* err_host = nullptr;       // pinned copy the engine step reads back with its sampled ids
     long long wait_cycles = 8000000000LL;  // limit of a wait on another rank (b2_ctx_set_wait_limit_ms), ~4 s
     int clock_khz = 1965000;
+    int* attn_counters = nullptr;  // arrival counters of the decode attention's fused merge (self-resetting)
+    size_t attn_counters_cap = 0;
     int* tile_counters = nullptr;  // per row-tile arrival counters of the split-K streaming kernel (self-resetting)
     bool use_tc = true;
     // optional per-kernel-class timing with CUDA events on the launching stream

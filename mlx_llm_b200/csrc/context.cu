@@ -68,6 +68,7 @@ int32_t b2_ctx_free(b2_ctx* ctx) {
     if (ctx->dev_err) cudaFree(ctx->dev_err);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
     if (ctx->tile_counters) cudaFree(ctx->tile_counters);
+    if (ctx->attn_counters) cudaFree(ctx->attn_counters);
     for (auto e : ctx->prof_ev) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);

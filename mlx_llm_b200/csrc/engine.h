@@ -164,6 +164,9 @@ struct SeqStep {
     const int32_t* ids;
     int n;
     bool want_logits;
+    // logits / greedy ids of EVERY new position, not only the last (CausalLm::decode_logits_all, llama.rs:372-392: the
+    // verify forward of speculative decoding).  Only for a step of one sequence.
+    bool all_positions = false;
 };
 // One forward over a ragged batch.  argmax_out[i] (per sequence that wants logits, in batch order)
 // and logits_out (rows in the same order: bf16, or f32 for an f32 model) are host pointers, nullable.
@@ -172,5 +175,5 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
 // *logits_dev receives the device address of the [n_logits, vocab] f32 logits.
 struct BatchMetaOut;
 int32_t b2_forward_f32(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const int32_t* seq_slot_dev, const int32_t* ids_dev, int T, int B,
-                       int n_logits, int max_ctx, float** logits_dev);
+                       int n_logits, const int32_t* logit_rows, int max_ctx, float** logits_dev);
 void b2_forward_f32_release(b2_model* m);

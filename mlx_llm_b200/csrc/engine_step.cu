@@ -150,7 +150,7 @@ int pick_chunk_tiles(long dec_ctx_sum, int hkv, int sm_count) {
 
 // The bf16 layers of one step: embedding, every decoder layer, the sampled rows' final norm, lm_head and argmax.
 int32_t forward_bf16_layers(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const BatchMetaIn& in, const int32_t* ids_dev, int T, int n_dec,
-                            long dec_ctx_sum, int W, int P, double pf_flops, int chunk_tiles, int q_tile, int n_logits) {
+                            long dec_ctx_sum, int W, int P, double pf_flops, int chunk_tiles, int q_tile, int n_logits, const int32_t* logit_rows) {
     b2_ctx* ctx = m->ctx;
     const b2_model_config& c = m->cfg;
     Workspace& w = m->ws;
@@ -208,6 +208,8 @@ int32_t forward_bf16_layers(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, 
             dp.part_o = w.attn_scratch;
             dp.part_ml = w.attn_scratch + (size_t)w.w_cap * hq * hd;
             dp.out = w.attn;
+            dp.num_seqs = n_dec;
+            B2_CHECK(b2_decode_attn_counters(ctx, n_dec, hkv, &dp.merge_counters));
             b2_prof_mark(ctx, B2_CLS_ATTN_DECODE);
             B2_CHECK(b2_decode_attn_launch(ctx, dp, hd, W, n_dec));
             ctx->attn_decode_bytes += (double)dec_ctx_sum * hkv * hd * 2 * 2;
@@ -258,7 +260,7 @@ int32_t forward_bf16_layers(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, 
     }
     if (n_logits > 0) {
         b2_prof_mark(ctx, B2_CLS_ELEMENTWISE);
-        B2_CHECK(b2_rms_norm_launch(ctx, w.x, m->norm, c.rms_norm_eps, n_logits, H, H, mo.logit_rows, w.last));
+        B2_CHECK(b2_rms_norm_launch(ctx, w.x, m->norm, c.rms_norm_eps, n_logits, H, H, logit_rows, w.last));
         Proj head;
         head.bits = 0;
         head.N = c.vocab_size;
@@ -283,6 +285,8 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
     b2_pool* pool = seqs[0].cache->pool;
     int T = 0, max_pos = 0, n_logits = 0, n_dec = 0;
     long dec_ctx_sum = 0;
+    const bool all_positions = seqs[0].all_positions;
+    B2_REQUIRE(!all_positions || B == 1, B2_ERR_MSG, "forward: logits of every position are available for a step of one sequence");
     for (auto& s : seqs) {
         B2_REQUIRE(s.cache && s.cache->pool == pool, B2_ERR_MSG, "forward: all caches of a step must share one pool");
         B2_REQUIRE(s.n > 0, B2_ERR_MSG, "forward: a sequence contributes no token");
@@ -317,9 +321,10 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
             P += (s.n + q_tile - 1) / q_tile;
         }
     }
+    if (all_positions) n_logits = T;  // rows 0..T-1 of the step, in order
     const int U = (int)pool->upd_slot.size();
     const size_t stage_ints = 4 * (size_t)B + 3 * (size_t)U + (size_t)T;
-    B2_CHECK(ensure_workspace(m, T, B, W, P, stage_ints));
+    B2_CHECK(ensure_workspace(m, T, std::max(B, n_logits), W, P, stage_ints));
     Workspace& w = m->ws;
     int32_t* sh = w.stage_host;
     for (int i = 0; i < B; i++) {
@@ -373,9 +378,10 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
 
     float* logits_f32_dev = nullptr;
     if (m->f32) {
-        B2_CHECK(b2_forward_f32(m, pool, mo, in.seq_slot, ids_dev, T, B, n_logits, max_pos, &logits_f32_dev));
+        B2_CHECK(b2_forward_f32(m, pool, mo, in.seq_slot, ids_dev, T, B, n_logits, all_positions ? nullptr : mo.logit_rows, max_pos, &logits_f32_dev));
     } else {
-        B2_CHECK(forward_bf16_layers(m, pool, mo, in, ids_dev, T, n_dec, dec_ctx_sum, W, P, pf_flops, chunk_tiles, q_tile, n_logits));
+        B2_CHECK(forward_bf16_layers(m, pool, mo, in, ids_dev, T, n_dec, dec_ctx_sum, W, P, pf_flops, chunk_tiles, q_tile, n_logits,
+                                     all_positions ? nullptr : mo.logit_rows));
     }
     if (n_logits > 0) {
         b2_prof_mark(ctx, B2_CLS_META);

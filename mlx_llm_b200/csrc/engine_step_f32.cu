@@ -206,7 +206,7 @@ void b2_forward_f32_release(b2_model* m) {
 }
 
 int32_t b2_forward_f32(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const int32_t* seq_slot_dev, const int32_t* ids_dev, int T, int B,
-                       int n_logits, int max_ctx, float** logits_dev) {
+                       int n_logits, const int32_t* logit_rows, int max_ctx, float** logits_dev) {
     b2_ctx* ctx = m->ctx;
     const b2_model_config& c = m->cfg;
     B2_REQUIRE(pool->esz == 4, B2_ERR_MSG, "forward: an f32 model needs a pool created for it");
@@ -227,9 +227,9 @@ int32_t b2_forward_f32(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const
         B2_CHECK(regrow(w.act, t * I));
         w.t_cap = (int)t;
     }
-    if (B > w.b_cap) {
+    if (std::max(B, n_logits) > w.b_cap) {
         B2_CUDA(cudaStreamSynchronize(ctx->stream));
-        const size_t b = (size_t)std::max(B, 16) * 5 / 4;
+        const size_t b = (size_t)std::max(std::max(B, n_logits), 16) * 5 / 4;
         B2_CHECK(regrow(w.last, b * H));
         B2_CHECK(regrow(w.logits, b * V));
         w.b_cap = (int)b;
@@ -262,7 +262,7 @@ int32_t b2_forward_f32(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const
         B2_CHECK(linear(ctx, w.act, L.down, w.x, T, w.x));
     }
     if (n_logits > 0) {
-        rms_norm_f32_kernel<<<n_logits, 128, 0, st>>>(w.x, (const float*)m->norm, c.rms_norm_eps, H, mo.logit_rows, w.last);
+        rms_norm_f32_kernel<<<n_logits, 128, 0, st>>>(w.x, (const float*)m->norm, c.rms_norm_eps, H, logit_rows, w.last);
         B2_LAUNCHED(ctx);
         head.bits = 0;
         head.N = V;

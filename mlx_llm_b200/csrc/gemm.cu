@@ -272,8 +272,12 @@ int32_t b2_gemm_launch(b2_ctx* ctx, const GemmParams& p) {
         B2_REQUIRE(p.K % 64 == 0, B2_ERR_UNSUPPORTED, "gemm: K must be a multiple of the group size");
         B2_REQUIRE(p.bits == 4 || p.bits == 8, B2_ERR_UNSUPPORTED, "gemm: bits must be 4 or 8");
     }
-    if (ctx->use_tc && b2_gemm_stream_eligible(p)) return b2_gemm_stream_launch(ctx, p);
-    if (ctx->use_tc && b2_gemm_tc_eligible(p)) return b2_gemm_tc_launch(ctx, p);
+    // Up to 32 tokens the weight-streaming kernel wins; from 33 on the tcgen05 kernel does where its tiling fits (one
+    // 16-token-granular block costs it the same as a full one, while the streaming kernel's cost grows with the tokens);
+    // the streaming kernel keeps 33..64 tokens for the shapes the tcgen05 tiling does not take.
+    const bool tc_ok = ctx->use_tc && b2_gemm_tc_eligible(p);
+    if (ctx->use_tc && b2_gemm_stream_eligible(p) && !tc_ok) return b2_gemm_stream_launch(ctx, p);
+    if (tc_ok) return b2_gemm_tc_launch(ctx, p);
     if (p.bits == 0) return dispatch_bm<0>(ctx, p);
     B2_REQUIRE(p.group == 64, B2_ERR_UNSUPPORTED, "gemm: only group size 64 is supported for quantized weights");
     B2_REQUIRE(p.K % 64 == 0, B2_ERR_UNSUPPORTED, "gemm: K must be a multiple of the group size");

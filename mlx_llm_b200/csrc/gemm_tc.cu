@@ -762,7 +762,7 @@ int32_t dispatch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
 }  // namespace
 
 bool b2_gemm_tc_eligible(const GemmParams& p) {
-    return p.M > 64 && p.N % TM == 0 && p.K % TK == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 &&
+    return p.M > 32 && p.N % TM == 0 && p.K % TK == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 &&
            ((uintptr_t)p.w & 15) == 0 && (p.bits == 0 || p.bits == 4 || p.bits == 8);
 }
 

@@ -15,7 +15,8 @@ struct DecodeAttnParams {
     const int32_t* bt_rows;       // nullable
     const int32_t* q_rows;        // nullable
     const int32_t* ctx_lens;      // [num_seqs]
-    const int32_t* work_seq;      // [n_work] sequence of each split-K work item
+    int num_seqs;                 // used when there is no work list
+    const int32_t* work_seq;      // [n_work] sequence of each split-K work item; null: the kernel derives the list from ctx_lens
     const int32_t* work_chunk;    // [n_work] chunk index inside its sequence
     const int32_t* seq_work_off;  // [num_seqs + 1] first work item of each sequence
     const int32_t* n_work;        // device scalar: number of valid work items (grid may be larger)
@@ -24,9 +25,11 @@ struct DecodeAttnParams {
     float scale_log2;             // softmax scale * log2(e)
     float* part_o;                // [n_work, hkv, group, hd] unnormalised partial outputs
     float* part_ml;               // [n_work, hkv, group, 2] running max (log2 domain) and sum
+    int* merge_counters;          // [num_seqs, hkv] arrivals per (sequence, kv head), zero between launches
     uint16_t* out;                // [rows, hq, hd] bf16
 };
 size_t b2_decode_attn_scratch_bytes(int max_work, int hq, int head_dim);
+int32_t b2_decode_attn_counters(b2_ctx* ctx, int num_seqs, int hkv, int** out);
 int32_t b2_decode_attn_launch(b2_ctx* ctx, const DecodeAttnParams& p, int head_dim, int grid_work, int num_seqs);
 
 // ---- GEMM (gemm.cu) ----------------------------------------------------------------------------

@@ -29,19 +29,17 @@ constexpr int kWarps = 4;
 constexpr int kStages = 3;
 constexpr unsigned kFull = 0xffffffffu;
 
+// One work item: chunk `chunk` of sequence `seq` (work index w; the sequence's items are w0 .. w0 + n_chunks - 1) for
+// kv head `kvh`.  Every thread of the CTA calls it; on return the shared memory may be reused.
 template <int HD>
-__global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const DecodeAttnParams p) {
+__device__ __forceinline__ void decode_item(const DecodeAttnParams& p, uint8_t* smem, int w, int kvh, int seq, int chunk, int w0,
+                                            int n_chunks) {
     constexpr int ROWB = HD * 2;        // bytes per token row of one head
     constexpr int CHUNKS = ROWB / 16;   // 16-byte chunks per row
     constexpr int TILE_B = 16 * ROWB;   // bytes of a 16-token tile
     constexpr int KSTEPS = HD / 16;
     constexpr int MT = HD / 16;
-    extern __shared__ __align__(128) uint8_t smem[];
-
-    const int w = blockIdx.x;
-    if (w >= *p.n_work) return;
-    const int kvh = blockIdx.y;
-    const int seq = p.work_seq[w], chunk = p.work_chunk[w];
+    __shared__ int s_last;
     const int ctx = min(p.ctx_lens[seq], p.max_blocks * p.page_tiles * 16);  // never past the block-table row
     const int tiles_total = (ctx + 15) >> 4;
     const int tile0 = chunk * p.chunk_tiles;
@@ -195,7 +193,6 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
         sm_l[warp * 8 + 2 * t + 1] = l1;
     }
     __syncthreads();
-    const int n_chunks = p.seq_work_off[seq + 1] - p.seq_work_off[seq];
     for (int e = threadIdx.x; e < group * HD; e += kWarps * 32) {
         const int h = e / HD, d = e % HD;
         float M = -INFINITY;
@@ -219,36 +216,179 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
             }
         }
     }
+    if (n_chunks == 1) return;
+    // Several chunks: the CTA of this (sequence, kv head) that finishes last merges them, in chunk order, so the
+    // result does not depend on who is last.  No CTA waits for another; the counter returns to zero for the next call.
+    __threadfence();  // this CTA's partial result is visible before its arrival is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = p.merge_counters + (size_t)seq * p.hkv + kvh;
+        const int arrived = atomicAdd(counter, 1);
+        s_last = arrived == n_chunks - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // out = sum_c O_c 2^(m_c-M) / sum_c l_c 2^(m_c-M), the sums taken in chunk order.  The merging CTA is on its own here,
+    // so its loads are kept independent of one another: every chunk's (max, sum) pair goes to shared memory in one
+    // sweep, one thread per head forms the weights in chunk order, then each output adds up its chunks with eight
+    // loads in flight.  Batches of kMergeBatch chunks keep the shared-memory use fixed whatever the chunk count.
+    constexpr int kMergeBatch = 512;
+    float* s_m = reinterpret_cast<float*>(smem);   // [kMergeBatch][8]: a chunk's maximum, then its weight f_c
+    float* s_l = s_m + kMergeBatch * 8;            // [kMergeBatch][8]: a chunk's sum
+    float* s_M = s_l + kMergeBatch * 8;            // [8]: overall maximum of a head
+    float* s_L = s_M + 8;                          // [8]: overall sum of a head
+    constexpr int PER = (8 * HD) / (kWarps * 32);  // outputs per thread when the group has 8 heads
+    float o_acc[PER];
+#pragma unroll
+    for (int k = 0; k < PER; k++) o_acc[k] = 0.f;
+    // overall maximum per head: taken from shared memory below when all chunks fit one batch (the usual case), else
+    // by a first sweep over the chunks (chunk order is irrelevant for a maximum)
+    const bool one_batch = n_chunks <= kMergeBatch;
+    if (threadIdx.x < group) {
+        float mx = -INFINITY;
+        if (!one_batch) {
+            int c = 0;
+            for (; c + 8 <= n_chunks; c += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = __ldcg(p.part_ml + ((((size_t)(w0 + c + j)) * p.hkv + kvh) * group + threadIdx.x) * 2);
+#pragma unroll
+                for (int j = 0; j < 8; j++) mx = fmaxf(mx, v[j]);
+            }
+            for (; c < n_chunks; c++) mx = fmaxf(mx, __ldcg(p.part_ml + ((((size_t)(w0 + c)) * p.hkv + kvh) * group + threadIdx.x) * 2));
+        }
+        s_M[threadIdx.x] = mx;
+        s_L[threadIdx.x] = 0.f;
+    }
+    __syncthreads();
+    for (int c0 = 0; c0 < n_chunks; c0 += kMergeBatch) {
+        const int nb = min(kMergeBatch, n_chunks - c0);
+        for (int i = threadIdx.x; i < nb * group; i += kWarps * 32) {
+            const int c = i / group, h = i - c * group;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((((size_t)(w0 + c0 + c)) * p.hkv + kvh) * group + h) * 2));
+            s_m[c * 8 + h] = ml.x;
+            s_l[c * 8 + h] = ml.y;
+        }
+        __syncthreads();
+        if (threadIdx.x < group) {  // weights and the running sum of this head, in chunk order
+            float M = s_M[threadIdx.x];
+            if (one_batch) {
+                for (int c = 0; c < nb; c++) M = fmaxf(M, s_m[c * 8 + threadIdx.x]);
+                s_M[threadIdx.x] = M;
+            }
+            float L = s_L[threadIdx.x];
+            for (int c = 0; c < nb; c++) {
+                const float f = fast_exp2(s_m[c * 8 + threadIdx.x] - M);
+                L += s_l[c * 8 + threadIdx.x] * f;
+                s_m[c * 8 + threadIdx.x] = f;
+            }
+            s_L[threadIdx.x] = L;
+        }
+        __syncthreads();
+        // partial outputs: eight chunks of every output of this thread in flight at a time
+        const size_t stride = (size_t)p.hkv * group * HD;  // from one chunk's partial output to the next
+        for (int c = 0; c < nb; c += 8) {
+            float v[PER][8];
+#pragma unroll
+            for (int k = 0; k < PER; k++) {
+                const int e = threadIdx.x + k * kWarps * 32;
+                const float* src = p.part_o + (((size_t)(w0 + c0 + c) * p.hkv + kvh) * group) * HD + e;  // e = h * HD + d
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[k][j] = (e < group * HD && c + j < nb) ? __ldcg(src + (size_t)j * stride) : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < PER; k++) {
+                const int e = threadIdx.x + k * kWarps * 32;
+                const int h = min(e / HD, 7);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (c + j < nb) o_acc[k] += v[k][j] * s_m[(c + j) * 8 + h];
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        const int e = threadIdx.x + k * kWarps * 32;
+        if (e >= group * HD) break;
+        const int h = e / HD, d = e % HD;
+        p.out[((size_t)qrow * p.hq + (size_t)kvh * group + h) * HD + d] = f2bf(o_acc[k] / s_L[h]);
+    }
 }
 
-// Merge the chunks of one (sequence, kv head): out = sum_c O_c 2^(m_c-M) / sum_c l_c 2^(m_c-M).
+// Two ways to find the work items.  With a work list (the engine's packer builds it with the rest of the step's
+// metadata) the grid is (items, kv heads), one item per CTA.  Without one, every CTA of a persistent grid derives the
+// list itself from the context lengths (a block-wide scan, up to kInlineSeqs sequences) and takes every gridDim.x-th
+// (item, kv head) pair: the whole operation is one launch.
+constexpr int kInlineSeqs = 1024;
+
 template <int HD>
-__global__ void paged_attn_merge_kernel(const DecodeAttnParams p) {
-    // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic
-    // stream serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
+__global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const DecodeAttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic stream
+    // serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    const int seq = blockIdx.x, kvh = blockIdx.y;
-    const int w0 = p.seq_work_off[seq], n = p.seq_work_off[seq + 1] - w0;
-    if (n == 1) return;  // written by the decode kernel itself
-    const int group = p.hq / p.hkv;
-    const int qrow = p.q_rows ? p.q_rows[seq] : seq;
-    if (n <= 0) {  // an empty context attends to nothing: its rows are zeros
-        for (int e = threadIdx.x; e < group * HD; e += blockDim.x)
-            p.out[((size_t)qrow * p.hq + (size_t)kvh * group + e / HD) * HD + e % HD] = 0;
+    if (p.work_seq) {
+        const int w = blockIdx.x;
+        if (w >= *p.n_work) return;
+        const int seq = p.work_seq[w];
+        const int w0 = p.seq_work_off[seq];
+        decode_item<HD>(p, smem, w, blockIdx.y, seq, p.work_chunk[w], w0, p.seq_work_off[seq + 1] - w0);
         return;
     }
-    for (int e = threadIdx.x; e < group * HD; e += blockDim.x) {
-        const int h = e / HD, d = e % HD;
-        float M = -INFINITY;
-        for (int c = 0; c < n; c++) M = fmaxf(M, p.part_ml[((((size_t)(w0 + c)) * p.hkv + kvh) * group + h) * 2]);
-        float L = 0.f, O = 0.f;
-        for (int c = 0; c < n; c++) {
-            const size_t slot = ((size_t)(w0 + c) * p.hkv + kvh) * group + h;
-            const float f = fast_exp2(p.part_ml[slot * 2] - M);
-            L += p.part_ml[slot * 2 + 1] * f;
-            O += p.part_o[slot * HD + d] * f;
+    __shared__ int s_off[kInlineSeqs + 1];  // first work item of every sequence
+    __shared__ int s_warp[kWarps];
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const int per_seq = (p.max_blocks * p.page_tiles + p.chunk_tiles - 1) / p.chunk_tiles;
+        int carry = 0;
+        for (int base = 0; base < p.num_seqs; base += kWarps * 32) {
+            const int i = base + threadIdx.x;
+            int n = 0;
+            if (i < p.num_seqs) {
+                const int tiles = (max(p.ctx_lens[i], 0) + 15) >> 4;
+                n = min((tiles + p.chunk_tiles - 1) / p.chunk_tiles, per_seq);
+            }
+            int incl = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(kFull, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (lane == 31) s_warp[warp] = incl;
+            __syncthreads();
+            int before = carry;
+            for (int ww = 0; ww < warp; ww++) before += s_warp[ww];
+            if (i < p.num_seqs) s_off[i] = before + incl - n;
+            int total = carry;
+            for (int ww = 0; ww < kWarps; ww++) total += s_warp[ww];
+            carry = total;
+            __syncthreads();
         }
-        p.out[((size_t)qrow * p.hq + (size_t)kvh * group + h) * HD + d] = f2bf(O / L);
+        if (threadIdx.x == 0) s_off[p.num_seqs] = carry;
+        __syncthreads();
+    }
+    const int n_work = s_off[p.num_seqs];
+    for (int i = blockIdx.x; i < p.num_seqs; i += gridDim.x)  // an empty context attends to nothing: rows of zeros
+        if (s_off[i + 1] == s_off[i]) {
+            const int qrow = p.q_rows ? p.q_rows[i] : i;
+            for (int e = threadIdx.x; e < p.hq * HD; e += kWarps * 32) p.out[(size_t)qrow * p.hq * HD + e] = 0;
+        }
+    for (int item = blockIdx.x; item < n_work * p.hkv; item += gridDim.x) {
+        const int w = item / p.hkv, kvh = item - w * p.hkv;
+        int lo = 0, hi = p.num_seqs - 1;  // the sequence whose items contain w: the last one with s_off <= w among those with items
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_off[mid] <= w)
+                lo = mid;
+            else
+                hi = mid - 1;
+        }
+        const int seq = lo;  // s_off[seq] <= w < s_off[seq + 1]: sequences without items are never the largest such index
+        decode_item<HD>(p, smem, w, kvh, seq, w - s_off[seq], s_off[seq], s_off[seq + 1] - s_off[seq]);
+        __syncthreads();  // the pipeline buffers are reused by the next item
     }
 }
 
@@ -300,14 +440,14 @@ int32_t launch_decode(b2_ctx* ctx, const DecodeAttnParams& p, int grid_work, int
     const int smem = kWarps * kStages * 2 * 16 * HD * 2;
     B2_SMEM_ONCE(ctx, paged_attn_decode_kernel<HD>, smem);
     dim3 grid(grid_work, p.hkv);
+    // in-kernel work list: a fixed grid of sixteen CTAs per SM, each taking every gridDim.x-th item.  Two are resident
+    // per SM at a time and none waits for another, so the rest simply queue; the fine grain lets the hardware's block
+    // scheduler even out items of different cost (measured: 4 / 8 / 16 CTAs per SM -> 174 / 150 / 137 us on 64 sequences)
+    if (!p.work_seq) grid = dim3(16 * ctx->sm_count);
     paged_attn_decode_kernel<HD><<<grid, kWarps * 32, smem, ctx->stream>>>(p);
     B2_LAUNCHED(ctx);
-    const int group = p.hq / p.hkv;
-    int threads = group * HD;
-    if (threads > 1024) threads = 1024;
-    paged_attn_merge_kernel<HD><<<dim3(num_seqs, p.hkv), threads, 0, ctx->stream>>>(p);
-    B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
+    (void)num_seqs;
     return B2_OK;
 }
 
@@ -318,11 +458,29 @@ size_t b2_decode_attn_scratch_bytes(int max_work, int hq, int head_dim) {
     return (size_t)max_work * hq * (head_dim + 2) * sizeof(float);
 }
 
+// Arrival counters of the fused merge: one int per (sequence, kv head), zero between calls (the kernel resets them).
+int32_t b2_decode_attn_counters(b2_ctx* ctx, int num_seqs, int hkv, int** out) {
+    const size_t need = (size_t)num_seqs * hkv;
+    if (need > ctx->attn_counters_cap) {
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->attn_counters) B2_CUDA(cudaFree(ctx->attn_counters));
+        ctx->attn_counters = nullptr;
+        const size_t cap = need + need / 4 + 1024;
+        B2_CUDA(cudaMalloc((void**)&ctx->attn_counters, cap * sizeof(int)));
+        B2_CUDA(cudaMemsetAsync(ctx->attn_counters, 0, cap * sizeof(int), ctx->stream));
+        ctx->attn_counters_cap = cap;
+    }
+    *out = ctx->attn_counters;
+    return B2_OK;
+}
+
 int32_t b2_decode_attn_launch(b2_ctx* ctx, const DecodeAttnParams& p, int head_dim, int grid_work, int num_seqs) {
     const int group = p.hq / p.hkv;
     B2_REQUIRE(p.hq % p.hkv == 0 && (group == 1 || group == 2 || group == 4 || group == 8), B2_ERR_UNSUPPORTED,
                "paged_attn_decode: q heads per kv head must be 1, 2, 4 or 8");
     B2_REQUIRE(p.chunk_tiles >= 1 && p.chunk_tiles <= 32 * kWarps, B2_ERR_MSG, "paged_attn_decode: chunk must be 16..2048 tokens");
+    B2_REQUIRE(p.merge_counters, B2_ERR_MSG, "paged_attn_decode: no arrival counters for the merge");
+    B2_REQUIRE(p.work_seq || (p.num_seqs >= 1 && p.num_seqs <= kInlineSeqs), B2_ERR_MSG, "paged_attn_decode: no work list and too many sequences to derive one in the kernel");
     if (grid_work <= 0 || num_seqs <= 0) return B2_OK;
     if (head_dim == 128) return launch_decode<128>(ctx, p, grid_work, num_seqs);
     if (head_dim == 64) return launch_decode<64>(ctx, p, grid_work, num_seqs);
@@ -349,10 +507,11 @@ extern "C" int32_t b2_paged_attn_decode(b2_ctx* ctx, const uint16_t* q_dev, cons
     const long max_work = per_seq * num_seqs;
     B2_REQUIRE(max_work < (1l << 30), B2_ERR_MSG, "b2_paged_attn_decode: work list too large");
 
-    // scratch: partials, then the work list
+    // scratch: partials, then (more than kInlineSeqs sequences only) the work list a first kernel builds
+    const bool inline_list = num_seqs <= kInlineSeqs;
     size_t part_bytes = b2_decode_attn_scratch_bytes((int)max_work, hq, head_dim);
     part_bytes = (part_bytes + 255) & ~(size_t)255;
-    const size_t list_bytes = ((size_t)max_work * 2 + num_seqs + 2) * sizeof(int32_t);
+    const size_t list_bytes = inline_list ? 0 : ((size_t)max_work * 2 + num_seqs + 2) * sizeof(int32_t);
     void* scratch = nullptr;
     B2_CHECK(b2_ctx_scratch(ctx, part_bytes + list_bytes, &scratch));
     DecodeAttnParams p{};
@@ -362,6 +521,7 @@ extern "C" int32_t b2_paged_attn_decode(b2_ctx* ctx, const uint16_t* q_dev, cons
     p.block_tables = block_tables_dev;
     p.max_blocks = max_blocks;
     p.ctx_lens = ctx_lens_dev;
+    p.num_seqs = num_seqs;
     p.chunk_tiles = chunk_tiles;
     p.hq = hq;
     p.hkv = hkv;
@@ -369,18 +529,19 @@ extern "C" int32_t b2_paged_attn_decode(b2_ctx* ctx, const uint16_t* q_dev, cons
     p.scale_log2 = scale * 1.4426950408889634f;
     p.part_o = reinterpret_cast<float*>(scratch);
     p.part_ml = p.part_o + (size_t)max_work * hq * head_dim;
-    int32_t* lists = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(scratch) + part_bytes);
-    int32_t* work_seq = lists;
-    int32_t* work_chunk = lists + max_work;
-    int32_t* seq_off = lists + 2 * max_work;
-    int32_t* n_work = seq_off + num_seqs + 1;
-    p.work_seq = work_seq;
-    p.work_chunk = work_chunk;
-    p.seq_work_off = seq_off;
-    p.n_work = n_work;
     p.out = out_dev;
-    decode_worklist_kernel<<<1, 1024, 0, ctx->stream>>>(ctx_lens_dev, num_seqs, chunk_tiles, (int)per_seq, work_seq, work_chunk, seq_off, n_work);
-    B2_LAUNCHED(ctx);
+    B2_CHECK(b2_decode_attn_counters(ctx, num_seqs, hkv, &p.merge_counters));
+    if (!inline_list) {
+        int32_t* lists = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(scratch) + part_bytes);
+        int32_t* seq_off = lists + 2 * max_work;
+        p.work_seq = lists;
+        p.work_chunk = lists + max_work;
+        p.seq_work_off = seq_off;
+        p.n_work = seq_off + num_seqs + 1;
+        decode_worklist_kernel<<<1, 1024, 0, ctx->stream>>>(ctx_lens_dev, num_seqs, chunk_tiles, (int)per_seq, lists, lists + max_work, seq_off,
+                                                            seq_off + num_seqs + 1);
+        B2_LAUNCHED(ctx);
+    }
     return b2_decode_attn_launch(ctx, p, head_dim, (int)max_work, num_seqs);
 }
 
@@ -409,9 +570,10 @@ extern "C" int32_t b2_paged_attn_decode_host(b2_ctx* ctx, const uint16_t* q_host
 // Some hosts of this library cannot reach cudaMalloc at the moment they need attention: a serving
 // loop that has handed every free byte of HBM to its KV pool, a thread that runs under a real-time
 // deadline, or an embedding runtime that owns the allocator and forbids foreign allocations.  For
-// them the split-K scratch (partial outputs, running max / sum, the work list) lives in the fixed
+// them the split-K scratch (partial outputs, running max / sum, the merge's arrival counters) lives in the fixed
 // array below, which every GPU that loads this library carries until the process exits.
 constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB per device
+constexpr size_t kStaticCounterBytes = 64u << 10;  // its first 64 KiB: the merge's arrival counters
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
 
 namespace {
@@ -422,6 +584,7 @@ namespace {
 // same values, which is harmless; after that the call only reads them.
 unsigned char* g_scratch_addr[64] = {};
 bool g_static_smem_set[64][2] = {};
+int g_static_grid[64][2] = {};  // sixteen CTAs per SM of the device
 }  // namespace
 
 extern "C" int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_dev, const uint16_t* k_pool_dev,
@@ -443,11 +606,11 @@ extern "C" int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_d
     const int chunk_tiles = chunk_tokens / 16, page_tiles = page_size / 16;
     const long per_seq = ((long)max_blocks * page_tiles + chunk_tiles - 1) / chunk_tiles;
     const long max_work = per_seq * num_seqs;
-    size_t part_bytes = (size_t)max_work * hq * (head_dim + 2) * sizeof(float);
-    part_bytes = (part_bytes + 255) & ~(size_t)255;
-    const size_t list_bytes = ((size_t)max_work * 2 + num_seqs + 2) * sizeof(int32_t);
-    B2_REQUIRE(part_bytes + list_bytes <= kStaticScratchBytes, B2_ERR_MSG,
-               "b2_paged_attn_decode_static: this batch needs " + std::to_string(part_bytes + list_bytes) +
+    B2_REQUIRE(num_seqs <= kInlineSeqs && (long)num_seqs * hkv * sizeof(int) <= (long)kStaticCounterBytes, B2_ERR_MSG,
+               "b2_paged_attn_decode_static: at most 1024 sequences and 16384 (sequence, kv head) pairs per call");
+    const size_t part_bytes = (size_t)max_work * hq * (head_dim + 2) * sizeof(float);
+    B2_REQUIRE(kStaticCounterBytes + part_bytes <= kStaticScratchBytes, B2_ERR_MSG,
+               "b2_paged_attn_decode_static: this batch needs " + std::to_string(kStaticCounterBytes + part_bytes) +
                    " bytes of split-K scratch, the fixed array holds " + std::to_string(kStaticScratchBytes) +
                    " (raise chunk_tokens, lower max_blocks, or use b2_paged_attn_decode)");
     int dev = 0;
@@ -468,6 +631,11 @@ extern "C" int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_d
     }
     unsigned char* scratch = g_scratch_addr[dev];
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (!g_static_grid[dev][head_dim == 128]) {
+        int sms = 0;
+        B2_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        g_static_grid[dev][head_dim == 128] = 16 * sms;
+    }
     DecodeAttnParams p{};
     p.q = q_dev;
     p.k_pool = k_pool_dev;
@@ -475,36 +643,24 @@ extern "C" int32_t b2_paged_attn_decode_static(void* stream, const uint16_t* q_d
     p.block_tables = block_tables_dev;
     p.max_blocks = max_blocks;
     p.ctx_lens = ctx_lens_dev;
+    p.num_seqs = num_seqs;
     p.chunk_tiles = chunk_tiles;
     p.hq = hq;
     p.hkv = hkv;
     p.page_tiles = page_tiles;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_o = reinterpret_cast<float*>(scratch);
+    // Layout of the array: [arrival counters, kStaticCounterBytes][partial outputs][running max / sum].  Only the counters
+    // have to start at zero: the array is zero when the library is loaded and the kernel returns every counter it used
+    // to zero before it ends; every partial result the merge reads is written by this call first.
+    p.merge_counters = reinterpret_cast<int*>(scratch);
+    p.part_o = reinterpret_cast<float*>(scratch + kStaticCounterBytes);
     p.part_ml = p.part_o + (size_t)max_work * hq * head_dim;
-    int32_t* lists = reinterpret_cast<int32_t*>(scratch + part_bytes);
-    int32_t* work_seq = lists;
-    int32_t* work_chunk = lists + max_work;
-    int32_t* seq_off = lists + 2 * max_work;
-    int32_t* n_work = seq_off + num_seqs + 1;
-    p.work_seq = work_seq;
-    p.work_chunk = work_chunk;
-    p.seq_work_off = seq_off;
-    p.n_work = n_work;
     p.out = out_dev;
-    // Nothing in the array has to start at zero: the work list (and its count) is rewritten by the
-    // first kernel of every call, and every partial the merge reads is written by this call's decode
-    // kernel first.
-    decode_worklist_kernel<<<1, 1024, 0, st>>>(ctx_lens_dev, num_seqs, chunk_tiles, (int)per_seq, work_seq, work_chunk, seq_off, n_work);
-    const dim3 grid((unsigned)max_work, hkv);
-    int threads = group * head_dim > 1024 ? 1024 : group * head_dim;
-    if (head_dim == 128) {
+    const dim3 grid((unsigned)g_static_grid[dev][head_dim == 128]);
+    if (head_dim == 128)
         paged_attn_decode_kernel<128><<<grid, kWarps * 32, smem, st>>>(p);
-        paged_attn_merge_kernel<128><<<dim3(num_seqs, hkv), threads, 0, st>>>(p);
-    } else {
+    else
         paged_attn_decode_kernel<64><<<grid, kWarps * 32, smem, st>>>(p);
-        paged_attn_merge_kernel<64><<<dim3(num_seqs, hkv), threads, 0, st>>>(p);
-    }
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }

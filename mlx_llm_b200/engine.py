@@ -381,6 +381,13 @@ class PagedKvCache:
         check(load().b2_cache_gather(self.h, int(layer), k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)))
         return k, v
 
+    def fork(self, length):
+        """A new cache holding the first `length` positions: whole blocks shared, a partial last block copied."""
+        c = PagedKvCache.__new__(PagedKvCache)
+        c.pool, c.h = self.pool, C.c_void_p()
+        check(load().b2_cache_fork(self.h, int(length), C.byref(c.h)))
+        return c
+
     def gather_f32(self, layer, n_kv_heads, head_dim):
         """The same for a pool of an f32 model: float32 arrays."""
         n = self.offset()
@@ -519,6 +526,96 @@ def generate(model, prompt_ids, max_new_tokens=256, stop_tokens=(), cancel: Opti
     if err:
         raise err[0]
     return GenerationOutput(buf[: out.n_tokens].tolist(), int(out.finish_reason))
+
+
+class CSpeculativeConfig(C.Structure):
+    _fields_ = [("max_ngram", C.c_int32), ("num_draft", C.c_int32)]
+
+
+class CSpeculativeStats(C.Structure):
+    _fields_ = [("forwards", C.c_int64), ("proposed", C.c_int64), ("accepted", C.c_int64)]
+
+
+class CPrefixStats(C.Structure):
+    _fields_ = [("lookups", C.c_int64), ("hits", C.c_int64), ("reused_prefix_tokens", C.c_int64), ("computed_prefill_tokens", C.c_int64)]
+
+
+@dataclass
+class SpeculativeConfig:  # src/decode/speculative.rs:45-60
+    max_ngram: int = 3
+    num_draft: int = 4
+
+
+def _single(fn_name, model, prompt_ids, max_new_tokens, stop_tokens, cancel, on_event, *extra):
+    """Shared driver of the single-sequence loops: builds the request, the output buffer and the callback."""
+    req = BatchRequest(list(prompt_ids), max_new_tokens, list(stop_tokens))
+    arr, keep = _c_requests([req])
+    buf = np.zeros(max(max_new_tokens, 1), np.int32)
+    out = CGenOutput(buf.ctypes.data_as(C.POINTER(C.c_int32)), buf.size, 0, 0)
+    err = []
+
+    def _cb(_user, _req, kind, a, b):
+        try:
+            if on_event:
+                on_event(("token", a, b) if kind == 0 else ("done", a, b))
+        except Exception as e:
+            err.append(e)
+
+    cb = EVENT_CB(_cb)
+    cancel_p = C.byref(cancel.v) if cancel else None
+    yield arr, cancel_p, cb, out
+    if err:
+        raise err[0]
+    yield GenerationOutput(buf[: out.n_tokens].tolist(), int(out.finish_reason))
+
+
+def generate_prompt_lookup(model, prompt_ids, max_new_tokens=256, spec: Optional[SpeculativeConfig] = None, stop_tokens=(),
+                           cancel: Optional[CancelFlag] = None, on_event=None):
+    """generate_prompt_lookup (src/decode/speculative.rs:73-171).  Returns (GenerationOutput, stats dict)."""
+    spec = spec or SpeculativeConfig()
+    g = _single("b2_generate_prompt_lookup", model, prompt_ids, max_new_tokens, stop_tokens, cancel, on_event)
+    arr, cancel_p, cb, out = next(g)
+    cs, st = CSpeculativeConfig(spec.max_ngram, spec.num_draft), CSpeculativeStats()
+    check(load().b2_generate_prompt_lookup(model.h, C.byref(arr[0]), C.byref(cs), cancel_p, cb, None, C.byref(out), C.byref(st)))
+    return next(g), dict(forwards=int(st.forwards), proposed=int(st.proposed), accepted=int(st.accepted))
+
+
+def ngram_propose(history, max_ngram, k):
+    h = np.ascontiguousarray(history, np.int32)
+    out = np.zeros(max(k, 1), np.int32)
+    n = C.c_int32(0)
+    check(load().b2_ngram_propose(h.ctypes.data_as(C.c_void_p), int(h.size), int(max_ngram), int(k), out.ctypes.data_as(C.c_void_p), C.byref(n)))
+    return out[: n.value].tolist()
+
+
+class PrefixCache:
+    """PrefixCache (src/decode/prefix.rs:56-131) over a page pool of its own."""
+
+    def __init__(self, ctx, model, capacity, max_pages=1024, max_blocks_per_seq=256):
+        self.h = C.c_void_p()
+        check(load().b2_prefix_cache_new(ctx.h, model.h, int(capacity), C.c_int64(max_pages), int(max_blocks_per_seq), C.byref(self.h)))
+
+    def stats(self):
+        s = CPrefixStats()
+        check(load().b2_prefix_cache_stats(self.h, C.byref(s)))
+        return {k: int(getattr(s, k)) for k, _ in CPrefixStats._fields_}
+
+    def __len__(self):
+        return int(load().b2_prefix_cache_len(self.h))
+
+    def free(self):
+        if self.h:
+            check(load().b2_prefix_cache_free(self.h))
+            self.h = C.c_void_p()
+
+
+def generate_cached(model, prompt_ids, max_new_tokens, prefix_cache: PrefixCache, stop_tokens=(), cancel: Optional[CancelFlag] = None,
+                    on_event=None):
+    """generate_cached (src/decode/prefix.rs:144-188)."""
+    g = _single("b2_generate_cached", model, prompt_ids, max_new_tokens, stop_tokens, cancel, on_event)
+    arr, cancel_p, cb, out = next(g)
+    check(load().b2_generate_cached(model.h, C.byref(arr[0]), cancel_p, cb, None, prefix_cache.h, C.byref(out)))
+    return next(g)
 
 
 class CProfile(C.Structure):

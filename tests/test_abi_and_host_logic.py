@@ -185,3 +185,35 @@ def test_page_policy_oracle_is_self_consistent():
     assert meta["slot_mapping"][:2].tolist() == [1 * 16 + 1, 1 * 16 + 2] and meta["slot_mapping"][15] == 3 * 16 + 0
     assert meta["slot_mapping"][16] == 2 * 16 and meta["logit_rows"].tolist() == [16] and meta["dec_ctx"].tolist() == [1]
     assert meta["pf_seq"].tolist() == [0] and meta["counts"].tolist() == [1, 1, 1, 1, 0, 17]
+
+
+def test_ngram_proposer_matches_its_restatement(lib):
+    """b2_ngram_propose (host code, no GPU) against oracle/policies.py on random small-alphabet histories."""
+    from mlx_llm_b200 import engine as eng
+    from oracle import policies as pol
+
+    rng = np.random.default_rng(0)
+    for _ in range(300):
+        h = rng.integers(0, 4, size=int(rng.integers(0, 40))).tolist()
+        n, k = int(rng.integers(1, 5)), int(rng.integers(0, 7))
+        assert eng.ngram_propose(h, n, k) == pol.ngram_propose(h, n, k), (h, n, k)
+    assert eng.ngram_propose([1, 2, 3, 9, 1, 2, 3], 3, 4) == [9, 1, 2, 3]      # longest n-gram first, copy to the end
+    assert eng.ngram_propose([7, 1, 2, 8, 1, 2, 5, 1, 2], 2, 1) == [5]           # the most recent earlier occurrence
+    assert eng.ngram_propose([1, 2, 3], 3, 2) == []
+
+
+def test_prefix_policy_restatement():
+    """The host policy of the prefix cache: longest stored prefix, whole-prompt cap, LRU, subsumed entries."""
+    from oracle import policies as pol
+
+    p = pol.PrefixPolicy(2)
+    assert p.lookup([1, 2, 3, 4]) == 0
+    p.store([1, 2, 3, 4, 9], 4)
+    assert p.lookup([1, 2, 3, 7]) == 3 and p.lookup([1, 2, 3, 4]) == 3      # whole-prompt match keeps one token to compute
+    assert p.lookup([1, 2, 3, 4, 9, 9]) == 4                                 # never beyond the stored KV
+    p.store([5, 6], 1)
+    p.store([1, 2, 3, 4, 9, 9, 9], 6)                                         # subsumes the first entry
+    assert [e["tokens"] for e in p.entries] == [[5, 6], [1, 2, 3, 4, 9, 9, 9]]
+    p.store([8], 0)
+    assert [e["tokens"] for e in p.entries] == [[1, 2, 3, 4, 9, 9, 9], [8]]  # [5, 6] was the least recently used
+    assert p.stats == dict(lookups=4, hits=3, reused_prefix_tokens=10, computed_prefill_tokens=8)

@@ -32,7 +32,7 @@ def quant_case(seed, n, k, bits):
 
 
 @pytest.mark.parametrize("bits", [4, 8, 0])
-@pytest.mark.parametrize("m,n,k", [(65, 128, 64), (100, 256, 512), (256, 128, 4096), (300, 384, 1024), (700, 256, 2048),
+@pytest.mark.parametrize("m,n,k", [(33, 256, 2048), (48, 384, 512), (64, 640, 1024), (65, 128, 64), (100, 256, 512), (256, 128, 4096), (300, 384, 1024), (700, 256, 2048),
                                    # more 256-token blocks than CTA pairs: several pieces per pair, two-block pieces,
                                    # a ragged last block, and an output width that is an odd multiple of 128
                                    (700, 20480, 256), (530, 19072, 128), (1100, 9984, 192)])
@@ -78,11 +78,12 @@ def test_tc_matches_warp_level_kernel(env):
 
 
 @pytest.mark.parametrize("bits", [4, 8, 0])
-@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (5, 256, 512), (8, 1024, 4096), (9, 128, 1024), (16, 384, 2048), (33, 256, 4096),
-                                   (64, 512, 1024), (3, 128, 14336)])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (5, 256, 512), (8, 1024, 4096), (9, 128, 1024), (16, 384, 2048), (17, 256, 4096),
+                                   (32, 512, 1024), (3, 128, 14336)])
 def test_stream_gemm_vs_oracle(env, bits, m, n, k):
-    """Up to 64 tokens with N a multiple of 128 and K of 256 take the weight-streaming kernel: every token-tile
-    count (8, 16, 32, 64 wide), one and several K ranges, ragged token counts."""
+    """Up to 32 tokens with N a multiple of 128 and K of 256 take the weight-streaming kernel: the token-tile counts
+    8, 16 and 32 wide, one and several K ranges, ragged token counts (from 33 tokens on the tcgen05 kernel takes every
+    shape its tiling fits, see test_tc_gemm_vs_oracle)."""
     ctx, K, orc, _lib = env
     rng = np.random.default_rng(7 * m + n + k)
     x = H.f32_to_bf16_np(rng.standard_normal((m, k)).astype(np.float32))

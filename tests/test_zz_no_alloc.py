@@ -125,7 +125,7 @@ def test_static_rejects_what_the_array_cannot_hold(env):
     o = ctx.empty(case["q"].shape, np.uint16)
     big = dict(case)
     big["max_blocks"] = 1024                       # 16 K tokens per table row
-    big["ctx_lens"] = np.zeros(64, np.int32)       # 64 rows x 32 chunks x 16648 B > 16 MiB; only the size is read
+    big["ctx_lens"] = np.zeros(64, np.int32)       # 64 rows x 32 chunks x 16640 B > 16 MiB; only the size is read
     rc = _static(_lib, 0, big, d, 512, o)
     assert rc == -7
     msg = _lib.load().b2_last_error().decode()
