@@ -323,6 +323,13 @@ int32_t b2_tp_peer_reduce_residual(b2_tp_group* g, int32_t rows);
  * that wait on one another must not be separate launches on one device. */
 int32_t b2_tp_peer_attach_local(b2_tp_group* const* groups, int32_t n);
 int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, int32_t rows);
+/* One forward step (b2_model_step) of EVERY rank of a group attached with b2_tp_peer_attach_local, each rank with a model
+ * and a context of its own on the one device: every rank runs on a host thread of this call, the ranks meet at each
+ * reduction, and rank 0 enqueues the single launch that reduces for all of them.  caches is [n][num_seqs] (rank r's
+ * caches live in rank r's pool), logits_host [n][num_seqs][vocab] bf16 and argmax_host [n][num_seqs] are nullable.  For
+ * testing whole tensor-parallel models on one GPU. */
+int32_t b2_model_step_local_group(b2_model* const* models, int32_t n, const int32_t* ids_host, const int32_t* n_tokens,
+                                  int32_t num_seqs, b2_cache* const* caches, uint16_t* logits_host, int32_t* argmax_host);
 /* The two constructors with a group (NULL: the whole model, as without the suffix).  b2_model_get_config
  * still reports the WHOLE model's dimensions. */
 int32_t b2_model_from_weights_tp(b2_ctx* ctx, const b2_weights* w, const char* prefix, const b2_model_config* cfg,

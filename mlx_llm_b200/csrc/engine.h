@@ -44,6 +44,9 @@ struct b2_tp_group {
     size_t peer_x_off = 0, peer_slot_bytes = 0;
     bool peer_ready = false, peer_ipc = false, peer_push = false;
     uint32_t peer_seq = 0;  // number of the last reduction; every rank advances it in step
+    // ranks emulated inside one process on one device (b2_tp_peer_attach_local): the object that lets the ranks' host
+    // threads meet at every reduction, shared by the groups, owned by rank 0's
+    struct b2_tp_lockstep* lockstep = nullptr;
 };
 // In-place sum over the group of an f32 device buffer, enqueued on the context's stream.
 int32_t b2_tp_all_reduce_sum_f32(b2_tp_group* g, float* buf, size_t n);

@@ -27,8 +27,41 @@
 // kernel raises the context's error word and returns; later reductions see the word and return at once.
 #include <cooperative_groups.h>
 
+#include <chrono>
+#include <condition_variable>
+#include <mutex>
+#include <thread>
+
 #include "common.cuh"
 #include "engine.h"
+
+// Ranks emulated in one process (one host thread and one context each, all on one device) step in lock-step: at every
+// reduction the threads meet here, rank 0's thread enqueues ONE cooperative launch that reduces for all ranks (kernels
+// that wait on one another must never be separate launches on one device), and CUDA events order it after every rank's
+// projection and before every rank's next kernel.
+struct b2_tp_lockstep {
+    int n = 0;
+    b2_tp_group* groups[8] = {};
+    cudaEvent_t projected[8] = {};  // rank r's projection has been enqueued up to here
+    cudaEvent_t reduced = nullptr;  // the group's reduction
+    std::mutex mu;
+    std::condition_variable cv;
+    int waiting = 0;
+    uint64_t generation = 0;
+    int32_t status = B2_OK;         // rank 0's launch status, read by the others after the second meeting
+    // All n threads arrive, or the wait gives up after a few seconds (a rank's thread failed before the meeting point).
+    bool meet() {
+        std::unique_lock<std::mutex> lk(mu);
+        const uint64_t gen = generation;
+        if (++waiting == n) {
+            waiting = 0;
+            generation++;
+            cv.notify_all();
+            return true;
+        }
+        return cv.wait_for(lk, std::chrono::seconds(10), [&] { return generation != gen; });
+    }
+};
 
 namespace {
 
@@ -165,6 +198,25 @@ int32_t b2_tp_peer_reduce_residual_launch(b2_tp_group* g, int M) {
     B2_REQUIRE(g && g->peer_ready, B2_ERR_MSG, "peer reduction: the group has no attached peer regions");
     B2_REQUIRE(M >= 0 && M <= g->peer_cap_rows, B2_ERR_MSG, "peer reduction: more rows than the regions hold");
     if (M == 0) return B2_OK;
+    if (g->lockstep && g->lockstep->groups[0]->ctx != g->lockstep->groups[g->world - 1]->ctx) {
+        // emulated ranks, one host thread each: meet, let rank 0 enqueue the one launch that reduces for everybody,
+        // meet again; events carry the order onto the ranks' streams
+        b2_tp_lockstep* ls = g->lockstep;
+        B2_CUDA(cudaEventRecord(ls->projected[g->rank], g->ctx->stream));
+        if (!ls->meet()) return b2_fail(B2_ERR_TIMEOUT, "peer reduction: an emulated rank did not reach the reduction");
+        if (g->rank == 0) {
+            int32_t rc = B2_OK;
+            for (int r = 1; r < ls->n && rc == B2_OK; r++)
+                if (cudaStreamWaitEvent(g->ctx->stream, ls->projected[r], 0) != cudaSuccess) rc = b2_fail(B2_ERR_CUDA, "cudaStreamWaitEvent failed");
+            if (rc == B2_OK) rc = b2_tp_peer_reduce_residual_local(ls->groups, ls->n, M);
+            if (rc == B2_OK && cudaEventRecord(ls->reduced, g->ctx->stream) != cudaSuccess) rc = b2_fail(B2_ERR_CUDA, "cudaEventRecord failed");
+            ls->status = rc;
+        }
+        if (!ls->meet()) return b2_fail(B2_ERR_TIMEOUT, "peer reduction: an emulated rank did not reach the reduction");
+        if (ls->status != B2_OK) return g->rank == 0 ? ls->status : b2_fail(ls->status, "peer reduction: rank 0's launch failed");
+        if (g->rank != 0) B2_CUDA(cudaStreamWaitEvent(g->ctx->stream, ls->reduced, 0));
+        return B2_OK;
+    }
     PeerReduceParams p{};
     for (int s = 0; s < g->world; s++) p.base[s] = static_cast<unsigned char*>(g->peer_base[s]);
     p.rank = g->rank;
@@ -251,9 +303,18 @@ int32_t b2_tp_peer_attach_local(b2_tp_group* const* groups, int32_t n) {
                        groups[s]->peer_hidden == groups[0]->peer_hidden && groups[s]->peer_cap_rows == groups[0]->peer_cap_rows &&
                        groups[s]->ctx->device == groups[0]->ctx->device,
                    B2_ERR_MSG, "b2_tp_peer_attach_local: the groups must be ranks 0..n-1 of one group with equal regions on one device");
+    b2_tp_lockstep* ls = new b2_tp_lockstep();
+    ls->n = n;
+    B2_CUDA(cudaSetDevice(groups[0]->ctx->device));
+    B2_CUDA(cudaEventCreateWithFlags(&ls->reduced, cudaEventDisableTiming));
+    for (int s = 0; s < n; s++) {
+        ls->groups[s] = groups[s];
+        B2_CUDA(cudaEventCreateWithFlags(&ls->projected[s], cudaEventDisableTiming));
+    }
     for (int s = 0; s < n; s++) {
         for (int t = 0; t < n; t++) groups[s]->peer_base[t] = groups[t]->peer_local;
         groups[s]->peer_ready = true;
+        groups[s]->lockstep = ls;
     }
     return B2_OK;
 }
@@ -338,11 +399,52 @@ int32_t b2_tp_peer_reduce_residual_local(b2_tp_group* const* groups, int32_t n, 
     return B2_OK;
 }
 
+// One forward step of every emulated rank, each on a host thread of its own (b2_model_step per rank); the reductions
+// inside meet through the group's lock-step object.  models[r] must be rank r's model of a group attached with
+// b2_tp_peer_attach_local, every rank on a context of its own.
+int32_t b2_model_step_local_group(b2_model* const* models, int32_t n, const int32_t* ids_host, const int32_t* n_tokens, int32_t num_seqs,
+                                  b2_cache* const* caches, uint16_t* logits_host, int32_t* argmax_host) {
+    B2_REQUIRE(models && ids_host && n_tokens && caches && n >= 1 && n <= kMaxWorld, B2_ERR_MSG, "b2_model_step_local_group: bad argument");
+    for (int r = 0; r < n; r++) {
+        B2_REQUIRE(models[r] && models[r]->tp && models[r]->tp->lockstep && models[r]->tp->rank == r && models[r]->tp->world == n, B2_ERR_MSG,
+                   "b2_model_step_local_group: models[r] must be rank r of a group attached with b2_tp_peer_attach_local");
+        for (int q = 0; q < r; q++)
+            B2_REQUIRE(models[q]->ctx != models[r]->ctx, B2_ERR_MSG, "b2_model_step_local_group: every emulated rank needs a context of its own");
+    }
+    const int vocab = models[0]->cfg.vocab_size;
+    std::vector<int32_t> rc(n, B2_OK);
+    std::vector<std::string> msg(n);
+    std::vector<std::thread> th;
+    for (int r = 0; r < n; r++)
+        th.emplace_back([&, r]() {
+            rc[r] = b2_model_step(models[r], ids_host, n_tokens, num_seqs, const_cast<b2_cache**>(caches + (size_t)r * num_seqs),
+                                  logits_host ? logits_host + (size_t)r * num_seqs * vocab : nullptr, argmax_host ? argmax_host + (size_t)r * num_seqs : nullptr);
+            if (rc[r] != B2_OK) msg[r] = b2_last_error();
+        });
+    for (auto& t : th) t.join();
+    for (int r = 0; r < n; r++)
+        if (rc[r] != B2_OK) return b2_fail(rc[r], "rank " + std::to_string(r) + ": " + msg[r]);
+    return B2_OK;
+}
+
 }  // extern "C"
 
 void b2_tp_peer_release(b2_tp_group* g) {
     if (!g->peer_local) return;
     cudaStreamSynchronize(g->ctx->stream);
+    if (g->lockstep) {
+        b2_tp_lockstep* ls = g->lockstep;
+        for (int r = 0; r < ls->n; r++)
+            if (ls->groups[r] == g) ls->groups[r] = nullptr;
+        bool last = true;
+        for (int r = 0; r < ls->n; r++) last = last && ls->groups[r] == nullptr;
+        g->lockstep = nullptr;
+        if (last) {
+            for (int r = 0; r < ls->n; r++) cudaEventDestroy(ls->projected[r]);
+            cudaEventDestroy(ls->reduced);
+            delete ls;
+        }
+    }
     if (g->peer_ipc)
         for (int s = 0; s < g->world; s++)
             if (s != g->rank && g->peer_base[s]) cudaIpcCloseMemHandle(g->peer_base[s]);

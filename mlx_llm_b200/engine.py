@@ -194,6 +194,23 @@ class CausalLm:
             self.h = C.c_void_p()
 
 
+def step_local_group(models, seqs_per_rank, want_logits=True):
+    """One forward of every emulated rank of a group attached with TpGroup.peer_attach_local (b2_model_step_local_group).
+    seqs_per_rank[r] is rank r's list of (ids, PagedKvCache) -- the same ids on every rank, each rank's own caches.
+    Returns (logits [n, B, vocab] bf16 as uint16 or None, argmax [n, B])."""
+    n, B = len(models), len(seqs_per_rank[0])
+    ids = np.concatenate([np.ascontiguousarray(s[0], np.int32) for s in seqs_per_rank[0]])
+    ntok = np.array([len(s[0]) for s in seqs_per_rank[0]], np.int32)
+    marr = (C.c_void_p * n)(*[m.h for m in models])
+    carr = (C.c_void_p * (n * B))(*[s[1].h for seqs in seqs_per_rank for s in seqs])
+    vocab = models[0].config().vocab_size
+    logits = np.empty((n, B, vocab), np.uint16) if want_logits else None
+    am = np.empty((n, B), np.int32)
+    check(load().b2_model_step_local_group(marr, n, ids.ctypes.data_as(C.c_void_p), ntok.ctypes.data_as(C.c_void_p), B, carr,
+                                           logits.ctypes.data_as(C.c_void_p) if want_logits else None, am.ctypes.data_as(C.c_void_p)))
+    return logits, am
+
+
 def write_snapshot(ctx, weights, config_json, out_dir, quant: Optional[QuantSpec] = None):
     """write_snapshot (src/snapshot.rs:86-148): dense tensors -> out_dir/{model.safetensors, config.json}, the
     projections re-quantized to MLX Q4/Q8 triplets when `quant` is given.  Returns the number of tensors written."""

@@ -104,3 +104,59 @@ def replica_requests(requests_per_replica, rank, world, rate_per_replica, **kw):
     if not (0 <= rank < world):
         raise ValueError(f"rank {rank} outside world of {world}")
     return wl.serving_requests(n=requests_per_replica, rate=rate_per_replica, **kw)
+
+
+class RankLost(RuntimeError):
+    """A rank of the group did not announce the step the others are about to launch."""
+
+
+class StepWatch:
+    """Host-side failure detection for ranks that step in lock-step (the tensor-parallel group: every rank launches the
+    same forward, whose reductions wait on every other rank).  Before each step a rank announces it in a key-value
+    store and looks for every peer's announcement; a peer that has left, crashed or hung on the host is then found
+    within `timeout_s` BEFORE anything that would wait for it is launched, and the survivors stop with RankLost between
+    steps, with no kernel or collective in flight.  (On the device every such wait is bounded as well -- see
+    b2_ctx_set_wait_limit_ms -- but the host check keeps the group from ever entering it.)  The reference has no
+    counterpart: it is a single-device program whose only failure path is cooperative cancel
+    (src/decode/continuous.rs:138-140, :198-214).
+
+    `store` is a torch.distributed store (TCPStore, FileStore, or the default store of an initialised process group)."""
+
+    def __init__(self, store, rank, world, timeout_s=5.0, poll_s=0.01):
+        self.store, self.rank, self.world, self.timeout_s, self.poll_s = store, rank, world, timeout_s, poll_s
+
+    def announce(self, step):
+        self.store.set(f"b2/step/{self.rank}", str(int(step)))
+
+    def leave(self):
+        """An orderly exit between steps: peers see it at once instead of after the timeout."""
+        self.store.set(f"b2/step/{self.rank}", "-1")
+
+    def _peer_step(self, r):
+        import datetime
+
+        key = f"b2/step/{r}"
+        try:
+            self.store.wait([key], datetime.timedelta(seconds=self.poll_s))
+        except Exception:  # the key does not exist yet
+            return None
+        return int(self.store.get(key).decode())
+
+    def ready(self, step):
+        """Announce `step`, then return once every peer has announced it too; raise RankLost otherwise."""
+        import time
+
+        self.announce(step)
+        deadline = time.monotonic() + self.timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            while True:
+                s = self._peer_step(r)
+                if s is not None and s < 0:
+                    raise RankLost(f"rank {r} left the group before step {step}")
+                if s is not None and s >= step:
+                    break
+                if time.monotonic() > deadline:
+                    raise RankLost(f"rank {r} did not announce step {step} within {self.timeout_s} s (last seen: {s})")
+                time.sleep(self.poll_s)

@@ -1,6 +1,7 @@
 """Tensor parallelism over KV heads on two GPUs: a rank-per-process group whose logits and greedy tokens must
-match the single-GPU model on the same weights (the only difference is the order of the f32 sums in o_proj
-and down_proj), for synthetic slices, for slices cut from a whole checkpoint, dense and quantized.
+match the CPU oracle's (whole model, same weights) and the single-GPU engine's (the only difference to the latter
+is the order of the f32 sums in o_proj and down_proj), for synthetic slices, for slices cut from a whole checkpoint,
+dense and quantized, with the reductions done by NCCL and by the kernel over peer memory.
 Needs two GPUs; skipped otherwise."""
 import os
 import sys
@@ -39,6 +40,16 @@ def _run_steps(eng, model, ctx, prompts):
         c.free()
     pool.free()
     return np.asarray(logits), toks, np.asarray(l2)
+
+
+def _oracle_steps(orc, omodel, prompts, toks):
+    """The oracle over the same schedule, fed the engine's own greedy tokens: (prefill logits, last decode logits)."""
+    caches = [orc.Cache(TP_CFG["layers"], block_size=16) for _ in prompts]
+    _, lg = omodel.forward([(p, c, 0) for p, c in zip(prompts, caches)])
+    l2 = None
+    for step in range(4):
+        _, l2 = omodel.forward([([t[step]], c, c.offset()) for t, c in zip(toks, caches)])
+    return lg, l2
 
 
 def _worker(rank, world, uid_q, q, inboxes):
@@ -129,6 +140,14 @@ def test_tp2_matches_single_gpu():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert res[0]["sum_ok"] and res[1]["sum_ok"] and res[0]["sum"] == 3.0
+    from oracle import oracle as orc
+
+    prompts = H.config0_prompts(lens=(17, 33, 64, 129))
+    oracle_models = {}
+    for name, bits in (("dense", 0), ("q8", 8), ("q4", 4)):
+        oracle_models[name] = H.build_oracle_model(orc, TP_CFG, quant_bits=bits)
+    oracle_models["synthetic"] = orc.Model(**dict(TP_CFG, quant_bits=8))
+    oracle_models["synthetic"].fill_synthetic(3)
     assert res[0]["peer_ok"] and res[1]["peer_ok"], "the peer regions could not be mapped on a two-GPU box"
     for name in ("dense", "q8", "q4", "synthetic", "dense_peer", "q4_peer", "q4_push"):
         lg0, tok0, d0 = res[0][name]
@@ -144,3 +163,8 @@ def test_tp2_matches_single_gpu():
             assert np.sqrt(np.mean(err * err)) <= 2e-3 and err.max() <= 1e-2, (name, float(err.max()))
         agree = sum(a == b for ta, tb in zip(tok0, ref_tok) for a, b in zip(ta, tb))
         assert agree >= 18, (name, tok0, ref_tok)  # 20 greedy tokens; a near-tie may flip under reordered sums
+        # against the oracle: the whole model on the CPU, fed this group's own tokens
+        o_lg, o_l2 = _oracle_steps(orc, oracle_models[name.replace("_peer", "").replace("_push", "")], prompts, tok0)
+        for got, ref in ((lg0, o_lg), (d0, o_l2)):
+            err = np.abs(H.bf16_to_f32_np(got) - ref)
+            assert np.sqrt(np.mean(err * err)) <= 2e-3 and err.max() <= 1e-2, (name, "oracle", float(err.max()))

@@ -97,3 +97,59 @@ def test_cpu_legs_take_every_core_they_may_use():
     out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, OMP_NUM_THREADS="1"), capture_output=True, text=True, check=True)
     before, after, cores = (int(x) for x in out.stdout.split())
     assert before == 1 and after == cores
+
+
+def _tp_worker(rank, world, port, q, die_at, how):
+    """A rank of a lock-step group on CPU: every step is announce -> all-reduce (stand-in for the forward's reductions)."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    from mlx_llm_b200 import replica
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    store = dist.TCPStore("127.0.0.1", port + 1, world, rank == 0, timeout=datetime.timedelta(seconds=20))
+    watch = replica.StepWatch(store, rank, world, timeout_s=1.5)
+    done, err = 0, None
+    try:
+        for step in range(8):
+            if rank == 1 and step == die_at:
+                if how == "leave":
+                    watch.leave()
+                break                                  # "crash": simply stops announcing
+            watch.ready(step)                          # nothing that waits on a peer is launched before this returns
+            t = torch.ones(4) * (rank + 1)
+            dist.all_reduce(t)
+            assert float(t[0]) == sum(range(1, world + 1))
+            done += 1
+    except replica.RankLost as e:
+        err = str(e)
+    q.put((rank, done, err))
+    # no destroy_process_group: a lost peer would make it wait
+
+
+@pytest.mark.parametrize("how", ["crash", "leave"])
+def test_lost_rank_is_detected_between_steps(how):
+    import time
+
+    import torch.multiprocessing as mp
+
+    world, port = 3, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    t0 = time.time()
+    procs = [ctx.Process(target=_tp_worker, args=(r, world, port, q, 3, how)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict((r, (done, err)) for r, done, err in (q.get(timeout=120) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=60)
+    assert res[1] == (3, None)                          # the rank that goes away did three steps
+    for r in (0, 2):                                    # the survivors did the same three, then stopped with a typed error,
+        done, err = res[r]                              # never entering the fourth step's collective
+        assert done == 3 and err is not None and "rank 1" in err and "step 3" in err, res
+    assert ("left the group" in res[0][1]) == (how == "leave")
+    assert time.time() - t0 < 60
