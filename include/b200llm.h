@@ -147,6 +147,11 @@ int32_t b2_unpack_codes(b2_ctx* ctx, const uint32_t* packed_dev, int64_t out_dim
 int32_t b2_qmm(b2_ctx* ctx, const uint16_t* x_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
                const uint16_t* biases_dev, int32_t m, int32_t out_dim, int32_t in_dim, int32_t group, int32_t bits,
                uint16_t* y_bf16_dev, float* y_f32_dev);
+/* h[m, out] = bf16(h + bf16(x @ dequant(W)^T)), in place: the residual add of LlamaLayer::forward
+ * (src/models/llama.rs:730-732) fused into the projection's epilogue, as the engine runs o_proj and down_proj. */
+int32_t b2_qmm_residual(b2_ctx* ctx, const uint16_t* x_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
+                        const uint16_t* biases_dev, int32_t m, int32_t out_dim, int32_t in_dim, int32_t group, int32_t bits,
+                        uint16_t* h_dev);
 /* The same call with HOST activations and a HOST bf16 result (pinned or pageable): copies x in, multiplies, copies y
  * back and waits for the stream. */
 int32_t b2_qmm_host(b2_ctx* ctx, const uint16_t* x_host, const uint32_t* packed_dev, const uint16_t* scales_dev,

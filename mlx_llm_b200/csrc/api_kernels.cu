@@ -87,6 +87,30 @@ int32_t b2_qmm(b2_ctx* ctx, const uint16_t* x_dev, const uint32_t* packed_dev, c
     return gemm_both(ctx, p, y_bf16_dev, y_f32_dev);
 }
 
+// h = h + x @ dequant(W)^T with the residual add fused into the projection's epilogue, in place.
+int32_t b2_qmm_residual(b2_ctx* ctx, const uint16_t* x_dev, const uint32_t* packed_dev, const uint16_t* scales_dev, const uint16_t* biases_dev,
+                        int32_t m, int32_t out_dim, int32_t in_dim, int32_t group, int32_t bits, uint16_t* h_dev) {
+    B2_REQUIRE(ctx && x_dev && packed_dev && scales_dev && biases_dev && h_dev, B2_ERR_MSG, "b2_qmm_residual: null argument");
+    B2_REQUIRE(bits == 4 || bits == 8, B2_ERR_UNSUPPORTED, "b2_qmm_residual: bits must be 4 or 8");
+    GemmParams p{};
+    p.x = x_dev;
+    p.w = packed_dev;
+    p.scales = scales_dev;
+    p.biases = biases_dev;
+    p.bits = bits;
+    p.group = group;
+    p.M = m;
+    p.N = out_dim;
+    p.K = in_dim;
+    p.ldx = in_dim;
+    p.ldo = out_dim;
+    p.ldres = out_dim;
+    p.epilogue = EPI_BF16_RESADD;
+    p.out = h_dev;
+    p.res = h_dev;
+    return b2_gemm_launch(ctx, p);
+}
+
 // The same with HOST activations and a host result (pinned or pageable): x in, kernel, y out, then a stream sync.
 int32_t b2_qmm_host(b2_ctx* ctx, const uint16_t* x_host, const uint32_t* packed_dev, const uint16_t* scales_dev, const uint16_t* biases_dev,
                     int32_t m, int32_t out_dim, int32_t in_dim, int32_t group, int32_t bits, uint16_t* y_bf16_host) {

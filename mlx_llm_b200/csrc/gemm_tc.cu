@@ -51,7 +51,9 @@ constexpr int RING_BYTES = 192 * 1024;  // 4 stages of (A + 2 units) for two-blo
 constexpr int BOX_BIG = 128, BOX_SMALL = 32;  // token rows per TMA box (one big box, or up to two small ones)
 constexpr int A_BYTES = TM * TK * 2, UNIT_BYTES = 128 * TK * 2;  // unit: 128 token rows x 64 K, one MMA instruction's B half
 constexpr int kProducerWarps = 16, kProducerThreads = kProducerWarps * 32;
-// warps: 16 producers, one for TMA, two MMA issuers (the second shares the slabs of one-block pieces)
+// warps: 16 producers (which also run the epilogue), one for TMA, two MMA issuers (the second shares the slabs of
+// one-block pieces)
+constexpr int kDequantWarps = kProducerWarps;
 constexpr int kTmaWarp = kProducerWarps, kMmaWarp = kProducerWarps + 1, kThreads = kProducerThreads + 96;
 constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t kSpinLimit = 64;  // try_wait attempts between two looks at the clock
@@ -197,7 +199,8 @@ __device__ __forceinline__ void dequant4_q8(uint32_t w, float s, float b, uint32
 // of cost; every pair gets a contiguous run of blocks, equal to within one.
 struct PairPlan {
     int n_pairs;          // CTA pairs launched
-    int blocks_per_tile;  // ceil(M / 256)
+    int block_tokens;     // tokens per block: a multiple of 16, at most 256 (the last block of a tile may hold fewer)
+    int blocks_per_tile;  // ceil(M / block_tokens)
     int total_blocks;     // ceil(N / 256) * blocks_per_tile
     int splits;           // K ranges per block (> 1 only when the blocks alone cannot occupy the pairs)
     float* partial;       // [splits, M, N] f32 partial sums when splits > 1
@@ -227,7 +230,7 @@ __device__ __forceinline__ uint32_t ring_advance(uint32_t par, int KT, int NS) {
 }
 // Work units are numbered block-major: unit = block * splits + K range.  Without split-K two consecutive
 // token blocks of a tile are taken together when the pair owns both.
-__device__ __forceinline__ Piece piece_at(int unit, int unit_end, int bpt, int M, int KT, int splits) {
+__device__ __forceinline__ Piece piece_at(int unit, int unit_end, int bpt, int bs, int M, int KT, int splits) {
     Piece pc;
     const int blk = unit / splits;
     pc.split = unit - blk * splits;
@@ -236,12 +239,12 @@ __device__ __forceinline__ Piece piece_at(int unit, int unit_end, int bpt, int M
     pc.fp = blk / bpt;
     const int tb = blk % bpt;
     pc.blocks = (splits == 1 && tb + 1 < bpt && unit + 1 < unit_end) ? 2 : 1;
-    pc.t0 = tb * 256;
+    pc.t0 = tb * bs;
     int cnt = M - pc.t0;
-    if (cnt > 256 * pc.blocks) cnt = 256 * pc.blocks;
+    if (cnt > bs * pc.blocks) cnt = bs * pc.blocks;
     pc.cnt = cnt;
     const int padded = (cnt + 15) & ~15;
-    pc.n0 = padded < 256 ? padded : 256;
+    pc.n0 = padded < bs ? padded : bs;
     pc.n1 = padded - pc.n0;
     return pc;
 }
@@ -268,14 +271,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const int pair = blockIdx.x >> 1;
     const int M = p.M, N = p.N, K = p.K;
     const int KT = K / TK;
-    const int bpt = plan.blocks_per_tile;
+    const int bpt = plan.blocks_per_tile, bs = plan.block_tokens;
     const int splits = plan.splits;
     const int total_units = plan.total_blocks * splits;
     const int blk_begin = (int)((long)pair * total_units / plan.n_pairs);  // first work unit of this pair
     const int blk_end = (int)((long)(pair + 1) * total_units / plan.n_pairs);
     // arrivals per stage on the leader's "full" barrier: the four warps that fill the A slab in each CTA
     // (quantised weights only) plus the leader's TMA thread (arrive.expect_tx for both CTAs' bytes)
-    constexpr uint32_t kFullCount = (WK != 0 ? 2 * (kProducerWarps / GROUPS) : 0) + 1;
+    constexpr uint32_t kFullCount = (WK != 0 ? 2 * (kDequantWarps / GROUPS) : 0) + 1;
     const uint32_t leader_accum_empty = map_to_cta(accum_empty, 0);
 
     if (tid == 0) {
@@ -302,7 +305,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         // Four groups of four warps; group g dequantises every 4th K slab, one thread per feature row (64
         // codes, one scale and one bias per slab).  While one group waits for its slot or for its barrier
         // arrive to travel to the leader CTA, the other three keep dequantising.
-        static_assert(kProducerWarps == 4 * GROUPS, "four warps per producer group");
+        static_assert(kDequantWarps == 4 * GROUPS, "four warps per producer group");
+        constexpr bool dequantises = true;
         const int grp = warp >> 2, row = tid & 127;
         const int groups = K / 64;
         const int lane_grp = warp & 3, col_grp = warp >> 2;
@@ -312,37 +316,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         uint32_t n_piece = 0;
         bool alive = true;
         for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
-            const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
+            const Piece pc = piece_at(blk, blk_end, bpt, bs, M, KT, splits);
             blk += pc.blocks;
             const int NS = ring_stages(pc);
             const uint32_t SB = ring_stage_bytes(pc);
-            if (WK != 0) {
+            if (WK != 0 && dequantises) {
                 const int gn = pc.fp * PAIR_F + (int)rank * TM + row;
                 const bool row_ok = gn < N;  // rows past N contribute exact zeros
                 const uint4* wq = reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p.w) + (size_t)(row_ok ? gn : 0) * (K * WK / 32));
                 const uint16_t* sc_row = p.scales + (size_t)(row_ok ? gn : 0) * groups;
                 const uint16_t* bi_row = p.biases + (size_t)(row_ok ? gn : 0) * groups;
                 constexpr int NQ = WK == 4 ? 2 : 4;  // 16-byte loads per 64 codes
-                uint4 q[NQ];
-                uint32_t sb = 0;
-                auto load_codes = [&](int kb) {
+                // Codes, scale and bias of the next DEPTH slabs of this group wait in registers (DEPTH * GROUPS slabs
+                // ahead of the one being dequantised): the loads come from DRAM or a busy L2, and with a single slab
+                // in flight per thread the group's period was that latency, not the arithmetic.
+                constexpr int DEPTH = 1;
+                uint4 q[DEPTH][NQ];
+                uint32_t sb[DEPTH];
+                auto load_codes = [&](int d, int kb) {
 #pragma unroll
-                    for (int i = 0; i < NQ; i++) q[i] = row_ok ? __ldg(wq + kb * NQ + i) : make_uint4(0, 0, 0, 0);
-                    sb = row_ok ? ((uint32_t)__ldg(sc_row + kb) | ((uint32_t)__ldg(bi_row + kb) << 16)) : 0u;
+                    for (int i = 0; i < NQ; i++) q[d][i] = row_ok ? __ldg(wq + kb * NQ + i) : make_uint4(0, 0, 0, 0);
+                    sb[d] = row_ok ? ((uint32_t)__ldg(sc_row + kb) | ((uint32_t)__ldg(bi_row + kb) << 16)) : 0u;
                 };
                 // first K slab of this piece that belongs to this group
-                int kb = (int)((grp + GROUPS - (it_global % GROUPS)) % GROUPS);  // slab index within the piece
-                if (kb < pc.nk) load_codes(pc.k0 + kb);
+                int kb0 = (int)((grp + GROUPS - (it_global % GROUPS)) % GROUPS);  // slab index within the piece
+#pragma unroll
+                for (int d = 0; d < DEPTH; d++)
+                    if (kb0 + d * GROUPS < pc.nk) load_codes(d, pc.k0 + kb0 + d * GROUPS);
                 const uint32_t sw = (uint32_t)(row & 7);
-                for (; kb < pc.nk; kb += GROUPS) {
+                for (; kb0 < pc.nk && alive; kb0 += GROUPS * DEPTH) {
+#pragma unroll
+                  for (int d = 0; d < DEPTH; d++) {
+                    const int kb = kb0 + d * GROUPS;
+                    if (kb >= pc.nk) break;
                     const int st = kb % NS;
                     const uint32_t ph = ((par >> st) ^ (uint32_t)(kb / NS)) & 1u;
                     const uint32_t sA = base + st * SB + row * 128;
                     uint4 cd[NQ];
 #pragma unroll
-                    for (int i = 0; i < NQ; i++) cd[i] = q[i];
-                    const uint32_t csc = sb & 0xffffu, cbi = sb >> 16;
-                    if (kb + GROUPS < pc.nk) load_codes(pc.k0 + kb + GROUPS);
+                    for (int i = 0; i < NQ; i++) cd[i] = q[d][i];
+                    const uint32_t csc = sb[d] & 0xffffu, cbi = sb[d] >> 16;
+                    if (kb + GROUPS * DEPTH < pc.nk) load_codes(d, pc.k0 + kb + GROUPS * DEPTH);
                     // the verdict is taken warp-wide so that no lane leaves the others at the __syncwarp below
                     if (!__all_sync(0xffffffffu, mbar_wait(empty(st), ph ^ 1u))) {
                         alive = false;
@@ -381,6 +395,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         else
                             mbar_arrive_cluster(leader_full0 + 8u * st);
                     }
+                  }
+                }
+                // the first lines of the next piece's weight rows start their way into L2 while this piece drains
+                if (blk < blk_end) {
+                    const Piece nx = piece_at(blk, blk_end, bpt, bs, M, KT, splits);
+                    const int gx = nx.fp * PAIR_F + (int)rank * TM + row;
+                    if (gx < N && (nx.fp != pc.fp || nx.k0 != pc.k0) && nx.k0 * (NQ * 16) + grp * 128 < K * WK / 8) {
+                        const uint8_t* line = reinterpret_cast<const uint8_t*>(p.w) + ((size_t)gx * (K * WK / 32) + (size_t)nx.k0 * (NQ * 4)) * 4 + grp * 128;
+                        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(line));
+                    }
                 }
             }
             it_global += (uint32_t)pc.nk;
@@ -390,6 +414,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             // ---------------- epilogue of this piece ----------------
             // (the residual it reads and the buffers it writes belong to earlier kernels until they have completed)
             if (n_piece == 0) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            // The residual rows of a 32-token column group are fetched a group ahead, all 32 in flight at once and the
+            // first group before the accumulator is waited for: in place (out == res) the compiler must otherwise order
+            // every load behind the store before it, and each load would pay the whole trip to L2.
+            const int f = pc.fp * PAIR_F + (int)rank * TM + lane_grp * 32 + lane;
+            // 32-column groups of the piece: those of the first block (TMEM columns from 0), then those of the second
+            // (columns from 256, tokens from t0 + block size)
+            const int cnt0 = pc.cnt < bs ? pc.cnt : bs, cnt1 = pc.cnt - cnt0;
+            const int grp0 = (cnt0 + 31) >> 5, grps = grp0 + ((cnt1 + 31) >> 5);
+            uint32_t r2[16];
+            auto load_res = [&](int g) {
+                if (EPI == EPI_BF16_RESADD && splits == 1 && f < N && g < grps) {
+                    const int tg = g < grp0 ? pc.t0 + g * 32 : pc.t0 + bs + (g - grp0) * 32;
+                    const int left = g < grp0 ? cnt0 - g * 32 : cnt1 - (g - grp0) * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const uint32_t lo = i < left ? p.res[(size_t)(tg + i) * p.ldres + f] : 0u;
+                        const uint32_t hi = i + 1 < left ? p.res[(size_t)(tg + i + 1) * p.ldres + f] : 0u;
+                        r2[i >> 1] = lo | (hi << 16);
+                    }
+                }
+            };
+            load_res(col_grp);
             bool ok = mbar_wait(accum_full, n_piece & 1u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -397,22 +443,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after();
-            const int f = pc.fp * PAIR_F + (int)rank * TM + lane_grp * 32 + lane;
 #pragma unroll 1
-            for (int j = col_grp; j * 32 < pc.cnt; j += kProducerWarps / 4) {
+            for (int g = col_grp; g < grps; g += kProducerWarps / 4) {
+                const int col = g < grp0 ? g * 32 : 256 + (g - grp0) * 32;
+                const int tg = g < grp0 ? pc.t0 + g * 32 : pc.t0 + bs + (g - grp0) * 32;
+                const int left = g < grp0 ? cnt0 - g * 32 : cnt1 - (g - grp0) * 32;
                 uint32_t v[32];
-                tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(j * 32), v);
+                tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)col, v);
                 if (pc.n1 == 0 && pc.nk > 1) {  // one block: the sums of the odd K slabs sit 256 columns further
                     uint32_t w[32];
-                    tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + 256u + (uint32_t)(j * 32), w);
+                    tc_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + 256u + (uint32_t)col, w);
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
                 }
                 if (f < N) {
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
-                        if (j * 32 + i >= pc.cnt) break;
-                        const int t = pc.t0 + j * 32 + i;
+                        if (i >= left) break;
+                        const int t = tg + i;
                         const float a = __uint_as_float(v[i]);
                         if (splits > 1) {
                             plan.partial[((size_t)pc.split * M + t) * N + f] = a;
@@ -421,10 +469,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         } else if (EPI == EPI_BF16) {
                             p.out[(size_t)t * p.ldo + f] = f2bf(a);
                         } else {
-                            p.out[(size_t)t * p.ldo + f] = f2bf(bf2f(p.res[(size_t)t * p.ldres + f]) + rbf(a));
+                            const uint32_t rr = r2[i >> 1];
+                            p.out[(size_t)t * p.ldo + f] = f2bf(((i & 1) ? bfhi(rr) : bflo(rr)) + rbf(a));
                         }
                     }
                 }
+                load_res(g + kProducerWarps / 4);
             }
             tc_fence_before();
             __syncwarp();
@@ -445,7 +495,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             // activations are that kernel's output.
             asm volatile("griddepcontrol.wait;\n" ::: "memory");
             for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
-                const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
+                const Piece pc = piece_at(blk, blk_end, bpt, bs, M, KT, splits);
                 blk += pc.blocks;
                 const int NS = ring_stages(pc);
                 const uint32_t SB = ring_stage_bytes(pc);
@@ -464,7 +514,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const uint32_t bb0 = (uint32_t)(big0 ? BOX_BIG : BOX_SMALL) * 128u, bb1 = (uint32_t)(big1 ? BOX_BIG : BOX_SMALL) * 128u;
                 const CUtensorMap* m0 = big0 ? &map_x : &map_x_small;
                 const CUtensorMap* m1 = big1 ? &map_x : &map_x_small;
-                const int y0 = pc.t0 + (int)rank * h0, y1 = pc.t0 + 256 + (int)rank * h1;
+                const int y0 = pc.t0 + (int)rank * h0, y1 = pc.t0 + bs + (int)rank * h1;
                 const uint32_t tx = 2u * ((uint32_t)nb0 * bb0 + (uint32_t)nb1 * bb1 + (WK == 0 ? (uint32_t)A_BYTES : 0u));
                 for (int kb = 0; kb < pc.nk; kb++) {
                     const int st = kb % NS;
@@ -502,7 +552,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             uint32_t par = 0, n_piece = 0;
             bool alive = true;
             for (int blk = blk_begin; blk < blk_end && alive; n_piece++) {
-                const Piece pc = piece_at(blk, blk_end, bpt, M, KT, splits);
+                const Piece pc = piece_at(blk, blk_end, bpt, bs, M, KT, splits);
                 blk += pc.blocks;
                 const int NS = ring_stages(pc);
                 const uint32_t SB = ring_stage_bytes(pc);
@@ -681,7 +731,8 @@ template <int WK, int EPI>
 int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
     B2_SMEM_ONCE(ctx, (gemm_tc_pair_kernel<WK, EPI>), SMEM_BYTES);
     PairPlan plan{};
-    plan.blocks_per_tile = (p.M + 255) / 256;
+    plan.block_tokens = 256;
+    plan.blocks_per_tile = (p.M + plan.block_tokens - 1) / plan.block_tokens;
     plan.total_blocks = ((p.N + PAIR_F - 1) / PAIR_F) * plan.blocks_per_tile;
     const int max_pairs = ctx->sm_count / 2;
     // Split K only when the blocks cannot occupy the pairs (down_proj at a few hundred tokens).  Cost model in K
@@ -733,7 +784,13 @@ int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B2_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<WK, EPI>, p, plan, map_x, map_s, map_w));
+    // with split K the pair kernel only writes partial sums: the residual variant's extra registers buy nothing there
+    if (best > 1 && EPI == EPI_BF16_RESADD) {
+        B2_SMEM_ONCE(ctx, (gemm_tc_pair_kernel<WK, EPI_BF16>), SMEM_BYTES);
+        B2_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<WK, EPI_BF16>, p, plan, map_x, map_s, map_w));
+    } else {
+        B2_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<WK, EPI>, p, plan, map_x, map_s, map_w));
+    }
     B2_LAUNCHED(ctx);
     if (best > 1) {
         const size_t total = (size_t)p.M * p.N;

@@ -48,6 +48,11 @@ def qmm(ctx, x, packed, scales, biases, m, out_dim, in_dim, bits, y_bf16=None, y
                         int(bits), ptr(y_bf16), ptr(y_f32)))
 
 
+def qmm_residual(ctx, x, packed, scales, biases, m, out_dim, in_dim, bits, h, group=64):
+    check(load().b2_qmm_residual(ctx.h, ptr(x), ptr(packed), ptr(scales), ptr(biases), int(m), int(out_dim), int(in_dim), int(group),
+                                 int(bits), ptr(h)))
+
+
 def qmm_host(ctx, x_host, packed, scales, biases, m, out_dim, in_dim, bits, y_host, group=64):
     check(load().b2_qmm_host(ctx.h, ptr(x_host), ptr(packed), ptr(scales), ptr(biases), int(m), int(out_dim), int(in_dim), int(group),
                              int(bits), ptr(y_host)))
