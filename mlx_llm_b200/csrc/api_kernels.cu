@@ -352,6 +352,8 @@ int32_t b2_paged_attn_prefill(b2_ctx* ctx, const uint16_t* q_dev, const uint16_t
         }
         p.pool_rows = ((int64_t)max_page + 1) * hkv * page_size;
     }
+    for (int i = 0; i < num_seqs; i++)
+        if (cu_seqlens_host[i + 1] > cu_seqlens_host[i]) p.max_ctx = std::max(p.max_ctx, (int)ctx_lens_host[i]);
     return b2_prefill_attn_launch(ctx, p, head_dim, P);
 }
 

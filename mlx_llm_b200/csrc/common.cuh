@@ -46,6 +46,8 @@ struct b2_ctx {
     size_t stage_bytes = 0;
     // tcgen05 GEMM: split-K partial sums and the device error word its bounded waits raise
     float* tc_partial = nullptr;
+    float* pf_part = nullptr;        // prefill attention split over keys: f32 partial outputs, maxima and sums
+    size_t pf_part_bytes = 0;
     size_t tc_partial_bytes = 0;
     int* dev_err = nullptr;        // raised by a bounded device-side wait that gave up (allocated with the context)
     int* err_host = nullptr;       // pinned copy the engine step reads back with its sampled ids

@@ -65,6 +65,7 @@ int32_t b2_ctx_free(b2_ctx* ctx) {
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->tc_partial) cudaFree(ctx->tc_partial);
+    if (ctx->pf_part) cudaFree(ctx->pf_part);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
     if (ctx->tile_counters) cudaFree(ctx->tile_counters);

@@ -150,7 +150,7 @@ int pick_chunk_tiles(long dec_ctx_sum, int hkv, int sm_count) {
 
 // The bf16 layers of one step: embedding, every decoder layer, the sampled rows' final norm, lm_head and argmax.
 int32_t forward_bf16_layers(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, const BatchMetaIn& in, const int32_t* ids_dev, int T, int n_dec,
-                            long dec_ctx_sum, int W, int P, double pf_flops, int chunk_tiles, int q_tile, int n_logits, const int32_t* logit_rows) {
+                            long dec_ctx_sum, int W, int P, double pf_flops, int pf_max_ctx, int chunk_tiles, int q_tile, int n_logits, const int32_t* logit_rows) {
     b2_ctx* ctx = m->ctx;
     const b2_model_config& c = m->cfg;
     Workspace& w = m->ws;
@@ -235,6 +235,7 @@ int32_t forward_bf16_layers(b2_model* m, b2_pool* pool, const BatchMetaOut& mo, 
             pp.q_tile = q_tile;
             pp.q_rows = w.t_cap;
             pp.pool_rows = (int64_t)pool->max_pages * hkv * pool->block_size;
+            pp.max_ctx = pf_max_ctx;
             b2_prof_mark(ctx, B2_CLS_ATTN_PREFILL);
             B2_CHECK(b2_prefill_attn_launch(ctx, pp, hd, P));
             ctx->attn_prefill_flops += pf_flops;
@@ -312,7 +313,9 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
     const int q_tile = b2_prefill_q_tile(ctx, c.head_dim);
     int W = 0, P = 0;
     double pf_flops = 0;  // 4*hd*hq flops per (query, visible key) pair
+    int pf_max_ctx = 0;   // longest context among the sequences that prefill in this step
     for (auto& s : seqs) {
+        if (s.n > 1) pf_max_ctx = std::max(pf_max_ctx, s.cache->len + s.n);
         if (s.n > 1) pf_flops += 4.0 * c.head_dim * m->hq_l * ((double)s.n * s.cache->len + 0.5 * (double)s.n * (s.n + 1));
         if (s.n == 1) {
             const int tiles = (s.cache->len + 1 + 15) / 16;
@@ -380,7 +383,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
     if (m->f32) {
         B2_CHECK(b2_forward_f32(m, pool, mo, in.seq_slot, ids_dev, T, B, n_logits, all_positions ? nullptr : mo.logit_rows, max_pos, &logits_f32_dev));
     } else {
-        B2_CHECK(forward_bf16_layers(m, pool, mo, in, ids_dev, T, n_dec, dec_ctx_sum, W, P, pf_flops, chunk_tiles, q_tile, n_logits,
+        B2_CHECK(forward_bf16_layers(m, pool, mo, in, ids_dev, T, n_dec, dec_ctx_sum, W, P, pf_flops, pf_max_ctx, chunk_tiles, q_tile, n_logits,
                                      all_positions ? nullptr : mo.logit_rows));
     }
     if (n_logits > 0) {

@@ -169,6 +169,7 @@ struct PrefillAttnParams {
     int q_tile;                  // queries per work item: b2_prefill_q_tile() at the time the work list was built
     int q_rows;                  // rows of the q allocation (>= T)
     int64_t pool_rows;           // rows of one layer's K (or V) pool = pages * hkv * page_size (or any bound >= it)
+    int max_ctx;                 // host's bound on the contexts of this launch (0: unknown): lets few, long work items be split over keys
 };
 // 128 when the tcgen05 kernel (paged_attn_prefill_tc.cu) will take the launch, else 64.
 int b2_prefill_q_tile(const b2_ctx* ctx, int head_dim);

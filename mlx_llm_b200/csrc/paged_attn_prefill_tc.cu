@@ -178,6 +178,12 @@ struct TcPrefillExtra {
     int oob_row;  // marks a 16-key box past the context: it is filled from a page of zeros
     int q_box;    // rows per Q box: 128, or the largest power of two that the q tensor's row count allows
     int page_shift;  // log2 of the page size in keys
+    // Split over keys (grid.z > 1): CTA z of a work item takes key tiles [z * per, (z + 1) * per) of the item's tiles,
+    // per = ceil(tiles / splits), and leaves its unnormalised output, reference maximum and row sum in part_o / part_ml
+    // for the merge kernel; with one split the kernel writes the attention output itself.
+    int splits;
+    float* part_o;   // [work item][q head][split][128 rows][128 dims]
+    float* part_ml;  // [work item][q head][split][128 rows][2]: maximum (log2 domain), row sum
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -221,7 +227,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int rows = min(QT, qn - q_start);
     const int page_size = p.page_tiles * 16;
     const int last_q_pos = ctx_before + q_start + rows - 1;
-    const int n_tiles = last_q_pos / KT + 1;
+    const int all_tiles = last_q_pos / KT + 1;
+    // this CTA's key tiles: global tile j0 + j for j < n_tiles (every index below is local; only key positions and
+    // page look-ups add j0)
+    const int tiles_per = (all_tiles + ex.splits - 1) / ex.splits;
+    const int j0 = (int)blockIdx.z * tiles_per;
+    const int n_tiles = min(tiles_per, all_tiles - j0);
+    if (n_tiles <= 0) return;  // the merge kernel computes the same ranges and skips this split
 
     if (tid == 0) {
         mbar_init(q_full, 1);
@@ -277,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t dst0 = base + (is_v ? (uint32_t)OFF_V + (uint32_t)sub * V_BOX_BYTES : (uint32_t)OFF_K + (uint32_t)sub * 2048u);
             // page of this lane's box; the index is clamped to the block-table row so the load is unconditional
             auto page_of = [&](int j) {
-                const int blk = (j * KT + sub * 16) >> ex.page_shift;
+                const int blk = ((j0 + j) * KT + sub * 16) >> ex.page_shift;
                 return __ldg(bt + (blk < p.max_blocks ? blk : p.max_blocks - 1));
             };
             int pg = page_of(0);
@@ -287,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int pg_next = j + 1 < n_tiles ? page_of(j + 1) : 0;
                 // row of the box in the pool's (page, kv head, slot) order; self-checks: never past the block-table
                 // row, never outside the pool; a box past the context is filled from a page of zeros
-                const int key0 = j * KT + sub * 16;
+                const int key0 = (j0 + j) * KT + sub * 16;
                 int row = ex.oob_row;
                 if (key0 < ctx) {
                     const long rr = (((long)pg * p.hkv + kvh) << ex.page_shift) + (key0 & (page_size - 1));
@@ -401,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after();
-            const int key_base = j * KT + wg * 64;
+            const int key_base = (j0 + j) * KT + wg * 64;
             const bool need_mask = key_base + 63 > kvis;
             // this thread's 64 scores (log2 domain, masked), their maximum, then the maximum of the whole row
             uint32_t v0[32], v1[32];
@@ -438,7 +450,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             float alpha = 1.f;
             bool rescale = false;
             if (j == 0) {
-                m_run = mx;  // key 0 is visible to every row, so this is finite
+                // key 0 is visible to every row, so the first tile of the whole range gives a finite maximum; a later
+                // split may begin on a tile that a row does not see at all: it starts from a finite floor instead, so
+                // that exp2(-inf - m) is 0 and not NaN, and is rescaled away by the first tile the row does see
+                m_run = fmaxf(mx, -1e30f);
             } else if (mx > m_run + kRescaleThreshold) {
                 alpha = exp2f(m_run - mx);
                 m_run = mx;
@@ -516,7 +531,25 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (!__all_sync(0xffffffffu, mbar_wait(l_ready, 0))) alive = false;
             l_run += xb[(slot * 2 + (wg ^ 1)) * 128 + r];
         }
-        if (alive) {
+        if (alive && ex.splits > 1) {
+            tc_fence_after();
+            const size_t slot = (((size_t)w * p.hq + head) * ex.splits + blockIdx.z) * QT + r;
+            float* dst = ex.part_o + slot * HD + wg * 64;
+#pragma unroll 1
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[32];
+                tc_ld32(tmem_o + lane_addr + (uint32_t)wg * 64u + (uint32_t)c * 32u, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int g = 0; g < 8; g++)
+                        *reinterpret_cast<uint4*>(dst + c * 32 + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                }
+            }
+            if (row_ok && wg == 0) {
+                ex.part_ml[slot * 2] = m_run;
+                ex.part_ml[slot * 2 + 1] = l_run;
+            }
+        } else if (alive) {
             tc_fence_after();
             const float inv = 1.0f / l_run;
             uint16_t* dst = p.out + ((size_t)(tok0 + q_start + (row_ok ? r : 0)) * p.hq + head) * HD + wg * 64;
@@ -545,6 +578,41 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// Sum of the key splits of one (work item, q head): out = sum_z 2^(m_z - M) O_z / sum_z 2^(m_z - M) l_z with M the
+// largest m_z, the splits taken in index order.  One warp per query row at a time, a lane per four head dimensions.
+__global__ void __launch_bounds__(128) paged_attn_prefill_merge_kernel(const PrefillAttnParams p, const TcPrefillExtra ex) {
+    const int w = blockIdx.x, head = blockIdx.y;
+    if (w >= *p.n_work) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = p.pf_seq[w], q_start = p.pf_qstart[w];
+    const int tok0 = p.cu_seqlens[b], qn = p.cu_seqlens[b + 1] - tok0;
+    const int ctx_before = p.context_lens[b] - qn;
+    const int rows = min(QT, qn - q_start);
+    const int all_tiles = (ctx_before + q_start + rows - 1) / KT + 1;
+    const int tiles_per = (all_tiles + ex.splits - 1) / ex.splits;
+    const int used = (all_tiles + tiles_per - 1) / tiles_per;  // splits that had tiles
+    const size_t slot0 = ((size_t)w * p.hq + head) * ex.splits * QT;
+    for (int r = warp; r < rows; r += 4) {
+        if (tok0 + q_start + r >= p.q_rows) break;
+        float M = -INFINITY;
+        for (int z = 0; z < used; z++) M = fmaxf(M, ex.part_ml[(slot0 + (size_t)z * QT + r) * 2]);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+        for (int z = 0; z < used; z++) {
+            const size_t s = slot0 + (size_t)z * QT + r;
+            const float wz = exp2f(ex.part_ml[s * 2] - M);
+            const float4 o = *reinterpret_cast<const float4*>(ex.part_o + s * HD + lane * 4);
+            acc.x = fmaf(wz, o.x, acc.x), acc.y = fmaf(wz, o.y, acc.y), acc.z = fmaf(wz, o.z, acc.z), acc.w = fmaf(wz, o.w, acc.w);
+            L = fmaf(wz, ex.part_ml[s * 2 + 1], L);
+        }
+        const float inv = 1.0f / L;
+        uint2 o2;
+        o2.x = pack_bf2(acc.x * inv, acc.y * inv);
+        o2.y = pack_bf2(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(p.out + ((size_t)(tok0 + q_start + r) * p.hq + head) * HD + lane * 4) = o2;
     }
 }
 
@@ -656,10 +724,41 @@ int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int g
     B2_CHECK(get_map_v(ctx, p.v_pool, (uint64_t)p.pool_rows, &mv));
     int page_shift = 4;
     while ((16 << (page_shift - 4)) < p.page_tiles * 16) page_shift++;
-    TcPrefillExtra ex{ctx->dev_err, -1, q_box, page_shift};
-    dim3 grid(grid_work, p.hq);
+    TcPrefillExtra ex{ctx->dev_err, -1, q_box, page_shift, 1, nullptr, nullptr};
+    // A CTA fills an SM (224 KB of operands), so the grid is (work items x q heads) CTAs at one per SM.  When that is
+    // well short of the machine and the contexts are long -- a 512-token chunk of a 32K-token prompt on one rank of
+    // a tensor-parallel group: 4 x 8 CTAs looping over up to 256 key tiles each -- the keys are split as well, up to
+    // what fills the SMs once and leaves every split at least four tiles.
+    const int base_ctas = grid_work * p.hq;
+    const int max_tiles = (p.max_ctx + KT - 1) / KT;
+    int splits = 1;
+    if (p.max_ctx > 0 && base_ctas * 2 <= ctx->sm_count) {
+        splits = ctx->sm_count / base_ctas;
+        if (splits > max_tiles / 4) splits = max_tiles / 4;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    if (splits > 1) {
+        const size_t slots = (size_t)grid_work * p.hq * splits * QT;
+        const size_t bytes = slots * (HD + 2) * sizeof(float);
+        if (bytes > ctx->pf_part_bytes) {
+            B2_CUDA(cudaStreamSynchronize(ctx->stream));
+            if (ctx->pf_part) B2_CUDA(cudaFree(ctx->pf_part));
+            ctx->pf_part = nullptr;
+            B2_CUDA(cudaMalloc((void**)&ctx->pf_part, bytes + (bytes >> 2)));
+            ctx->pf_part_bytes = bytes + (bytes >> 2);
+        }
+        ex.splits = splits;
+        ex.part_o = ctx->pf_part;
+        ex.part_ml = ctx->pf_part + slots * HD;
+    }
+    dim3 grid(grid_work, p.hq, splits);
     paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv, mz, mzv);
     B2_LAUNCHED(ctx);
+    if (splits > 1) {
+        paged_attn_prefill_merge_kernel<<<dim3(grid_work, p.hq), 128, 0, ctx->stream>>>(p, ex);
+        B2_LAUNCHED(ctx);
+    }
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }

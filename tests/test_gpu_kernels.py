@@ -350,6 +350,27 @@ def test_prefill_attention_long_contexts_hd128(env, hq, hkv, page):
     assert ok, f"max-abs {err}"
 
 
+def test_prefill_attention_key_split_hd128(env):
+    """Few (work item, head) pairs and a long context: the launch splits every work item's key tiles over several CTAs
+    and a second kernel adds the partial results up.  The 704-token sequence starts 64 tokens into a key tile, so some
+    splits begin on a tile that half of the query rows do not see at all (their partial is empty)."""
+    ctx, K, orc = env
+    hq, hkv, hd, page = 2, 1, 128, 16
+    q_lens = [300, 640]
+    ctx_lens = [8192 + 37, 64 + 640]
+    case = H.make_paged_case(23, ctx_lens, hq, hkv, hd, page, q_lens=q_lens)
+    kp, vp, bt, q = ctx.buf(case["kpool"]), ctx.buf(case["vpool"]), ctx.buf(case["block_tables"]), ctx.buf(case["q"])
+    out = ctx.empty(case["q"].shape, np.uint16)
+    n0 = ctx.launch_count()
+    K.paged_attn_prefill(ctx, q, kp, vp, bt, case["max_blocks"], case["cu_seqlens"], case["ctx_lens"], hq, hkv, hd, page, case["scale"], out)
+    ctx.sync()
+    assert ctx.launch_count() - n0 == 2, "expected the split kernel and its merge"
+    ref = orc.paged_attention(case["q"], case["kpool"], case["vpool"], case["block_tables"], case["cu_seqlens"], case["ctx_lens"],
+                              case["scale"])
+    ok, err = H.close_bf16_out(out.download(), ref)
+    assert ok, f"max-abs {err}"
+
+
 def test_prefill_attention_rising_scores_hd128(env):
     """Scores that keep growing along the context force the running maximum up by more than the lazy-rescale
     threshold several times (the accumulator in TMEM is rescaled in place), and a peaked softmax exercises the
