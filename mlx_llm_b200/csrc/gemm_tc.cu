@@ -15,23 +15,30 @@
 // half of the tokens: one dequantised weight element feeds up to 512 MACs, and the activation bytes
 // per MAC are a quarter of a 128 x 256 single-CTA tile.
 //
-// Work split.  The output is cut along (feature pair-tile, token) into one contiguous run of columns
-// per CTA pair ("pieces" of at most 512 tokens of one 256-feature tile).  Runs are equal to within one
-// column, so every SM finishes together whatever N and M are, and no piece shares an output element
-// with another: there is no split-K, no partial sums and no reduction pass.
+// Work split.  The output is cut into blocks of 256 tokens of one 256-feature tile; every CTA pair takes one
+// contiguous run of blocks, equal to within one, and walks it in "pieces" of one or two consecutive blocks of a
+// tile (two blocks = all 512 TMEM columns, eight MMAs per 64-wide K slab).  When the blocks alone cannot occupy the
+// 74 pairs (down_proj at a few hundred tokens) K is split as well: pieces then write f32 partial sums and a second
+// kernel adds the K ranges in range order and applies the epilogue.
 //
-// Roles per CTA (576 threads):
-//   warps 0-15  weight producers: packed codes prefetched into registers, dequantised
-//               (w = bf16(code*scale+bias), one rounding), stored in the 128B-swizzled K-major UMMA
-//               layout, generic->async proxy fence, one mbarrier arrive per warp on the LEADER CTA's
-//               "full" barrier (a remote arrive from the second CTA); afterwards the epilogue:
-//               tcgen05.ld 32 lanes x 32 columns, bf16 / residual-add / f32 stores
-//   warp 16     one thread drives TMA (tiled bulk-tensor loads, cta_group::2 form, each CTA fetching its own rows): this
-//               CTA's half of the token rows of every stage (32-row boxes), plus the W tile when the
-//               weights are dense bf16; completion bytes land on the leader's "full" barrier
-//   warp 17     leader CTA only: one thread issues tcgen05.mma.cta_group::2 (two instructions per
-//               K=16 step when the piece is wider than 256 tokens) and releases stages / publishes
-//               the accumulator with one tcgen05.commit that arrives on both CTAs' barriers
+// Roles per CTA (608 threads):
+//   warps 0-15  weight producers, four groups of four warps, group g converting every 4th K slab (thread = feature
+//               row): packed codes prefetched into registers, dequantised (w = bf16(code*scale+bias), one
+//               rounding), stored in the 128B-swizzled K-major UMMA layout, generic->async proxy fence, one
+//               mbarrier arrive per warp on the LEADER CTA's "full" barrier (a remote arrive from the second CTA);
+//               afterwards the piece's epilogue: tcgen05.ld 32 lanes x 32 columns, then bf16 / residual-add /
+//               f32 / partial-sum stores (the residual rows are fetched a column group ahead)
+//   warp 16     one thread drives TMA (tiled bulk-tensor loads, cta_group::2 form, each CTA fetching its own
+//               rows): this CTA's half of the token rows of every stage (one 128-row box, or 32-row boxes for
+//               short blocks), plus the W tile when the weights are dense bf16; completion bytes land on the
+//               leader's "full" barrier
+//   warps 17-18 leader CTA only, one thread each issues tcgen05.mma.cta_group::2 and releases stages / publishes
+//               the accumulator with tcgen05.commit arriving on both CTAs' barriers: a two-block piece (two
+//               instructions per K=16 step) belongs to the first; a one-block piece is shared, even K slabs into
+//               TMEM columns 0-255 by the first, odd slabs into 256-511 by the second, added by the epilogue
+// An MMA of the pair occupies the tensor pipe for max(93, N/2) cycles (128.6 at N = 256) whatever the accumulator
+// pattern; what keeps the kernel under that rate is the turn-around of a ring stage (commit, both CTAs see it free,
+// dequantise / TMA, remote arrive, issue), which shared memory does not let the ring hide.
 // Every mbarrier wait is bounded: on expiry the kernel raises an error word, stops producing and
 // falls through to the common exit, where the TMEM columns are freed.
 #include <cuda.h>
