@@ -82,7 +82,7 @@ int32_t b2_launch_count(b2_ctx* ctx, int64_t* out);
  * Decode: one query token per sequence, causal over its ctx_lens[i] cached positions (the query's
  * own K/V already appended).  GQA: q head h reads kv head h / (hq/hkv) (adjacent grouping,
  * attention.rs:300-301).  Split-K over chunks of `chunk_tokens` positions followed by a
- * log-sum-exp merge; chunk_tokens == 0 means 256.  fp32 accumulate, bf16 I/O.  A ctx_lens[i] larger than
+ * log-sum-exp merge; chunk_tokens == 0 lets the library choose (128 to 1024 by the size of the batch).  fp32 accumulate, bf16 I/O.  A ctx_lens[i] larger than
  * max_blocks * page_size is read as that maximum; a sequence with ctx_lens[i] == 0 gets rows of zeros.
  *   q_dev            [num_seqs, hq, head_dim]
  *   block_tables_dev [num_seqs, max_blocks] physical page per logical block
