@@ -63,6 +63,7 @@ struct Proj {  // Projection::{Dense,Quantized} (src/primitives/projection.rs:34
     void* w = nullptr;
     uint16_t* scales = nullptr;
     uint16_t* biases = nullptr;
+    uint32_t* sbt = nullptr;  // scales and biases once more, transposed and interleaved (GemmParams::sbt), built at load
 };
 struct LayerW {
     uint16_t* input_ln = nullptr;

@@ -169,7 +169,25 @@ int32_t set_local_dims(b2_model* m, b2_tp_group* tp) {
     return B2_OK;
 }
 
+// The large-M projection kernel reads scale and bias of 32 feature rows at one K group in one instruction: a second
+// copy of both, transposed and interleaved, makes that one line instead of 64.  (Not counted in weight_bytes: it is a
+// derived layout, 1/9 of the packed 4-bit codes.)
+static int32_t build_sbt(b2_model* m, Proj& p) {
+    if (p.bits == 0 || p.sbt) return B2_OK;
+    const int G = p.K / 64;
+    B2_CUDA(cudaMalloc((void**)&p.sbt, (size_t)p.N * G * 4));
+    m->allocs.push_back(p.sbt);
+    return b2_gemm_build_sbt(m->ctx, p.scales, p.biases, p.N, G, p.sbt);
+}
+
 int32_t finish_model(b2_model* m) {
+    for (auto& L : m->layers) {
+        B2_CHECK(build_sbt(m, L.qkv));
+        B2_CHECK(build_sbt(m, L.o));
+        B2_CHECK(build_sbt(m, L.gu));
+        B2_CHECK(build_sbt(m, L.down));
+    }
+    B2_CUDA(cudaStreamSynchronize(m->ctx->stream));
     m->inv_freq.resize(m->cfg.head_dim / 2);
     B2_CHECK(b2_rope_inv_freq(m->cfg.head_dim, m->cfg.rope_theta, m->cfg.rope_kind, m->cfg.rope_factor, m->cfg.rope_low_freq_factor,
                               m->cfg.rope_high_freq_factor, m->cfg.rope_original_context, m->inv_freq.data()));

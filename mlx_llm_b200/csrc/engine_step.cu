@@ -91,6 +91,7 @@ int32_t gemm(b2_model* m, const Proj& p, const uint16_t* x, int M, int ldx, uint
     g.w = p.w;
     g.scales = p.scales;
     g.biases = p.biases;
+    g.sbt = p.sbt;
     g.bits = p.bits;
     g.group = 64;
     g.M = M;
@@ -115,6 +116,7 @@ int32_t gemm_reduce_residual(b2_model* m, const Proj& p, const uint16_t* a, int 
     g.w = p.w;
     g.scales = p.scales;
     g.biases = p.biases;
+    g.sbt = p.sbt;
     g.bits = p.bits;
     g.group = 64;
     g.M = M;

@@ -335,6 +335,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const uint4* wq = reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p.w) + (size_t)(row_ok ? gn : 0) * (K * WK / 32));
                 const uint16_t* sc_row = p.scales + (size_t)(row_ok ? gn : 0) * groups;
                 const uint16_t* bi_row = p.biases + (size_t)(row_ok ? gn : 0) * groups;
+                const uint32_t* sbt_col = p.sbt ? p.sbt + (row_ok ? gn : 0) : nullptr;
                 constexpr int NQ = WK == 4 ? 2 : 4;  // 16-byte loads per 64 codes
                 // Codes, scale and bias of the next DEPTH slabs of this group wait in registers (DEPTH * GROUPS slabs
                 // ahead of the one being dequantised): the loads come from DRAM or a busy L2, and with a single slab
@@ -345,7 +346,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 auto load_codes = [&](int d, int kb) {
 #pragma unroll
                     for (int i = 0; i < NQ; i++) q[d][i] = row_ok ? __ldg(wq + kb * NQ + i) : make_uint4(0, 0, 0, 0);
-                    sb[d] = row_ok ? ((uint32_t)__ldg(sc_row + kb) | ((uint32_t)__ldg(bi_row + kb) << 16)) : 0u;
+                    // scale and bias: one coalesced 4-byte load where the caller supplies the transposed table (a warp's 32
+                    // rows read one 128-byte line), two 2-byte loads that each touch 32 lines where it does not
+                    if (!row_ok)
+                        sb[d] = 0u;
+                    else if (sbt_col)
+                        sb[d] = __ldg(sbt_col + (size_t)kb * N);
+                    else
+                        sb[d] = (uint32_t)__ldg(sc_row + kb) | ((uint32_t)__ldg(bi_row + kb) << 16);
                 };
                 // first K slab of this piece that belongs to this group
                 int kb0 = (int)((grp + GROUPS - (it_global % GROUPS)) % GROUPS);  // slab index within the piece
@@ -736,6 +744,21 @@ int32_t get_map(b2_ctx* ctx, const void* ptr, uint64_t rows, uint64_t k, uint64_
     return B2_OK;
 }
 
+__global__ void sbt_build_kernel(const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases, int N, int G, uint32_t* __restrict__ sbt) {
+    // 32 x 32 tiles through shared memory: coalesced reads along the groups of a row, coalesced writes along the rows
+    __shared__ uint32_t tile[32][33];
+    const int g0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int n = n0 + r, g = g0 + threadIdx.x;
+        if (n < N && g < G) tile[r][threadIdx.x] = (uint32_t)scales[(size_t)n * G + g] | ((uint32_t)biases[(size_t)n * G + g] << 16);
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int g = g0 + r, n = n0 + threadIdx.x;
+        if (n < N && g < G) sbt[(size_t)g * N + n] = tile[threadIdx.x][r];
+    }
+}
+
 template <int WK, int EPI>
 int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
     B2_SMEM_ONCE(ctx, (gemm_tc_pair_kernel<WK, EPI>), SMEM_BYTES);
@@ -826,6 +849,13 @@ int32_t dispatch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
 }
 
 }  // namespace
+
+int32_t b2_gemm_build_sbt(b2_ctx* ctx, const uint16_t* scales_dev, const uint16_t* biases_dev, int N, int G, uint32_t* sbt_dev) {
+    sbt_build_kernel<<<dim3((unsigned)((G + 31) / 32), (unsigned)((N + 31) / 32)), dim3(32, 8), 0, ctx->stream>>>(scales_dev, biases_dev, N, G, sbt_dev);
+    B2_LAUNCHED(ctx);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
 
 bool b2_gemm_tc_eligible(const GemmParams& p) {
     return p.M > 32 && p.N % TM == 0 && p.K % TK == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 &&

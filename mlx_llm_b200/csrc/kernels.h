@@ -54,6 +54,9 @@ struct GemmParams {
     // sum to the rank that will add it up.  f32_chunk is a multiple of 4.
     float* out_f32_by_chunk[8];
     int f32_chunk;
+    // Optional (quantized, tcgen05 path): sbt[g * N + n] = scale(n, g) | bias(n, g) << 16, the scales and biases
+    // transposed and interleaved so that the 32 feature rows of a warp read one 128-byte line per K group.
+    const uint32_t* sbt;
 };
 #ifdef __CUDACC__
 __device__ __forceinline__ float* gemm_f32_dst(const GemmParams& p, int t, int f) {
@@ -75,6 +78,8 @@ int32_t b2_gemm_stream_launch(b2_ctx* ctx, const GemmParams& p);
 // tcgen05 / TMEM path, CTA-pair form (gemm_tc.cu): taken by b2_gemm_launch when eligible.
 bool b2_gemm_tc_eligible(const GemmParams& p);
 int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p);
+// fills sbt (N * G words) from scales / biases [N, G] (see GemmParams::sbt); enqueued on the context's stream
+int32_t b2_gemm_build_sbt(b2_ctx* ctx, const uint16_t* scales_dev, const uint16_t* biases_dev, int N, int G, uint32_t* sbt_dev);
 
 // ---- elementwise / normalisation / embedding / sampling (fused_ops.cu) ---------------------------
 // out = rmsnorm(x) * w, one row per token; rows gathered through `row_idx` when non-null.
