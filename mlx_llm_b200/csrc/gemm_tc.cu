@@ -178,6 +178,12 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// 32-byte read-only global load (32-byte aligned address)
+__device__ __forceinline__ void ldg256(const uint4* p, uint4& a, uint4& b) {
+    asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+        : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+        : "l"(p));
+}
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -344,8 +350,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 uint4 q[DEPTH][NQ];
                 uint32_t sb[DEPTH];
                 auto load_codes = [&](int d, int kb) {
+                    // 32 bytes per instruction (sm_100 has 256-bit global loads): a row's 32 or 64 bytes of codes lie in one
+                    // 128-byte line of their own, and every load instruction of a warp costs the load unit one tag look-up
+                    // per line it touches, so half as many instructions is half of that cost
 #pragma unroll
-                    for (int i = 0; i < NQ; i++) q[d][i] = row_ok ? __ldg(wq + kb * NQ + i) : make_uint4(0, 0, 0, 0);
+                    for (int i = 0; i < NQ; i += 2) {
+                        if (row_ok)
+                            ldg256(wq + kb * NQ + i, q[d][i], q[d][i + 1]);
+                        else
+                            q[d][i] = q[d][i + 1] = make_uint4(0, 0, 0, 0);
+                    }
                     // scale and bias: one coalesced 4-byte load where the caller supplies the transposed table (a warp's 32
                     // rows read one 128-byte line), two 2-byte loads that each touch 32 lines where it does not
                     if (!row_ok)
@@ -859,7 +873,7 @@ int32_t b2_gemm_build_sbt(b2_ctx* ctx, const uint16_t* scales_dev, const uint16_
 
 bool b2_gemm_tc_eligible(const GemmParams& p) {
     return p.M > 32 && p.N % TM == 0 && p.K % TK == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 &&
-           ((uintptr_t)p.w & 15) == 0 && (p.bits == 0 || p.bits == 4 || p.bits == 8);
+           ((uintptr_t)p.w & (p.bits ? 31 : 15)) == 0 && (p.bits == 0 || p.bits == 4 || p.bits == 8);
 }
 
 int32_t b2_gemm_tc_launch(b2_ctx* ctx, const GemmParams& p) {
