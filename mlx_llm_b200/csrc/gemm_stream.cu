@@ -118,9 +118,6 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
     // rows of this thread: tile r in {0,1}: n0 + 16 r + g and + 8
     const uint8_t* wrow[4];
     const uint16_t *srow[4], *brow[4];
-    // scale | bias of (row, K group) from the transposed table when the caller has one (GemmParams::sbt): the eight
-    // rows a load instruction covers are then 32 contiguous bytes instead of eight lines twice
-    const uint32_t* trow[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int row = n0 + (i >> 1) * 16 + (i & 1) * 8 + g;
@@ -128,7 +125,6 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
         wrow[i] = reinterpret_cast<const uint8_t*>(p.w) + (size_t)row * row_bytes;
         srow[i] = WK ? p.scales + (size_t)row * groups : nullptr;
         brow[i] = WK ? p.biases + (size_t)row * groups : nullptr;
-        trow[i] = WK && p.sbt ? p.sbt + row : nullptr;
     }
 
     // activations of chunk c (256 K of every token) into buffer `buf`, permuted span by span
@@ -165,10 +161,7 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
             wq[slot][i] = __ldg(reinterpret_cast<const uint4*>(wrow[i] + byte_off));
             if (WK) {
                 const int grp = (k0 + SP::E * t) / 64;
-                if (trow[i])
-                    sb[slot][i] = __ldg(trow[i] + (size_t)grp * N);
-                else
-                    sb[slot][i] = (uint32_t)__ldg(srow[i] + grp) | ((uint32_t)__ldg(brow[i] + grp) << 16);
+                sb[slot][i] = (uint32_t)__ldg(srow[i] + grp) | ((uint32_t)__ldg(brow[i] + grp) << 16);
             }
         }
     };
