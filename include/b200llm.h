@@ -464,6 +464,20 @@ typedef struct b2_continuous b2_continuous;
 int32_t b2_continuous_new(b2_model* m, const b2_request* reqs, int32_t n, const b2_continuous_config* cfg,
                           const volatile int32_t* cancel, b2_event_cb cb, void* user, b2_continuous** out);
 int32_t b2_continuous_step(b2_continuous* e, int32_t max_steps, int32_t* done_out, b2_run_stats* stats);
+/* Serving form of the same loop, for a host that routes TextLlm::generate calls (src/provider.rs:567-918) of several
+ * connections through ONE batch -- which the reference does not do (its provider runs generate_with per request,
+ * provider.rs:838-846): the engine starts with no requests (cfg->max_pages and cfg->max_blocks_per_seq must be given),
+ * b2_continuous_submit adds one at any time between steps (the engine copies the prompt and the stop tokens; *id_out is
+ * the request's index in events and results), b2_continuous_halt ends one request between steps with Done{reason}
+ * -- B2_FINISH_CANCELLED for a client that went away (CancelFlag, stream.rs:9-12), B2_FINISH_STOPPED for a stop
+ * string matched in the detokenised text (should_stop, provider.rs:826-828) -- and b2_continuous_result reads a
+ * request's tokens so far and its finish reason (-1 while it runs).  b2_continuous_step's *done_out == 1 then means
+ * "idle": more may be submitted.  Not re-entrant: one thread drives an engine. */
+int32_t b2_continuous_open(b2_model* m, const b2_continuous_config* cfg, b2_event_cb cb, void* user, b2_continuous** out);
+int32_t b2_continuous_submit(b2_continuous* e, const b2_request* req, int32_t* id_out);
+int32_t b2_continuous_halt(b2_continuous* e, int32_t id, int32_t finish_reason);
+int32_t b2_continuous_result(b2_continuous* e, int32_t id, int32_t* tokens_out, int32_t capacity, int32_t* n_out,
+                             int32_t* finish_out);
 int32_t b2_continuous_finish(b2_continuous* e, b2_gen_output* outs, b2_run_stats* stats);
 int32_t b2_continuous_free(b2_continuous* e);
 

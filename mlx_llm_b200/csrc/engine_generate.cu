@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cstring>
+#include <deque>
 #include <memory>
 #include <thread>
 
@@ -75,6 +76,13 @@ struct b2_continuous {
     std::vector<SeqStep> batch;
     std::vector<int> batch_lane;
     std::vector<int32_t> toks;
+    // Serving mode (b2_continuous_open / _submit): requests arrive while the loop runs, so the engine keeps its own copy
+    // of each (prompt and stop tokens included); `reqs` / `n` then follow `own_reqs`.
+    bool open = false;
+    std::vector<b2_request> own_reqs;
+    std::deque<std::vector<int32_t>> own_ids;
+    std::vector<char> req_cancel;  // per-request cancel / halt: 0 none, else the finish reason to report
+    int max_blocks_row = 0;
 
     double now_s() const { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t_start).count(); }
     int64_t pages_of(const b2_request& r) const { return (int64_t)((r.n_prompt + std::max(r.max_new_tokens, 0) + bs - 1) / bs); }
@@ -117,6 +125,11 @@ struct b2_continuous {
     int admit(int ri, int32_t& rc) {
         const b2_request& r = reqs[ri];
         if (r.arrival_s > 0 && now_s() < r.arrival_s) return -1;
+        if (!req_cancel.empty() && req_cancel[ri] && sched[ri].finish == -1) {  // cancelled while it waited
+            sched[ri].finish = req_cancel[ri];
+            emit(ri, 1, req_cancel[ri], 0);
+            return 0;
+        }
         if (sched[ri].finish != -1) {  // zero budget: terminal event, no prefill (continuous.rs:247-252)
             emit(ri, 1, B2_FINISH_MAX_TOKENS, 0);
             return 0;
@@ -176,6 +189,19 @@ struct b2_continuous {
             cancelled = true;
             *done = true;
             return B2_OK;
+        }
+        if (!req_cancel.empty()) {  // requests halted one by one (a stop string matched, a client went away)
+            std::vector<Lane> keep;
+            for (auto& l : lanes) {
+                if (req_cancel[l.req]) {
+                    sched[l.req].finish = req_cancel[l.req];
+                    emit(l.req, 1, req_cancel[l.req], (int)sched[l.req].generated.size());
+                    retire(l);
+                } else {
+                    keep.push_back(l);
+                }
+            }
+            lanes.swap(keep);
         }
         if (chunked || lanes.empty()) B2_CHECK(fill_slots());  // lanes can be empty while requests have yet to arrive
         if (lanes.empty()) {
@@ -326,8 +352,82 @@ int32_t b2_continuous_new(b2_model* m, const b2_request* reqs, int32_t n, const 
     return B2_OK;
 }
 
+int32_t b2_continuous_open(b2_model* m, const b2_continuous_config* cfg, b2_event_cb cb, void* user, b2_continuous** out) {
+    B2_REQUIRE(m && cfg && out, B2_ERR_MSG, "b2_continuous_open: null argument");
+    B2_REQUIRE(cfg->max_batch > 0 && cfg->block_size > 0, B2_ERR_MSG, "b2_continuous_open: max_batch and block_size must be > 0");
+    B2_REQUIRE(cfg->max_pages > 0 && cfg->max_blocks_per_seq > 0, B2_ERR_MSG,
+               "b2_continuous_open: max_pages and max_blocks_per_seq must be given (there are no requests to size the pool from)");
+    auto e = std::make_unique<b2_continuous>();
+    e->m = m;
+    e->cfg = *cfg;
+    e->cb = cb;
+    e->user = user;
+    e->bs = cfg->block_size;
+    e->chunked = cfg->prefill_chunk_tokens > 0;
+    e->throughput = cfg->exactness != 0;
+    e->open = true;
+    e->max_pages = cfg->max_pages;
+    e->max_blocks_row = cfg->max_blocks_per_seq;
+    B2_CHECK(b2_pool_new(m->ctx, m, e->bs, cfg->max_pages, cfg->max_batch, cfg->max_blocks_per_seq, &e->pool));
+    e->dev0 = m->device_ms;
+    e->h2d0 = m->h2d_bytes;
+    e->d2h0 = m->d2h_bytes;
+    e->launch0 = m->ctx->launches;
+    e->t_start = std::chrono::steady_clock::now();
+    *out = e.release();
+    return B2_OK;
+}
+
+int32_t b2_continuous_submit(b2_continuous* e, const b2_request* req, int32_t* id_out) {
+    B2_REQUIRE(e && req && id_out, B2_ERR_MSG, "b2_continuous_submit: null argument");
+    B2_REQUIRE(e->open && !e->finished, B2_ERR_MSG, "b2_continuous_submit: the engine was not opened for submissions (b2_continuous_open) or has finished");
+    B2_REQUIRE(req->n_prompt > 0 && req->prompt_ids, B2_ERR_MSG, "b2_continuous_submit: empty prompt");
+    B2_CHECK(check_greedy(*req));
+    const int64_t need = e->pages_of(*req) + 1;
+    B2_REQUIRE(need <= e->max_blocks_row && need <= e->max_pages, B2_ERR_OOM_PAGES,
+               "b2_continuous_submit: prompt + max_new_tokens needs " + std::to_string(need) + " pages, more than a block-table row (" +
+                   std::to_string(e->max_blocks_row) + ") or the pool (" + std::to_string(e->max_pages) + ") holds");
+    b2_request r = *req;
+    e->own_ids.emplace_back(req->prompt_ids, req->prompt_ids + req->n_prompt);
+    r.prompt_ids = e->own_ids.back().data();
+    e->own_ids.emplace_back(req->stop_tokens, req->stop_tokens + (req->stop_tokens ? req->n_stop : 0));
+    r.stop_tokens = e->own_ids.back().data();
+    r.n_stop = (int32_t)e->own_ids.back().size();
+    r.arrival_s = 0;  // it has arrived
+    e->own_reqs.push_back(r);
+    e->reqs = e->own_reqs.data();
+    e->n = (int)e->own_reqs.size();
+    e->sched.emplace_back();
+    if (r.max_new_tokens <= 0) e->sched.back().finish = B2_FINISH_MAX_TOKENS;  // retired at admission
+    e->req_cancel.push_back(0);
+    *id_out = e->n - 1;
+    return B2_OK;
+}
+
+int32_t b2_continuous_halt(b2_continuous* e, int32_t id, int32_t finish_reason) {
+    B2_REQUIRE(e, B2_ERR_MSG, "b2_continuous_halt: null engine");
+    B2_REQUIRE(id >= 0 && id < e->n, B2_ERR_MSG, "b2_continuous_halt: no such request");
+    B2_REQUIRE(finish_reason == B2_FINISH_CANCELLED || finish_reason == B2_FINISH_STOPPED, B2_ERR_MSG,
+               "b2_continuous_halt: the reason must be B2_FINISH_CANCELLED or B2_FINISH_STOPPED");
+    if (e->req_cancel.size() < (size_t)e->n) e->req_cancel.resize(e->n, 0);
+    if (e->sched[id].finish == -1 && !e->req_cancel[id]) e->req_cancel[id] = (char)finish_reason;
+    return B2_OK;
+}
+
+int32_t b2_continuous_result(b2_continuous* e, int32_t id, int32_t* tokens_out, int32_t capacity, int32_t* n_out, int32_t* finish_out) {
+    B2_REQUIRE(e && n_out && finish_out, B2_ERR_MSG, "b2_continuous_result: null argument");
+    B2_REQUIRE(id >= 0 && id < e->n, B2_ERR_MSG, "b2_continuous_result: no such request");
+    const SchedSeq& s = e->sched[id];
+    *n_out = (int32_t)s.generated.size();
+    *finish_out = s.finish;
+    if (tokens_out)
+        for (int i = 0; i < *n_out && i < capacity; i++) tokens_out[i] = s.generated[i];
+    return B2_OK;
+}
+
 int32_t b2_continuous_step(b2_continuous* e, int32_t max_steps, int32_t* done_out, b2_run_stats* stats) {
     B2_REQUIRE(e, B2_ERR_MSG, "b2_continuous_step: null engine");
+    B2_CUDA(cudaSetDevice(e->m->ctx->device));  // the serving thread may not be the one that built the model
     bool done = false;
     for (int i = 0; i < max_steps && !done; i++) B2_CHECK(e->step(&done));
     if (done_out) *done_out = done ? 1 : 0;

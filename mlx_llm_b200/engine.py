@@ -706,3 +706,54 @@ class ContinuousEngine:
         if self.h:
             load().b2_continuous_free(self.h)
             self.h = C.c_void_p()
+
+
+class ServingEngine:
+    """The continuous-batching loop opened for submissions (b2_continuous_open / _submit / _halt / _result): requests
+    join between iterations, each can be halted on its own.  One thread drives it.  on_event(request_id, event) with
+    event = ("token", id, step) or ("done", reason, generated) is called from step()."""
+
+    def __init__(self, model, config: ContinuousConfig, on_event=None):
+        self._err = []
+
+        def _cb(_user, req, kind, a, b):
+            try:
+                if on_event:
+                    on_event(req, ("token", a, b) if kind == 0 else ("done", a, b))
+            except Exception as e:  # a Python exception must not unwind through the C frame
+                self._err.append(e)
+
+        self._cb = EVENT_CB(_cb)
+        cfg = CContinuousConfig(config.max_batch, config.block_size, config.exactness, config.prefill_chunk_tokens, config.max_pages,
+                                config.max_blocks_per_seq)
+        self.h = C.c_void_p()
+        check(load().b2_continuous_open(model.h, C.byref(cfg), self._cb, None, C.byref(self.h)))
+
+    def submit(self, request: BatchRequest) -> int:
+        arr, _keep = _c_requests([request])  # the engine copies the prompt and the stop tokens
+        rid = C.c_int32(-1)
+        check(load().b2_continuous_submit(self.h, arr, C.byref(rid)))
+        return rid.value
+
+    def halt(self, request_id, reason=2):
+        check(load().b2_continuous_halt(self.h, int(request_id), int(reason)))
+
+    def result(self, request_id, capacity=4096):
+        buf = np.zeros(max(capacity, 1), np.int32)
+        n, fin = C.c_int32(0), C.c_int32(-1)
+        check(load().b2_continuous_result(self.h, int(request_id), buf.ctypes.data_as(C.POINTER(C.c_int32)), buf.size, C.byref(n), C.byref(fin)))
+        return GenerationOutput([int(t) for t in buf[:min(n.value, buf.size)]], fin.value)
+
+    def step(self, max_steps=1):
+        """Runs up to max_steps iterations; returns True when the engine is idle (nothing admitted, nothing waiting)."""
+        done = C.c_int32(0)
+        check(load().b2_continuous_step(self.h, int(max_steps), C.byref(done), None))
+        if self._err:
+            raise self._err.pop(0)
+        return bool(done.value)
+
+    def free(self):
+        if self.h:
+            load().b2_continuous_free(self.h)
+            self.h = C.c_void_p()
+
