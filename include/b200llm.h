@@ -73,6 +73,10 @@ int32_t b2_flush_l2(b2_ctx* ctx);
 /* Open (on != 0) or close the range an external profiler started with "--profile-from-start off"
  * looks at (cudaProfilerStart / cudaProfilerStop); the stream is drained first.  No effect otherwise. */
 int32_t b2_profiler_range(b2_ctx* ctx, int32_t on);
+/* NVTX ranges ("gemm", "attn_decode", "attn_prefill", "rope_kv", "elementwise", "meta_copies", "collective") around
+ * the launches of each kernel class of every step, for timeline tools; off by default (also switched on by the
+ * environment variable B2_NVTX=1 when the context is created).  No reference counterpart. */
+int32_t b2_nvtx_enable(b2_ctx* ctx, int32_t on);
 /* Number of this library's kernels launched on the context since creation. */
 int32_t b2_launch_count(b2_ctx* ctx, int64_t* out);
 

@@ -118,6 +118,10 @@ class Context:
     def profiler_range(self, on):
         check(load().b2_profiler_range(self.h, C.c_int32(1 if on else 0)))
 
+    def nvtx(self, on):
+        """NVTX ranges per kernel class around every step's launches (b2_nvtx_enable)."""
+        check(load().b2_nvtx_enable(self.h, C.c_int32(1 if on else 0)))
+
     def mem_info(self):
         f, t = C.c_size_t(0), C.c_size_t(0)
         check(load().b2_mem_info(self.h, C.byref(f), C.byref(t)))

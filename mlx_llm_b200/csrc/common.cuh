@@ -59,6 +59,9 @@ struct b2_ctx {
     bool use_tc = true;
     // optional per-kernel-class timing with CUDA events on the launching stream
     bool profile = false;
+    // NVTX ranges around every kernel class of a step ("gemm", "attn_decode", ...), for timeline tools; off by default
+    bool nvtx = false;
+    bool nvtx_open = false;
     std::vector<cudaEvent_t> prof_ev;
     std::vector<int> prof_cls;
     std::vector<int64_t> prof_launch;

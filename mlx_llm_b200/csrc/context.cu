@@ -1,4 +1,7 @@
 // Context, error reporting and raw device-memory plumbing of the C ABI.
+#include <cstdlib>
+#include <nvtx3/nvToolsExt.h>
+
 #include <cstdio>
 #include <cstring>
 
@@ -53,6 +56,7 @@ int32_t b2_ctx_create(int32_t device, b2_ctx** out) {
     B2_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     B2_CUDA(cudaEventCreate(&c->ev0));
     B2_CUDA(cudaEventCreate(&c->ev1));
+    if (const char* v = std::getenv("B2_NVTX")) c->nvtx = v[0] == '1';
     *out = c;
     return B2_OK;
 }
@@ -184,6 +188,14 @@ int32_t b2_launch_count(b2_ctx* ctx, int64_t* out) {
     return B2_OK;
 }
 
+int32_t b2_nvtx_enable(b2_ctx* ctx, int32_t on) {
+    B2_REQUIRE(ctx, B2_ERR_MSG, "b2_nvtx_enable: null context");
+    if (ctx->nvtx_open) nvtxRangePop();
+    ctx->nvtx_open = false;
+    ctx->nvtx = on != 0;
+    return B2_OK;
+}
+
 int32_t b2_profile_enable(b2_ctx* ctx, int32_t on) {
     B2_REQUIRE(ctx, B2_ERR_MSG, "b2_profile_enable: null context");
     B2_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -214,7 +226,14 @@ int32_t b2_profile_read(b2_ctx* ctx, b2_profile_t* out) {
 
 }  // extern "C"
 
+static const char* const kClassNames[8] = {"gemm", "attn_decode", "attn_prefill", "rope_kv", "elementwise", "meta_copies", "collective", "other"};
+
 void b2_prof_mark(b2_ctx* ctx, int cls) {
+    if (ctx->nvtx) {  // one range per run of launches of a class; cls < 0 closes the step's last range
+        if (ctx->nvtx_open) nvtxRangePop();
+        ctx->nvtx_open = cls >= 0;
+        if (cls >= 0) nvtxRangePushA(kClassNames[cls & 7]);
+    }
     if (!ctx->profile) return;
     if (ctx->prof_used == ctx->prof_ev.size()) {
         cudaEvent_t e;

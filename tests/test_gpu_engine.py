@@ -541,3 +541,23 @@ def test_f32_model_limits(env32):
     assert e.value.code == -5
     with pytest.raises(B2Error):
         eng.CausalLm.synthetic(ctx, H.engine_config(eng, CONFIG0_F32), seed=0)
+
+
+def test_nvtx_ranges_do_not_change_a_step(env):
+    """With NVTX ranges on (no tool attached: the calls are no-ops) a step gives the same logits and launches."""
+    ctx, eng, model = env[0], env[1], env[3]
+    prompts = H.config0_prompts()
+    outs = []
+    for on in (False, True):
+        ctx.nvtx(on)
+        pool = eng.BlockPool(ctx, model, 16, 32, 4, 16)
+        caches = [eng.PagedKvCache(pool) for _ in range(2)]
+        n0 = ctx.launch_count()
+        logits, am = model.step([(prompts[0], caches[0]), (prompts[1], caches[1])])
+        outs.append((logits.copy(), am.copy(), ctx.launch_count() - n0))
+        for c in caches:
+            c.free()
+        pool.free()
+    ctx.nvtx(False)
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1]) and outs[0][2] == outs[1][2]
+
