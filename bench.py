@@ -92,15 +92,25 @@ class ClockSampler:
                     samples=len(sm))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernels, from the ncu captures summarised under
+# profiles/ (each summary gives the capturing command).
+NCU_TRAFFIC = {
+    "gemm_gate_up": dict(kernel="gemm_tc_pair_kernel<4,0>", bytes_per_launch=94.1e6, summary="gemm_tc_pair_kernel_q4_2layer_step.md",
+                         note="gate+up projection launch (N 28672, K 4096) at ~570 tokens in the 2-layer capture; algorithmic 66.1 MB of packed "
+                              "weights + activations/outputs that mostly stay in L2"),
+    "paged_attn_decode_config1": dict(kernel="paged_attn_decode_kernel<128>", bytes_per_launch=572.7e6, summary="paged_attn_decode_kernel_config1.md",
+                                      note="the configuration-1 batch (algorithmic 565.0 MB)"),
+    "gemm_stream_gate_up": dict(kernel="gemm_stream_kernel<4,1,0>", bytes_per_launch=66.2e6, summary="gemm_stream_kernel_decode_only_step.md",
+                                note="gate+up projection (28672 x 4096, Q4) at 8 tokens in a decode-only iteration; algorithmic 66.1 MB"),
+}
+
+
 def ncu_traffic(key):
-    """dram__bytes_read.sum + dram__bytes_write.sum per launch of a dominant kernel, read from profiles/ncu_traffic.json
-    (written beside the ncu summaries it is taken from, which give the capturing commands).  Returns (bytes, note)."""
-    try:
-        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
-            e = json.load(f)[key]
-        return float(e["bytes_per_launch"]), f"{e['kernel']}: {e['note']} (summary: profiles/{e['summary']})"
-    except (OSError, KeyError, ValueError):
+    """Returns (bytes per launch, note) for a dominant kernel, or (None, reason)."""
+    e = NCU_TRAFFIC.get(key)
+    if not e:
         return None, "no ncu capture recorded for this kernel"
+    return float(e["bytes_per_launch"]), f"{e['kernel']}: {e['note']} (summary: profiles/{e['summary']})"
 
 
 def host_threads():
