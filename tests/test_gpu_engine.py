@@ -532,6 +532,22 @@ def test_config0_f32_greedy_streams_identical(env32, mode):
         assert eng.generate(model, p.tolist(), 32).tokens == o.tokens
 
 
+def test_config0_f32_streams_match_committed_fixture(env32):
+    """The committed golden fixture (tests/golden/config0.json, written by tests/golden/gen_config0.py from the CPU
+    oracle): all four greedy streams of the f32 engine, 32 tokens each, and the block-id table of the run."""
+    import json
+    import os
+
+    ctx, eng, orc, model, omodel = env32
+    with open(os.path.join(os.path.dirname(__file__), "golden", "config0.json")) as f:
+        g = json.load(f)
+    if g["weights_crc"] != H.weights_crc(H.tiny_weights()):
+        pytest.skip("this platform's libm draws different Box-Muller weights than the fixture's")
+    reqs = [eng.BatchRequest(p, 32) for p in g["prompts"]]
+    outs = eng.generate_continuous(model, reqs, eng.ContinuousConfig(max_batch=8, block_size=16, exactness=eng.THROUGHPUT))
+    assert [o.tokens for o in outs] == g["tokens_f32"]
+
+
 def test_f32_model_limits(env32):
     ctx, eng, orc, model, omodel = env32
     from mlx_llm_b200._lib import B2Error

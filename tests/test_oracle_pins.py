@@ -353,6 +353,9 @@ def test_config0_golden_fixture(tiny):
     assert [p.tolist() for p in prompts] == g["prompts"]
     out = m.generate_continuous(prompts, [32] * 4)
     assert out["tokens"] == g["tokens"] and out["block_ids"] == g["block_ids"]
+    m32 = H.build_oracle_model(orc, cfg=dict(H.CONFIG0, f32_mode=1), weights=w)
+    assert m32.generate_continuous(prompts, [32] * 4)["tokens"] == g["tokens_f32"]
+    m32.free()
 
 
 def test_admit_on_retire_and_event_order(tiny):  # tests/continuous.rs:123-149
