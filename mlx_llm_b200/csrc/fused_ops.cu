@@ -26,6 +26,7 @@ __global__ void rms_norm_kernel(const uint16_t* __restrict__ x, const uint16_t* 
     // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic
     // stream serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();
     const int row = blockIdx.x;
     const int src = row_idx ? row_idx[row] : row;
     const uint16_t* xr = x + (size_t)src * ldx;
@@ -100,6 +101,7 @@ __global__ void swiglu_kernel(const uint16_t* __restrict__ gu, int inter, uint16
     // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic
     // stream serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();
     const int row = blockIdx.y;
     const uint16_t* g = gu + (size_t)row * 2 * inter;
     const uint16_t* u = g + inter;
@@ -262,7 +264,7 @@ int32_t b2_rms_norm_launch(b2_ctx* ctx, const uint16_t* x, const uint16_t* w, fl
     if (rows <= 0) return B2_OK;
     int threads = dim / 8;
     threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : ((threads + 31) / 32) * 32);
-    rms_norm_kernel<<<rows, threads, 0, ctx->stream>>>(x, w, eps, dim, ldx, row_idx, out);
+    B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, rms_norm_kernel, dim3(rows), dim3(threads), 0, ctx->stream, x, w, eps, dim, ldx, row_idx, out));
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
@@ -279,7 +281,7 @@ int32_t b2_embed_launch(b2_ctx* ctx, const uint16_t* table, const int32_t* ids, 
 int32_t b2_swiglu_launch(b2_ctx* ctx, const uint16_t* gate_up, int rows, int inter, uint16_t* out) {
     if (rows <= 0) return B2_OK;
     dim3 grid(((inter + 7) / 8 + 255) / 256, rows);
-    swiglu_kernel<<<grid, 256, 0, ctx->stream>>>(gate_up, inter, out);
+    B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, swiglu_kernel, grid, dim3(256), 0, ctx->stream, gate_up, inter, out));
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     return B2_OK;

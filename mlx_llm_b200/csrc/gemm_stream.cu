@@ -354,6 +354,8 @@ __global__ void __launch_bounds__(kThreads) gemm_stream_kernel(const GemmParams 
 // tile would be too little parallelism for the sums
 template <int EPI>
 __global__ void stream_reduce_kernel(const GemmParams p, const float* __restrict__ partial, int splits) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();  // (launched with programmatic stream serialisation behind the kernel that writes the partial sums)
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)p.M * p.N;
     if (i >= total) return;
@@ -415,7 +417,7 @@ int32_t launch_stream(b2_ctx* ctx, const GemmParams& p) {
     B2_LAUNCHED(ctx);
     if (splits > 1 && !ex.counters) {
         const size_t total = (size_t)p.M * p.N;
-        stream_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, ex.partial, splits);
+        B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, stream_reduce_kernel<EPI>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, ctx->stream, p, (const float*)ex.partial, splits));
         B2_LAUNCHED(ctx);
     }
     B2_CUDA(cudaGetLastError());

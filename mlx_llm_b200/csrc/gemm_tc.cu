@@ -316,6 +316,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     cluster_sync_all();  // both CTAs' barriers exist before anyone arrives remotely
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // All CTAs of this grid are resident from the start (one per SM), so the kernel after it in the stream may be
+    // scheduled into whatever frees up as pairs finish; it waits for this grid's completion before it reads anything.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
     if (warp < kProducerWarps) {
         // Four groups of four warps; group g dequantises every 4th K slab, one thread per feature row (64
@@ -671,6 +674,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 // four features per thread (N, the output / residual strides and their base addresses allow 16- and 8-byte accesses)
 template <int EPI>
 __global__ void splitk_reduce4_kernel(const GemmParams p, const float* __restrict__ partial, int splits) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();  // (launched with programmatic stream serialisation behind the kernel that writes the partial sums)
     const size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)p.M * p.N;
     const size_t i = q * 4;
@@ -844,7 +849,8 @@ int32_t launch_pair(b2_ctx* ctx, const GemmParams& p, int* err) {
         const bool vec4 = p.N % 4 == 0 && p.ldo % 4 == 0 && (EPI != EPI_BF16_RESADD || (p.ldres % 4 == 0 && ((uintptr_t)p.res & 7) == 0)) &&
                           (EPI == EPI_F32 ? (((uintptr_t)p.out_f32 & 15) == 0 && p.f32_chunk % 4 == 0) : ((uintptr_t)p.out & 7) == 0);
         if (vec4)
-            splitk_reduce4_kernel<EPI><<<(unsigned)((total / 4 + 255) / 256), 256, 0, ctx->stream>>>(p, plan.partial, best);
+            B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, splitk_reduce4_kernel<EPI>, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, ctx->stream, p,
+                                  (const float*)plan.partial, best));
         else
             splitk_reduce_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p, plan.partial, best);
         B2_LAUNCHED(ctx);

@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_decode_kernel(const De
     // lets a dependent launch (the projection that consumes this kernel's output, launched with programmatic stream
     // serialisation) begin its weight prefetch now; it still waits for this grid to complete before it reads
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();
     if (p.work_seq) {
         const int w = blockIdx.x;
         if (w >= *p.n_work) return;
@@ -444,7 +445,7 @@ int32_t launch_decode(b2_ctx* ctx, const DecodeAttnParams& p, int grid_work, int
     // per SM at a time and none waits for another, so the rest simply queue; the fine grain lets the hardware's block
     // scheduler even out items of different cost (measured: 4 / 8 / 16 CTAs per SM -> 174 / 150 / 137 us on 64 sequences)
     if (!p.work_seq) grid = dim3(16 * ctx->sm_count);
-    paged_attn_decode_kernel<HD><<<grid, kWarps * 32, smem, ctx->stream>>>(p);
+    B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, paged_attn_decode_kernel<HD>, grid, dim3(kWarps * 32), (size_t)smem, ctx->stream, p));
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     (void)num_seqs;

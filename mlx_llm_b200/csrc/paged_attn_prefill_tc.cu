@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // lets a dependent launch (the o_proj kernel, launched with programmatic stream serialisation) set itself up and
     // fetch its first weights now; it still waits for this grid to complete before it reads the attention output
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();
     const int w = blockIdx.x;
     if (w >= *p.n_work) return;
     const uint32_t raw = smem_u32(smem_raw);
@@ -584,6 +585,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 // Sum of the key splits of one (work item, q head): out = sum_z 2^(m_z - M) O_z / sum_z 2^(m_z - M) l_z with M the
 // largest m_z, the splits taken in index order.  One warp per query row at a time, a lane per four head dimensions.
 __global__ void __launch_bounds__(128) paged_attn_prefill_merge_kernel(const PrefillAttnParams p, const TcPrefillExtra ex) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();
     const int w = blockIdx.x, head = blockIdx.y;
     if (w >= *p.n_work) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -753,10 +756,10 @@ int32_t b2_prefill_attn_tc_launch(b2_ctx* ctx, const PrefillAttnParams& p, int g
         ex.part_ml = ctx->pf_part + slots * HD;
     }
     dim3 grid(grid_work, p.hq, splits);
-    paged_attn_prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(p, ex, mq, mk, mv, mz, mzv);
+    B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, paged_attn_prefill_tc_kernel, grid, dim3(kThreads), (size_t)SMEM_BYTES, ctx->stream, p, ex, mq, mk, mv, mz, mzv));
     B2_LAUNCHED(ctx);
     if (splits > 1) {
-        paged_attn_prefill_merge_kernel<<<dim3(grid_work, p.hq), 128, 0, ctx->stream>>>(p, ex);
+        B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, paged_attn_prefill_merge_kernel, dim3(grid_work, p.hq), dim3(128), 0, ctx->stream, p, ex));
         B2_LAUNCHED(ctx);
     }
     B2_CUDA(cudaGetLastError());

@@ -18,6 +18,10 @@ constexpr unsigned kFull = 0xffffffffu;
 template <int HD>
 __global__ void rope_kv_kernel(const RopeKvParams p) {
     constexpr int V = HD / 64;  // elements per lane per half (1 or 2)
+    // the attention kernel after this one may be scheduled as soon as every CTA of this grid has started; it waits for the
+    // grid's completion itself
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    pdl_wait();  // (launched with programmatic stream serialisation: the projection before it may still be finishing)
     const int heads_total = p.hq + 2 * p.hkv;
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (wid >= p.T * heads_total) return;
@@ -107,9 +111,9 @@ int32_t b2_rope_kv_launch(b2_ctx* ctx, const RopeKvParams& p) {
     const int wpb = 8;
     const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
     if (p.hd == 128)
-        rope_kv_kernel<128><<<grid, wpb * 32, 0, ctx->stream>>>(p);
+        B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, rope_kv_kernel<128>, dim3(grid), dim3(wpb * 32), 0, ctx->stream, p));
     else
-        rope_kv_kernel<64><<<grid, wpb * 32, 0, ctx->stream>>>(p);
+        B2_CUDA(b2_launch_pdl(ctx->pdl_consumers, rope_kv_kernel<64>, dim3(grid), dim3(wpb * 32), 0, ctx->stream, p));
     B2_LAUNCHED(ctx);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
