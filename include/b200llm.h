@@ -77,6 +77,10 @@ int32_t b2_profiler_range(b2_ctx* ctx, int32_t on);
  * the launches of each kernel class of every step, for timeline tools; off by default (also switched on by the
  * environment variable B2_NVTX=1 when the context is created).  No reference counterpart. */
 int32_t b2_nvtx_enable(b2_ctx* ctx, int32_t on);
+/* Environment, read when a context is created: B2_PDL_MIN_TOKENS=n makes the engine launch the small kernels of an
+ * iteration (norms, SwiGLU, RoPE + KV append, attention, split-K sums) the ordinary way when the iteration has fewer
+ * than n tokens, instead of with programmatic stream serialisation (default 1: always programmatic).  For comparison
+ * runs; results are identical either way. */
 /* Number of this library's kernels launched on the context since creation. */
 int32_t b2_launch_count(b2_ctx* ctx, int64_t* out);
 

@@ -58,6 +58,7 @@ struct b2_ctx {
     int* tile_counters = nullptr;  // per row-tile arrival counters of the split-K streaming kernel (self-resetting)
     bool use_tc = true;
     bool pdl_consumers = true;     // norm / SwiGLU / RoPE / attention / split-K sums launched with programmatic stream serialisation
+    int pdl_min_tokens = 1;        // ... by the engine on iterations of at least this many tokens (B2_PDL_MIN_TOKENS at context creation)
     // optional per-kernel-class timing with CUDA events on the launching stream
     bool profile = false;
     // NVTX ranges around every kernel class of a step ("gemm", "attn_decode", ...), for timeline tools; off by default
@@ -96,8 +97,10 @@ int32_t b2_ctx_stage(b2_ctx* ctx, size_t bytes, void** out);
 // Launch with programmatic stream serialisation: the grid may be scheduled while the kernel before it in the stream is
 // still finishing (once every CTA of that kernel has started and signalled, or exited).  The launched kernel must call
 // pdl_wait() before it touches anything an earlier kernel reads or writes.
-// `programmatic` false gives an ordinary launch (iterations of a few tokens: there the early scheduling measured 2-3 %
-// SLOWER, a 64-sequence iteration 7 % and a ~680-token iteration 2.7 % faster).
+// `programmatic` false gives an ordinary launch (kept for comparison: B2_PDL_MIN_TOKENS).  Measured against ordinary
+// launches: decode iterations of 4 to 32 sequences 8-15 % faster, of 64 sequences 6 %, a ~680-token iteration 3 %.  The
+// weight-streaming projection kernel does NOT signal its dependents early: with that, iterations of 1 and 8 sequences
+// were 2.7 % slower than with ordinary launches.
 template <typename... KArgs, typename... Args>
 inline cudaError_t b2_launch_pdl(bool programmatic, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args&&... args) {

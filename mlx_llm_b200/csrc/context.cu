@@ -57,6 +57,7 @@ int32_t b2_ctx_create(int32_t device, b2_ctx** out) {
     B2_CUDA(cudaEventCreate(&c->ev0));
     B2_CUDA(cudaEventCreate(&c->ev1));
     if (const char* v = std::getenv("B2_NVTX")) c->nvtx = v[0] == '1';
+    if (const char* v = std::getenv("B2_PDL_MIN_TOKENS")) c->pdl_min_tokens = std::atoi(v);
     *out = c;
     return B2_OK;
 }

@@ -308,7 +308,7 @@ int32_t b2_engine_forward(b2_model* m, std::vector<SeqStep>& seqs, void* logits_
             s.cache->step_stamp = stamp;
         }
     }
-    ctx->pdl_consumers = T > 32;  // (see b2_launch_pdl: early scheduling pays from the tensor-core projections on)
+    ctx->pdl_consumers = T >= ctx->pdl_min_tokens;  // (see b2_launch_pdl)
     B2_CHECK(b2_model_ensure_rope(m, max_pos));
     // pages for the new tokens (host allocator), then the step descriptors
     for (auto& s : seqs) B2_CHECK(b2_cache_reserve(s.cache, s.n));
